@@ -1,0 +1,269 @@
+/*
+ * sparsetir_b200 — C ABI of the B200 (sm_100a) sparse-operator library.
+ *
+ * The library replaces the functions SparseTIR *builds* for its sparse operators (CSR SpMM,
+ * hyb/ELL SpMM, SDDMM, BSR SpMM, RGMS) and its host-side format conversion routines.  A
+ * built SparseTIR operator is a DSO symbol of type TVMBackendPackedCFunc
+ * (reference: include/tvm/runtime/c_backend_api.h:49-51) that LibraryModule wraps into a
+ * PackedFunc (src/runtime/library_module.cc:74-86).  Every `sparsetir_*` operator symbol below
+ * has exactly that type and takes the arguments of the reference function it stands in for,
+ * in the reference's order.  Plain-pointer `*_raw` twins take device pointers and sizes.
+ *
+ * Conventions shared by all operator entry points (they are those of the host stub the
+ * reference generates, src/tir/transforms/make_packed_api.cc:138-305 and
+ * src/tir/transforms/arg_binder.cc:152-282):
+ *   - array arguments are DLTensor* (type code kTVMDLTensorHandle, kTVMNDArrayHandle or
+ *     kTVMOpaqueHandle); every buffer is flat and compact (strides NULL or compact,
+ *     byte_offset 0); all arrays live on the same CUDA device;
+ *   - integer scalars arrive as kTVMArgInt in v_int64;
+ *   - all tensors are borrowed for the duration of the call; outputs are caller-allocated;
+ *   - the call is asynchronous on the stream registered with sparsetir_set_stream for that
+ *     device (default: the legacy default stream); no synchronisation inside;
+ *   - returns 0, or -1 after recording a message readable with sparsetir_get_last_error
+ *     (reference: TVMAPISetLastError / TVMGetLastError, src/runtime/c_runtime_api.cc:371-386).
+ * There is no CPU fallback: a non-CUDA tensor is an error.
+ */
+#ifndef SPARSETIR_B200_H_
+#define SPARSETIR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define SPARSETIR_API
+#else
+#define SPARSETIR_API __attribute__((visibility("default")))
+#endif
+
+/* ---- DLPack tensor (layout identical in DLPack 0.x and 1.x) -------------------------- */
+#ifndef DLPACK_DLPACK_H_
+typedef enum { kDLCPU = 1, kDLCUDA = 2, kDLCUDAHost = 3 } SpDLDeviceType;
+typedef struct { int32_t device_type; int32_t device_id; } DLDevice;
+typedef enum { kDLInt = 0U, kDLUInt = 1U, kDLFloat = 2U } SpDLDataTypeCode;
+typedef struct { uint8_t code; uint8_t bits; uint16_t lanes; } DLDataType;
+typedef struct {
+  void* data;
+  DLDevice device;
+  int32_t ndim;
+  DLDataType dtype;
+  int64_t* shape;
+  int64_t* strides;
+  uint64_t byte_offset;
+} DLTensor;
+#endif
+
+/* ---- TVM PackedFunc calling convention (include/tvm/runtime/c_runtime_api.h:110-151) -- */
+#ifndef TVM_RUNTIME_C_RUNTIME_API_H_
+typedef enum {
+  kTVMArgInt = 0U,
+  kTVMArgFloat = 2U,
+  kTVMOpaqueHandle = 3U,
+  kTVMNullptr = 4U,
+  kTVMDLTensorHandle = 7U,
+  kTVMNDArrayHandle = 13U
+} SpTVMArgTypeCode;
+typedef union {
+  int64_t v_int64;
+  double v_float64;
+  void* v_handle;
+  const char* v_str;
+  DLDataType v_type;
+  DLDevice v_device;
+} TVMValue;
+#endif
+
+#define SPARSETIR_PACKED_ARGS                                                              \
+  TVMValue *args, int *type_codes, int num_args, TVMValue *out_ret_value, int *out_ret_tcode, \
+      void *resource_handle
+
+/* ---- runtime glue -------------------------------------------------------------------- */
+
+/* Message of the last failed call on this thread (TVMGetLastError,
+ * include/tvm/runtime/c_runtime_api.h:195). */
+SPARSETIR_API const char* sparsetir_get_last_error(void);
+
+/* Stream used by later calls from ANY thread for `device_id` (TVMSetStream,
+ * include/tvm/runtime/c_runtime_api.h:496; src/runtime/cuda/cuda_device_api.cc:209-211).
+ * `stream` is a cudaStream_t; NULL selects the legacy default stream. */
+SPARSETIR_API int sparsetir_set_stream(int device_id, void* stream);
+SPARSETIR_API void* sparsetir_get_stream(int device_id);
+
+/* Library version and the compute capability the kernels were compiled for (100). */
+SPARSETIR_API int sparsetir_version(void);
+SPARSETIR_API int sparsetir_sm_arch(void);
+
+/* ---- operators (TVMBackendPackedCFunc symbols) ---------------------------------------- */
+
+/* CSR SpMM, fp32.  C[i,:] = sum_{p in row i} A[p] * B[indices[p],:]; rows without entries are
+ * written as zeros.
+ * args: (a f32[nnz], b f32[n*feat], c f32[m*feat], indptr i32[m+1], indices i32[nnz]
+ *        [, m, n, feat_size, nnz])  — the trailing four integers may be omitted when
+ *        m >= 1 (feat_size is then len(c)/m).
+ * Replaces the function built from `csrmm`
+ * (tests/python/sparsetir/sparse_tir_scripts.py:22-44; flat signature
+ * tests/python/sparsetir/sparse_tir_lowered_buffer_scripts.py:22-39). */
+SPARSETIR_API int sparsetir_csrmm(SPARSETIR_PACKED_ARGS);
+
+/* Decomposed hyb (column-partitioned, ELL-bucketed) SpMM, fp32, one launch for all buckets.
+ * For every bucket q, ELL row r, slot s: C[rows_q[r],:] += W_q[r,s] * B[cols_q[r,s],:].
+ * args: (b f32[n*feat], c f32[m*feat], {w_q f32[nrows_q*width_q], rows_q i32[nrows_q],
+ *        cols_q i32[nrows_q*width_q]} x K, feat_size [, flags])
+ * The bucket width is len(cols_q)/len(rows_q); buckets with no rows are accepted.
+ * flags (bit field, default 0 = reference behaviour: the caller has zero-filled C,
+ * examples/spmm/bench_spmm.py:206):
+ *   SPARSETIR_HYB_ZERO_C       the call zero-fills all of C first;
+ *   SPARSETIR_HYB_REARM        the call first zeroes only the C rows that buckets accumulate
+ *                              into atomically, so that repeated calls on a C that was
+ *                              zero-filled once stay correct;
+ *   SPARSETIR_HYB_ALL_ATOMIC   every bucket accumulates atomically (needed when the same row
+ *                              occurs in several buckets, i.e. with more than one column
+ *                              partition); without it only the LAST bucket triple of the
+ *                              argument list is treated as holding split rows.
+ * Replaces the function built by examples/spmm/bench_spmm.py:116-199 (argument list :207-222). */
+SPARSETIR_API int sparsetir_hyb_spmm(SPARSETIR_PACKED_ARGS);
+#define SPARSETIR_HYB_ZERO_C 1
+#define SPARSETIR_HYB_REARM 2
+#define SPARSETIR_HYB_ALL_ATOMIC 4
+#define SPARSETIR_HYB_MAX_BUCKETS 64
+
+/* SDDMM, fp32.  C[p] = sum_k A[row(p),k] * B[indices[p],k].
+ * args: (a f32[m*feat], b f32[n*feat], c f32[nnz], indptr i32[m+1], indices i32[nnz]
+ *        [, m, n, feat_size, nnz] [, scale f32[nnz]])
+ * A trailing tensor argument, when present, is a per-edge factor multiplied into the result
+ * (not part of the reference operator).
+ * Replaces the functions built from `sddmm` / `fused_sddmm`
+ * (tests/python/sparsetir/sparse_tir_scripts.py:268-318; flat signature
+ * tests/python/sparsetir/sparse_tir_lowered_buffer_scripts.py:458-475). */
+SPARSETIR_API int sparsetir_sddmm(SPARSETIR_PACKED_ARGS);
+
+/* Edge -> row lookup, the preprocess kernel of fused SDDMM:
+ * mid[p] = upper_bound(indptr, p) - 1.
+ * args: (indptr i32[m+1], mid i32[nnz])
+ * Replaces the binary-search block emitted by LowerSparseIter
+ * (src/tir/transforms/lower_sparse_iter.cc:768-783; golden
+ * tests/python/sparsetir/sparse_tir_lowered_buffer_scripts.py:530-549). */
+SPARSETIR_API int sparsetir_sddmm_edge_to_row(SPARSETIR_PACKED_ARGS);
+
+/* BSR SpMM, fp16 blocks and dense operand, fp32 accumulation and output.
+ * C[i*blk+bi, f] = sum_{p in block-row i} sum_bj A[p,bi,bj] * B[indices[p]*blk+bj, f].
+ * args: (a f16[nnzb*blk*blk], b f16[mb*blk*feat], c f32[nb*blk*feat], indptr i32[nb+1],
+ *        indices i32[nnzb], nb, mb, nnzb, blk, feat_size)
+ * (nb = block rows of A and C, mb = block rows of B, the reference's naming.)
+ * Replaces the function built from `bsrmm`
+ * (tests/python/sparsetir/sparse_tir_scripts.py:114-146; call examples/blocksparse/bsr_spmm.py:432). */
+SPARSETIR_API int sparsetir_bsrmm(SPARSETIR_PACKED_ARGS);
+
+/* RGMS (relational gather-matmul-scatter), fp32.
+ * Y[I[i], fo] += sum_{p in CSF row i of relation r} A[p] * sum_fi W[r,fo,fi] * X[J[p],fi],
+ * accumulated over all relations into the caller's Y (zero-filled by the caller, as
+ * examples/rgms/rgcn/bench_rgcn_non_composable.py:88-90 does).
+ * args: (a f32[nnz_j], w f32[R*feat*feat], x f32[n*feat], y f32[m*feat], indptr_i i32[R+1],
+ *        indices_i i32[nnz_i], indptr_j i32[nnz_i+1], indices_j i32[nnz_j]
+ *        [, m, n, num_rels, feat_size, nnz_i, nnz_j])  — feat_size is inferred from
+ *        len(w) = R*feat^2 when the scalars are omitted.
+ * Replaces the function built from `rgcn_hetero_forward`
+ * (tests/python/sparsetir/sparse_tir_scripts.py:468-499; call
+ * examples/rgms/rgcn/bench_rgcn_non_composable.py:108). */
+SPARSETIR_API int sparsetir_rgms(SPARSETIR_PACKED_ARGS);
+
+/* ---- operators, plain-pointer form (device pointers; stream is a cudaStream_t) -------- */
+SPARSETIR_API int sparsetir_csrmm_raw(const float* a, const float* b, float* c,
+                                      const int32_t* indptr, const int32_t* indices, int m, int n,
+                                      int feat, int nnz, int device_id, void* stream);
+
+typedef struct {
+  const float* w;      /* [nrows*width] */
+  const int32_t* rows; /* [nrows] */
+  const int32_t* cols; /* [nrows*width] */
+  int32_t nrows;
+  int32_t width;
+} SparsetirEllBucket;
+SPARSETIR_API int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirEllBucket* buckets,
+                                         int num_buckets, int m, int n, int feat, int flags,
+                                         int device_id, void* stream);
+SPARSETIR_API int sparsetir_sddmm_raw(const float* a, const float* b, float* c,
+                                      const int32_t* indptr, const int32_t* indices,
+                                      const float* scale, int m, int n, int feat, int nnz,
+                                      int device_id, void* stream);
+SPARSETIR_API int sparsetir_sddmm_edge_to_row_raw(const int32_t* indptr, int32_t* mid, int m,
+                                                  int nnz, int device_id, void* stream);
+SPARSETIR_API int sparsetir_bsrmm_raw(const void* a_f16, const void* b_f16, float* c,
+                                      const int32_t* indptr, const int32_t* indices, int nb,
+                                      int mb, int nnzb, int blk, int feat, int device_id,
+                                      void* stream);
+SPARSETIR_API int sparsetir_rgms_raw(const float* a, const float* w, const float* x, float* y,
+                                     const int32_t* indptr_i, const int32_t* indices_i,
+                                     const int32_t* indptr_j, const int32_t* indices_j, int m,
+                                     int n, int num_rels, int feat, int nnz_i, int nnz_j,
+                                     int device_id, void* stream);
+
+/* ---- host-side format conversion (CPU int32 arrays) ----------------------------------- */
+
+/* Column partitioning + ELL bucketing of a CSR matrix, bit-exact with ColumnPartHyb
+ * (src/sparse/format.cc:46-168; Python wrapper python/tvm/sparse/format.py:89-116).
+ * The reference returns Array<Array<Array<NDArray>>>; without TVM's object system the result
+ * is an opaque handle that is queried per (partition, bucket) and then freed.
+ *   indptr i32[num_rows+1], indices i32[nnz]  host memory
+ *   buckets: ascending ELL widths;  num_threads <= 0 selects the hardware concurrency.
+ * Returns NULL after recording an error. */
+typedef struct SparsetirHyb SparsetirHyb;
+SPARSETIR_API SparsetirHyb* sparsetir_column_part_hyb(int num_rows, int num_cols,
+                                                      const int32_t* indptr,
+                                                      const int32_t* indices, int num_col_parts,
+                                                      const int32_t* buckets, int num_buckets,
+                                                      int num_threads);
+/* number of ELL rows of bucket (part, bucket) */
+SPARSETIR_API int64_t sparsetir_hyb_num_rows(const SparsetirHyb* h, int part, int bucket);
+/* Copies the bucket's arrays into caller buffers (any may be NULL):
+ * row_indices i32[nrows], col_indices i32[nrows*width], mask i32[nrows*width] are the
+ * reference's three outputs (format.cc:146-149); csr_pos i32[nrows*width] is the CSR position
+ * each slot came from (-1 for padding) — the gather index of the reference's rewrite_A copy
+ * blocks (src/tir/transforms/sparse_format_decompose.cc:242-268); values f32[nrows*width] is
+ * csr_data[csr_pos] (0 for padding) when csr_data is non-NULL. */
+SPARSETIR_API int sparsetir_hyb_copy_bucket(const SparsetirHyb* h, int part, int bucket,
+                                            int32_t* row_indices, int32_t* col_indices,
+                                            int32_t* mask, int32_t* csr_pos,
+                                            const float* csr_data, float* values);
+SPARSETIR_API void sparsetir_hyb_free(SparsetirHyb* h);
+
+/* TC-GNN style condensing, bit-exact with ConDense (src/sparse/format.cc:353-429; wrapper
+ * python/tvm/sparse/format.py:119-139).  Two-call pattern: with tile_indices == NULL only the
+ * number of groups is returned; group_indptr i32[ceil(n/t)+1], tile_indices i32[groups*g],
+ * mask i32[groups*t*g].  Returns the number of groups, or -1 on error. */
+SPARSETIR_API int64_t sparsetir_condense(int num_rows, const int32_t* indptr, const int32_t* indices,
+                                         int t, int g, int32_t* group_indptr,
+                                         int32_t* tile_indices, int32_t* mask);
+
+/* 3-level CSF -> per-bucket ELL3D, bit-exact with CSFToELL3D (src/sparse/format.cc:180-343;
+ * wrapper python/tvm/sparse/format.py:142-170).  Opaque handle like column_part_hyb. */
+typedef struct SparsetirEll3d SparsetirEll3d;
+SPARSETIR_API SparsetirEll3d* sparsetir_csf_to_ell3d(int num_rels, const int32_t* csf_indptr_0,
+                                                     const int32_t* csf_indices_0,
+                                                     const int32_t* csf_indptr_1,
+                                                     const int32_t* csf_indices_1,
+                                                     const int32_t* nnz_rows_bkt,
+                                                     const int32_t* nnz_cols_bkt, int num_buckets);
+SPARSETIR_API int64_t sparsetir_ell3d_num_groups(const SparsetirEll3d* h, int bucket);
+/* indptr i32[num_rels+1], row_indices i32[groups*rows_b], col_indices / mask
+ * i32[groups*rows_b*cols_b] */
+SPARSETIR_API int sparsetir_ell3d_copy_bucket(const SparsetirEll3d* h, int bucket, int32_t* indptr,
+                                              int32_t* row_indices, int32_t* col_indices,
+                                              int32_t* mask);
+SPARSETIR_API void sparsetir_ell3d_free(SparsetirEll3d* h);
+
+/* ---- multi-GPU row partitioning (no counterpart in the reference, which is single-GPU) - */
+
+/* nnz-balanced contiguous row cuts: cuts[k] = first row of shard k (cuts[0] = 0,
+ * cuts[num_shards] = num_rows), chosen so that indptr[cuts[k]] is the first row boundary at or
+ * after k*nnz/num_shards.  cuts i64[num_shards+1]. */
+SPARSETIR_API int sparsetir_row_partition(int num_rows, const int32_t* indptr, int num_shards,
+                                          int64_t* cuts);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSETIR_B200_H_ */

@@ -1,0 +1,198 @@
+"""ctypes loader for the CPU oracle (``oracle/sparse_oracle.c``).
+
+TEST INFRASTRUCTURE ONLY: imported by ``tests/``, by the smoke check and by the
+benchmark's CPU-baseline leg.  The product package never imports this module.
+
+All functions take and return numpy arrays; the ``*_omp`` entry points are the
+same loops spread over host threads (used only for timing the CPU baseline).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_SO = os.path.join(_HERE, "liboracle.so")
+_lib = None
+
+_i32p = ctypes.POINTER(ctypes.c_int32)
+_f32p = ctypes.POINTER(ctypes.c_float)
+_u16p = ctypes.POINTER(ctypes.c_uint16)
+
+
+def build(force: bool = False) -> str:
+    """Compile the oracle with the Makefile beside this file."""
+    src = os.path.join(_HERE, "sparse_oracle.c")
+    if force or not os.path.exists(_SO) or os.path.getmtime(_SO) < os.path.getmtime(src):
+        subprocess.run(["make", "-C", _HERE, "-B", "liboracle.so"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return _SO
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        _lib = ctypes.CDLL(_SO)
+        _lib.oracle_hyb_create.restype = ctypes.c_void_p
+        _lib.oracle_ell3d_create.restype = ctypes.c_void_p
+    return _lib
+
+
+def _i32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.int32)
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _p(a: Optional[np.ndarray], ty):
+    if a is None:
+        return ctypes.cast(None, ty)
+    return a.ctypes.data_as(ty)
+
+
+def num_threads() -> int:
+    return int(lib().oracle_num_threads())
+
+
+# ----------------------------------------------------------------- formats
+def column_part_hyb(num_rows: int, num_cols: int, indptr, indices, num_col_parts: int,
+                    buckets: Sequence[int], with_pos: bool = False):
+    """Returns (row_indices, col_indices, mask[, pos]) as [part][bucket] lists of int32 arrays,
+    shaped like the reference's output (src/sparse/format.cc:146-149)."""
+    L = lib()
+    indptr, indices = _i32(indptr), _i32(indices)
+    bk = _i32(list(buckets))
+    h = ctypes.c_void_p(L.oracle_hyb_create(int(num_rows), int(num_cols), _p(indptr, _i32p),
+                                            _p(indices, _i32p), int(num_col_parts),
+                                            _p(bk, _i32p), len(bk)))
+    rows_o, cols_o, mask_o, pos_o = [], [], [], []
+    try:
+        for p in range(num_col_parts):
+            rp, cp, mp, pp = [], [], [], []
+            for b, width in enumerate(bk):
+                n = L.oracle_hyb_nrows(h, p, b)
+                r = np.empty((n,), np.int32)
+                c = np.empty((n, int(width)), np.int32)
+                m = np.empty((n, int(width)), np.int32)
+                q = np.empty((n, int(width)), np.int32)
+                L.oracle_hyb_copy(h, p, b, _p(r, _i32p), _p(c, _i32p), _p(m, _i32p), _p(q, _i32p))
+                rp.append(r); cp.append(c); mp.append(m); pp.append(q)
+            rows_o.append(rp); cols_o.append(cp); mask_o.append(mp); pos_o.append(pp)
+    finally:
+        L.oracle_hyb_free(h)
+    if with_pos:
+        return rows_o, cols_o, mask_o, pos_o
+    return rows_o, cols_o, mask_o
+
+
+def condense(indptr, indices, t: int, g: int):
+    """(group_indptr[ntiles+1], tile_indices[ngroups, g], mask[ngroups, t, g])."""
+    L = lib()
+    indptr, indices = _i32(indptr), _i32(indices)
+    n = len(indptr) - 1
+    ng = L.oracle_condense(n, _p(indptr, _i32p), _p(indices, _i32p), int(t), int(g),
+                           _p(None, _i32p), _p(None, _i32p), _p(None, _i32p))
+    gi = np.empty(((n + t - 1) // t + 1,), np.int32)
+    ti = np.empty((ng, g), np.int32)
+    mk = np.empty((ng, t, g), np.int32)
+    L.oracle_condense(n, _p(indptr, _i32p), _p(indices, _i32p), int(t), int(g),
+                      _p(gi, _i32p), _p(ti, _i32p), _p(mk, _i32p))
+    return gi, ti, mk
+
+
+def csf_to_ell3d(indptr0, indices0, indptr1, indices1, nnz_rows_bkt: Sequence[int],
+                 nnz_cols_bkt: Sequence[int]):
+    """(indptr, row_indices, col_indices, mask), each a per-bucket list."""
+    L = lib()
+    indptr0, indices0, indptr1, indices1 = map(_i32, (indptr0, indices0, indptr1, indices1))
+    rb, cb = _i32(list(nnz_rows_bkt)), _i32(list(nnz_cols_bkt))
+    R = len(indptr0) - 1
+    h = ctypes.c_void_p(L.oracle_ell3d_create(R, _p(indptr0, _i32p), _p(indices0, _i32p),
+                                              _p(indptr1, _i32p), _p(indices1, _i32p),
+                                              _p(rb, _i32p), _p(cb, _i32p), len(rb)))
+    out = ([], [], [], [])
+    try:
+        for b in range(len(rb)):
+            ng = L.oracle_ell3d_ngroups(h, b, int(rb[b]))
+            ip = np.empty((R + 1,), np.int32)
+            r = np.empty((ng, int(rb[b])), np.int32)
+            c = np.empty((ng, int(rb[b]), int(cb[b])), np.int32)
+            m = np.empty((ng, int(rb[b]), int(cb[b])), np.int32)
+            L.oracle_ell3d_copy(h, b, _p(ip, _i32p), _p(r, _i32p), _p(c, _i32p), _p(m, _i32p))
+            for lst, arr in zip(out, (ip, r, c, m)):
+                lst.append(arr)
+    finally:
+        L.oracle_ell3d_free(h)
+    return out
+
+
+# --------------------------------------------------------------------- ops
+def csrmm(a, b, c, indptr, indices, m, n, feat, omp: bool = False) -> np.ndarray:
+    """Writes into (and returns) ``c``; rows without entries are left untouched."""
+    a, b, indptr, indices = _f32(a), _f32(b), _i32(indptr), _i32(indices)
+    assert c.dtype == np.float32 and c.flags.c_contiguous
+    fn = lib().oracle_csrmm_omp if omp else lib().oracle_csrmm
+    fn(_p(a, _f32p), _p(b, _f32p), _p(c, _f32p), _p(indptr, _i32p), _p(indices, _i32p),
+       int(m), int(n), int(feat), int(len(indices)))
+    return c
+
+
+def ell_spmm(w, rows, cols, b, c, feat) -> np.ndarray:
+    """Accumulates one (partition, bucket) term into ``c``."""
+    w, rows, cols, b = _f32(w), _i32(rows), _i32(cols), _f32(b)
+    nrows = len(rows)
+    width = (cols.size // nrows) if nrows else 0
+    assert c.dtype == np.float32 and c.flags.c_contiguous
+    lib().oracle_ell_spmm(_p(w, _f32p), _p(rows, _i32p), _p(cols, _i32p), nrows, width,
+                          _p(b, _f32p), _p(c, _f32p), int(feat))
+    return c
+
+
+def edge_to_row(indptr, nnz: int) -> np.ndarray:
+    indptr = _i32(indptr)
+    out = np.empty((nnz,), np.int32)
+    lib().oracle_edge_to_row(_p(indptr, _i32p), len(indptr) - 1, int(nnz), _p(out, _i32p))
+    return out
+
+
+def sddmm(a, b, indptr, indices, m, n, feat, scale=None, omp: bool = False) -> np.ndarray:
+    a, b, indptr, indices = _f32(a), _f32(b), _i32(indptr), _i32(indices)
+    sc = None if scale is None else _f32(scale)
+    c = np.zeros((len(indices),), np.float32)
+    fn = lib().oracle_sddmm_omp if omp else lib().oracle_sddmm
+    fn(_p(a, _f32p), _p(b, _f32p), _p(c, _f32p), _p(indptr, _i32p), _p(indices, _i32p),
+       _p(sc, _f32p), int(m), int(n), int(feat), int(len(indices)))
+    return c
+
+
+def bsrmm_f16(a, b, indptr, indices, nb, mb, blk, feat, omp: bool = False) -> np.ndarray:
+    """fp16 blocks and dense operand, fp32 accumulate and output."""
+    a = np.ascontiguousarray(a, dtype=np.float16)
+    b = np.ascontiguousarray(b, dtype=np.float16)
+    indptr, indices = _i32(indptr), _i32(indices)
+    c = np.empty((nb * blk * feat,), np.float32)
+    fn = lib().oracle_bsrmm_f16_omp if omp else lib().oracle_bsrmm_f16
+    fn(_p(a.view(np.uint16), _u16p), _p(b.view(np.uint16), _u16p), _p(c, _f32p),
+       _p(indptr, _i32p), _p(indices, _i32p), int(nb), int(mb), int(len(indices)), int(blk),
+       int(feat))
+    return c
+
+
+def rgms(a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, m, n, num_rels, feat,
+         omp: bool = False) -> np.ndarray:
+    """Accumulates into (and returns) ``y``."""
+    a, w, x = _f32(a), _f32(w), _f32(x)
+    indptr_i, indices_i, indptr_j, indices_j = map(_i32, (indptr_i, indices_i, indptr_j, indices_j))
+    assert y.dtype == np.float32 and y.flags.c_contiguous
+    fn = lib().oracle_rgms_omp if omp else lib().oracle_rgms
+    fn(_p(a, _f32p), _p(w, _f32p), _p(x, _f32p), _p(y, _f32p), _p(indptr_i, _i32p),
+       _p(indices_i, _i32p), _p(indptr_j, _i32p), _p(indices_j, _i32p), int(m), int(n),
+       int(num_rels), int(feat), int(len(indices_i)), int(len(indices_j)))
+    return y

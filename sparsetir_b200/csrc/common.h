@@ -1,0 +1,50 @@
+// Shared host-side plumbing of the library: thread-local error string, per-device stream
+// table, launch checking.  Nothing here allocates device memory.
+#ifndef SPARSETIR_B200_COMMON_H_
+#define SPARSETIR_B200_COMMON_H_
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "sparsetir_b200.h"
+
+namespace sptir {
+
+// Records a printf-style message for sparsetir_get_last_error and returns -1, so that
+// `return fail("...")` mirrors the reference's "set last error, return -1" protocol
+// (src/runtime/c_runtime_api.cc:371-386).
+int fail(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+
+// Makes `device_id` current (the generated reference stub does the same through
+// __tvm_set_device, src/tir/transforms/make_packed_api.cc:286-305).
+int use_device(int device_id);
+
+cudaStream_t stream_for(int device_id);
+
+constexpr int kNumSMs = 148;  // B200
+
+inline int ceil_div(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }
+
+}  // namespace sptir
+
+#define SPTIR_CUDA_OK(expr)                                                                  \
+  do {                                                                                       \
+    cudaError_t err__ = (expr);                                                              \
+    if (err__ != cudaSuccess)                                                                \
+      return ::sptir::fail("CUDA error %s at %s:%d: %s", cudaGetErrorName(err__), __FILE__,  \
+                           __LINE__, cudaGetErrorString(err__));                             \
+  } while (0)
+
+// After a kernel launch: report launch-configuration errors without synchronising.
+#define SPTIR_LAUNCH_OK(name)                                                                \
+  do {                                                                                       \
+    cudaError_t err__ = cudaGetLastError();                                                  \
+    if (err__ != cudaSuccess)                                                                \
+      return ::sptir::fail("launch of %s failed: %s (%s)", name, cudaGetErrorName(err__),    \
+                           cudaGetErrorString(err__));                                       \
+  } while (0)
+
+#endif  // SPARSETIR_B200_COMMON_H_

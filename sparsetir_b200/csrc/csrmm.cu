@@ -1,0 +1,106 @@
+// CSR SpMM, fp32:  C[i,:] = sum_{p in row i} A[p] * B[indices[p],:]
+// Semantics: tests/python/sparsetir/sparse_tir_lowered_buffer_scripts.py:22-68 of the reference;
+// like the reference's scheduled GPU kernel (examples/spmm/bench_spmm_naive.py:102-119) rows
+// without entries are written as zeros.
+//
+// Mapping: a group of LPR lanes owns ROWS_PER_ITEM consecutive rows and streams their stored
+// entries as one contiguous slot stream (see spmm_core.cuh); each lane keeps VPL 16-byte
+// pieces of the output row in registers and stores them when the row's last entry has been
+// consumed.  One writer per output row: no atomics, deterministic summation in CSR order.
+#include "common.h"
+#include "spmm_core.cuh"
+
+namespace sptir {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kRowsPerItem = 4;
+
+template <int LPR, int VPL, int VEC>
+__global__ void __launch_bounds__(kThreads)
+csrmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+             const int32_t* __restrict__ indptr, const int32_t* __restrict__ indices, int m,
+             int feat) {
+  using V = typename Vec<VEC>::type;
+  constexpr int SUBS = kThreads / LPR;
+  const int lane = threadIdx.x % LPR;
+  const unsigned mask = group_mask<LPR>();
+  const long long item = static_cast<long long>(blockIdx.x) * SUBS + threadIdx.x / LPR;
+  const long long r0l = item * kRowsPerItem;
+  if (r0l >= m) return;
+  const int r0 = static_cast<int>(r0l);
+  const int r1 = min(m, r0 + kRowsPerItem);
+  const FeatLane<LPR, VPL, VEC> fl(feat, blockIdx.y, lane);
+  V* cv = reinterpret_cast<V*>(c);
+
+  int row = r0;
+  int row_end = __ldg(indptr + r0 + 1);
+  const int p0 = __ldg(indptr + r0);
+  const int p1 = __ldg(indptr + r1);
+  int p = p0;  // next slot to be consumed
+
+  V acc[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) acc[v] = Vec<VEC>::zero();
+
+  auto flush_finished_rows = [&]() {
+    // store every row whose last entry has been consumed (also rows without entries)
+    while (row < r1 && p >= row_end) {
+      V* dst = cv + static_cast<size_t>(row) * fl.row_vecs;
+#pragma unroll
+      for (int v = 0; v < VPL; ++v) {
+        if (fl.valid[v]) dst[fl.off[v]] = acc[v];
+        acc[v] = Vec<VEC>::zero();
+      }
+      ++row;
+      if (row < r1) row_end = __ldg(indptr + row + 1);
+    }
+  };
+
+  flush_finished_rows();  // leading empty rows
+  stream_slots<LPR, VPL, VEC>(indices + p0, a + p0, p1 - p0, reinterpret_cast<const V*>(b), fl,
+                              lane, mask, acc, [&](V(&)[VPL]) {
+                                ++p;
+                                flush_finished_rows();
+                              });
+}
+
+template <int LPR, int VPL, int VEC>
+int launch(const float* a, const float* b, float* c, const int32_t* indptr, const int32_t* indices,
+           int m, int feat, cudaStream_t stream) {
+  constexpr int SUBS = kThreads / LPR;
+  const int tile_feat = LPR * VPL * VEC;
+  dim3 grid(ceil_div(ceil_div(m, kRowsPerItem), SUBS), ceil_div(feat, tile_feat));
+  csrmm_kernel<LPR, VPL, VEC><<<grid, kThreads, 0, stream>>>(a, b, c, indptr, indices, m, feat);
+  SPTIR_LAUNCH_OK("csrmm_kernel");
+  return 0;
+}
+
+}  // namespace
+}  // namespace sptir
+
+extern "C" int sparsetir_csrmm_raw(const float* a, const float* b, float* c, const int32_t* indptr,
+                                   const int32_t* indices, int m, int n, int feat, int nnz,
+                                   int device_id, void* stream) {
+  using namespace sptir;
+  (void)n;
+  if (m < 0 || feat < 0 || nnz < 0) return fail("sparsetir_csrmm: negative size");
+  if (m == 0 || feat == 0) return 0;
+  if (!b || !c || !indptr || (nnz > 0 && (!a || !indices)))
+    return fail("sparsetir_csrmm: null pointer argument");
+  if (use_device(device_id) != 0) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
+  if (vec4) {
+    const int nv = feat / 4;
+    if (nv <= 8) return launch<8, 1, 4>(a, b, c, indptr, indices, m, feat, st);
+    if (nv <= 16) return launch<16, 1, 4>(a, b, c, indptr, indices, m, feat, st);
+    if (nv <= 32) return launch<32, 1, 4>(a, b, c, indptr, indices, m, feat, st);
+    if (nv <= 64) return launch<32, 2, 4>(a, b, c, indptr, indices, m, feat, st);
+    return launch<32, 4, 4>(a, b, c, indptr, indices, m, feat, st);  // tiles of 512 features
+  }
+  if (feat <= 8) return launch<8, 1, 1>(a, b, c, indptr, indices, m, feat, st);
+  if (feat <= 16) return launch<16, 1, 1>(a, b, c, indptr, indices, m, feat, st);
+  if (feat <= 32) return launch<32, 1, 1>(a, b, c, indptr, indices, m, feat, st);
+  return launch<32, 4, 1>(a, b, c, indptr, indices, m, feat, st);  // tiles of 128 features
+}

@@ -1,0 +1,205 @@
+// Decomposed hyb SpMM, fp32: for every (partition, bucket) array q, ELL row r, slot s
+//     C[rows_q[r], :] (+)= W_q[r,s] * B[cols_q[r,s], :]
+// Replaces the horizontally fused kernel the reference generates in
+// examples/spmm/bench_spmm.py:116-199 (argument list :207-222).  As there, ONE launch covers
+// all buckets: the blockIdx.x range is the concatenation of the buckets' block ranges
+// (the idea of src/tir/transforms/horizontal_fusion.cc:80-171), described by a small table
+// passed by value in the kernel parameters — no device-side scratch, no host->device copy.
+//
+// Differences from the reference schedule, all invisible in the results:
+//  - work per sub-warp is a fixed number of slots (~kSlotsPerItem), i.e. several ELL rows of a
+//    narrow bucket or one ELL row of a wide one; wide buckets are scheduled first so the long
+//    items do not form the tail of the launch;
+//  - whether an ELL row must be accumulated atomically is decided per ELL row, from the data:
+//    a row id that equals its neighbour's id in the same array is a row that was split into
+//    several ELL rows (src/sparse/format.cc:110-116) and is reduced with one 16-byte vector
+//    atomic per lane; every other ELL row is the only writer of its output row and is stored.
+//    The reference marks whole buckets atomic instead (bench_spmm.py:170,174-177).
+//    With several column partitions the same output row appears in several arrays, which the
+//    kernel cannot see; the caller says so with SPARSETIR_HYB_ALL_ATOMIC.
+#include <algorithm>
+#include <vector>
+
+#include "common.h"
+#include "spmm_core.cuh"
+
+namespace sptir {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kSlotsPerItem = 32;
+constexpr int kMaxB = SPARSETIR_HYB_MAX_BUCKETS;
+
+struct HybTable {
+  const float* w[kMaxB];
+  const int32_t* rows[kMaxB];
+  const int32_t* cols[kMaxB];
+  int32_t nrows[kMaxB];
+  int32_t width[kMaxB];
+  int32_t rows_per_item[kMaxB];
+  int32_t block_start[kMaxB + 1];
+  int32_t nb;
+};
+
+__device__ __forceinline__ int find_bucket(const HybTable& tb, int block) {
+  int q = 0;
+  while (q + 1 < tb.nb && block >= tb.block_start[q + 1]) ++q;
+  return q;
+}
+
+__device__ __forceinline__ bool is_split_row(const int32_t* __restrict__ rows, int r, int nrows,
+                                             int row) {
+  return (r > 0 && __ldg(rows + r - 1) == row) || (r + 1 < nrows && __ldg(rows + r + 1) == row);
+}
+
+template <int LPR, int VPL, int VEC>
+__global__ void __launch_bounds__(kThreads)
+hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b,
+                float* __restrict__ c, int feat, int all_atomic) {
+  using V = typename Vec<VEC>::type;
+  constexpr int SUBS = kThreads / LPR;
+  const int lane = threadIdx.x % LPR;
+  const unsigned mask = group_mask<LPR>();
+  const int q = find_bucket(tb, blockIdx.x);
+  const int width = tb.width[q], nrows = tb.nrows[q], rpi = tb.rows_per_item[q];
+  const long long item =
+      static_cast<long long>(blockIdx.x - tb.block_start[q]) * SUBS + threadIdx.x / LPR;
+  const long long r0l = item * rpi;
+  if (r0l >= nrows) return;
+  const int r0 = static_cast<int>(r0l);
+  const int r1 = min(nrows, r0 + rpi);
+  const int32_t* __restrict__ rows = tb.rows[q];
+  const FeatLane<LPR, VPL, VEC> fl(feat, blockIdx.y, lane);
+  V* cv = reinterpret_cast<V*>(c);
+
+  V acc[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) acc[v] = Vec<VEC>::zero();
+  int r = r0, left = width;
+  const size_t first = static_cast<size_t>(r0) * width;
+  stream_slots<LPR, VPL, VEC>(
+      tb.cols[q] + first, tb.w[q] + first, (r1 - r0) * width, reinterpret_cast<const V*>(b), fl,
+      lane, mask, acc, [&](V(&)[VPL]) {
+        if (--left != 0) return;
+        const int row = __ldg(rows + r);
+        const bool atomic = all_atomic || is_split_row(rows, r, nrows, row);
+        V* dst = cv + static_cast<size_t>(row) * fl.row_vecs;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) {
+          if (fl.valid[v]) {
+            if (atomic) Vec<VEC>::atomic_add(dst + fl.off[v], acc[v]);
+            else dst[fl.off[v]] = acc[v];
+          }
+          acc[v] = Vec<VEC>::zero();
+        }
+        ++r;
+        left = width;
+      });
+}
+
+// Zeroes the output rows that the main kernel will accumulate into atomically (split rows),
+// so that repeated calls on the same C stay correct without a full memset.
+__global__ void __launch_bounds__(kThreads)
+hyb_rearm_kernel(const __grid_constant__ HybTable tb, float* __restrict__ c, int feat) {
+  const int q = find_bucket(tb, blockIdx.x);
+  const int nrows = tb.nrows[q];
+  const int32_t* __restrict__ rows = tb.rows[q];
+  const int warps = kThreads / 32;
+  const long long r = static_cast<long long>(blockIdx.x - tb.block_start[q]) * warps +
+                      threadIdx.x / 32;
+  if (r >= nrows) return;
+  const int row = __ldg(rows + r);
+  if (!is_split_row(rows, static_cast<int>(r), nrows, row)) return;
+  float* dst = c + static_cast<size_t>(row) * feat;
+  for (int f = threadIdx.x % 32; f < feat; f += 32) dst[f] = 0.f;
+}
+
+template <int LPR, int VPL, int VEC>
+int launch(HybTable& tb, const float* b, float* c, int feat, int all_atomic, cudaStream_t stream) {
+  constexpr int SUBS = kThreads / LPR;
+  long long blocks = 0;
+  for (int q = 0; q < tb.nb; ++q) {
+    tb.rows_per_item[q] = std::max(1, kSlotsPerItem / tb.width[q]);
+    tb.block_start[q] = static_cast<int32_t>(blocks);
+    blocks += ceil_div(ceil_div(tb.nrows[q], tb.rows_per_item[q]), SUBS);
+  }
+  tb.block_start[tb.nb] = static_cast<int32_t>(blocks);
+  if (blocks > INT32_MAX) return fail("sparsetir_hyb_spmm: too many thread blocks");
+  const int tile_feat = LPR * VPL * VEC;
+  dim3 grid(static_cast<unsigned>(blocks), ceil_div(feat, tile_feat));
+  hyb_spmm_kernel<LPR, VPL, VEC><<<grid, kThreads, 0, stream>>>(tb, b, c, feat, all_atomic);
+  SPTIR_LAUNCH_OK("hyb_spmm_kernel");
+  return 0;
+}
+
+}  // namespace
+}  // namespace sptir
+
+extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirEllBucket* buckets,
+                                      int num_buckets, int m, int n, int feat, int flags,
+                                      int device_id, void* stream) {
+  using namespace sptir;
+  (void)n;
+  if (num_buckets < 0 || num_buckets > kMaxB)
+    return fail("sparsetir_hyb_spmm: %d buckets exceed the maximum of %d", num_buckets, kMaxB);
+  if (m < 0 || feat < 0) return fail("sparsetir_hyb_spmm: negative size");
+  if (num_buckets > 0 && !buckets) return fail("sparsetir_hyb_spmm: null bucket table");
+  if (feat == 0 || m == 0) return 0;
+  if (!b || !c) return fail("sparsetir_hyb_spmm: null pointer argument");
+  if (use_device(device_id) != 0) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int all_atomic = (flags & SPARSETIR_HYB_ALL_ATOMIC) ? 1 : 0;
+
+  // Table in launch order: widest bucket first, empty buckets dropped.
+  std::vector<int> order;
+  for (int q = 0; q < num_buckets; ++q) {
+    const SparsetirEllBucket& bk = buckets[q];
+    if (bk.nrows < 0 || bk.width < 0) return fail("sparsetir_hyb_spmm: negative bucket size");
+    if (bk.nrows == 0) continue;
+    if (bk.width == 0) return fail("sparsetir_hyb_spmm: bucket %d has rows but width 0", q);
+    if (!bk.w || !bk.rows || !bk.cols) return fail("sparsetir_hyb_spmm: null bucket array");
+    order.push_back(q);
+  }
+  std::stable_sort(order.begin(), order.end(),
+                   [&](int x, int y) { return buckets[x].width > buckets[y].width; });
+  HybTable tb{};
+  tb.nb = static_cast<int32_t>(order.size());
+  for (int k = 0; k < tb.nb; ++k) {
+    const SparsetirEllBucket& bk = buckets[order[k]];
+    tb.w[k] = bk.w; tb.rows[k] = bk.rows; tb.cols[k] = bk.cols;
+    tb.nrows[k] = bk.nrows; tb.width[k] = bk.width;
+  }
+
+  if (flags & SPARSETIR_HYB_ZERO_C) {
+    SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(m) * feat * sizeof(float), st));
+  } else if (flags & SPARSETIR_HYB_REARM) {
+    if (all_atomic) {
+      SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(m) * feat * sizeof(float), st));
+    } else if (tb.nb > 0) {
+      long long blocks = 0;
+      for (int q = 0; q < tb.nb; ++q) {
+        tb.block_start[q] = static_cast<int32_t>(blocks);
+        blocks += ceil_div(tb.nrows[q], kThreads / 32);
+      }
+      tb.block_start[tb.nb] = static_cast<int32_t>(blocks);
+      if (blocks > INT32_MAX) return fail("sparsetir_hyb_spmm: too many thread blocks");
+      hyb_rearm_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(tb, c, feat);
+      SPTIR_LAUNCH_OK("hyb_rearm_kernel");
+    }
+  }
+  if (tb.nb == 0) return 0;
+
+  bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
+  if (vec4) {
+    const int nv = feat / 4;
+    if (nv <= 8) return launch<8, 1, 4>(tb, b, c, feat, all_atomic, st);
+    if (nv <= 16) return launch<16, 1, 4>(tb, b, c, feat, all_atomic, st);
+    if (nv <= 32) return launch<32, 1, 4>(tb, b, c, feat, all_atomic, st);
+    if (nv <= 64) return launch<32, 2, 4>(tb, b, c, feat, all_atomic, st);
+    return launch<32, 4, 4>(tb, b, c, feat, all_atomic, st);
+  }
+  if (feat <= 8) return launch<8, 1, 1>(tb, b, c, feat, all_atomic, st);
+  if (feat <= 16) return launch<16, 1, 1>(tb, b, c, feat, all_atomic, st);
+  if (feat <= 32) return launch<32, 1, 1>(tb, b, c, feat, all_atomic, st);
+  return launch<32, 4, 1>(tb, b, c, feat, all_atomic, st);
+}

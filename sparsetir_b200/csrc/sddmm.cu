@@ -1,0 +1,236 @@
+// SDDMM, fp32:  C[p] = sum_k A[row(p),k] * B[indices[p],k]   (optionally times scale[p])
+// Semantics: tests/python/sparsetir/sparse_tir_lowered_buffer_scripts.py:458-507 (sddmm) and
+// :510-569 (fused_sddmm with the edge->row binary search) of the reference; generated kernel
+// being replaced: examples/sddmm/bench_sddmm.py:97-167.
+//
+// Mapping.  The reference runs a separate preprocess kernel that stores row(p) for every
+// stored position and then gives every (ty, group) slot one edge with the dot product split
+// over tx lanes and reduced across threads.  Here one kernel does both:
+//  - a warp owns a contiguous range of stored positions and walks it 32 positions at a time;
+//    lane l reads indices[base+l] (coalesced) and finds row(base+l) by advancing from the
+//    warp's current row through indptr (the positions are sorted by row, so this is a short
+//    walk, with a binary search as the fallback for long runs of empty rows);
+//  - the 32 positions are split over the warp's sub-warps of LPR lanes, LPR positions each;
+//    a sub-warp loads the B row of one position at a time (every lane VPL 16-byte pieces,
+//    several positions in flight), keeps the A row in registers while the row id stays the
+//    same, and accumulates one partial sum per position in its own registers;
+//  - the LPR partial sums held by each of the LPR lanes are then reduced with a transposing
+//    butterfly: LPR-1 shuffles leave lane l with the finished dot product of position l,
+//    instead of log2(LPR) shuffles per position; the warp stores 32 consecutive results with
+//    one coalesced store.
+#include "common.h"
+#include "vec.cuh"
+
+namespace sptir {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kEdgesPerWarp = 256;
+
+// row(p) = upper_bound(indptr[0..m], p) - 1, the search of
+// tests/python/sparsetir/sparse_tir_lowered_buffer_scripts.py:530-549
+__device__ __forceinline__ int edge_row_search(const int32_t* __restrict__ indptr, int lo_row,
+                                               int m, int p) {
+  int low = lo_row, high = m + 1;
+  while (low < high) {
+    int mid = low + (high - low) / 2;
+    if (__ldg(indptr + mid) > p) high = mid; else low = mid + 1;
+  }
+  return low - 1;
+}
+
+template <int LPR, int VPL, int VEC>
+__global__ void __launch_bounds__(kThreads)
+sddmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+             const int32_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+             const float* __restrict__ scale, int m, int feat, int nnz) {
+  using V = typename Vec<VEC>::type;
+  constexpr int U = (8 / VPL) < LPR ? (8 / VPL) : LPR;  // positions whose B rows are in flight
+  const int wlane = threadIdx.x & 31;
+  const int lane = wlane % LPR;
+  const int sub = wlane / LPR;
+  const unsigned mask = group_mask<LPR>();
+  const long long warp = static_cast<long long>(blockIdx.x) * (kThreads / 32) + threadIdx.x / 32;
+  const long long e_begin = warp * kEdgesPerWarp;
+  if (e_begin >= nnz) return;
+  const int e_end = static_cast<int>(min(static_cast<long long>(nnz), e_begin + kEdgesPerWarp));
+  const int row_vecs = feat / VEC;
+  const V* av = reinterpret_cast<const V*>(a);
+  const V* bv = reinterpret_cast<const V*>(b);
+
+  int off[VPL];
+  bool valid[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) {
+    off[v] = v * LPR + lane;
+    valid[v] = off[v] < row_vecs;
+  }
+
+  int warp_row = edge_row_search(indptr, 0, m, static_cast<int>(e_begin));
+  int cur_row = -1;
+  V arow[VPL];
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) arow[v] = Vec<VEC>::zero();
+
+  for (int base = static_cast<int>(e_begin); base < e_end; base += 32) {
+    const int e = base + wlane;
+    const bool live = e < e_end;
+    int col = 0, row = warp_row;
+    if (live) {
+      col = __ldg(indices + e);
+      int steps = 0;
+      while (__ldg(indptr + row + 1) <= e) {
+        ++row;
+        if (++steps == 8) {  // long run of empty rows: finish with a search
+          row = edge_row_search(indptr, row, m, e);
+          break;
+        }
+      }
+    }
+    // the next batch starts from the row of this batch's last live position
+    warp_row = __shfl_sync(0xffffffffu, row, min(31, e_end - 1 - base));
+
+    const int cnt = min(LPR, e_end - (base + sub * LPR));  // live positions of this sub-warp (may be <= 0)
+    float part[LPR];
+#pragma unroll
+    for (int k = 0; k < LPR; ++k) part[k] = 0.f;
+#pragma unroll
+    for (int k0 = 0; k0 < LPR; k0 += U) {
+      if (k0 < cnt) {  // uniform inside the sub-warp
+        V x[U][VPL];
+        int rk[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          int ck = __shfl_sync(mask, col, k0 + u, LPR);  // dead positions carry column 0
+          rk[u] = __shfl_sync(mask, row, k0 + u, LPR);
+          const V* src = bv + static_cast<size_t>(ck) * row_vecs;
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) x[u][v] = valid[v] ? __ldg(src + off[v]) : Vec<VEC>::zero();
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (rk[u] != cur_row) {  // uniform inside the sub-warp
+            cur_row = rk[u];
+            const V* src = av + static_cast<size_t>(cur_row) * row_vecs;
+#pragma unroll
+            for (int v = 0; v < VPL; ++v) arow[v] = valid[v] ? __ldg(src + off[v]) : Vec<VEC>::zero();
+          }
+          float s = 0.f;
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) s = Vec<VEC>::dot(arow[v], x[u][v], s);
+          part[k0 + u] = s;
+        }
+      }
+    }
+    // transposing butterfly: afterwards part[0] of lane l is the dot product of position l
+#pragma unroll
+    for (int offl = LPR / 2, n = LPR; offl >= 1; offl >>= 1, n >>= 1) {
+      const bool upper = (lane & offl) != 0;
+#pragma unroll
+      for (int i = 0; i < n / 2; ++i) {
+        float send = upper ? part[i] : part[i + n / 2];
+        float keep = upper ? part[i + n / 2] : part[i];
+        part[i] = keep + __shfl_xor_sync(mask, send, offl, LPR);
+      }
+    }
+    if (live) {
+      float r = part[0];
+      if (scale != nullptr) r *= __ldg(scale + e);
+      c[e] = r;
+    }
+  }
+}
+
+// Fallback for feature sizes beyond the register-resident variants: a full warp per position,
+// looping over the feature dimension.
+__global__ void __launch_bounds__(kThreads)
+sddmm_generic_kernel(const float* __restrict__ a, const float* __restrict__ b,
+                     float* __restrict__ c, const int32_t* __restrict__ indptr,
+                     const int32_t* __restrict__ indices, const float* __restrict__ scale, int m,
+                     int feat, int nnz) {
+  const int lane = threadIdx.x & 31;
+  const long long warp = static_cast<long long>(blockIdx.x) * (kThreads / 32) + threadIdx.x / 32;
+  const long long e_begin = warp * 32;
+  if (e_begin >= nnz) return;
+  const int e_end = static_cast<int>(min(static_cast<long long>(nnz), e_begin + 32));
+  int row = edge_row_search(indptr, 0, m, static_cast<int>(e_begin));
+  for (int e = static_cast<int>(e_begin); e < e_end; ++e) {
+    while (__ldg(indptr + row + 1) <= e) ++row;
+    const float* ar = a + static_cast<size_t>(row) * feat;
+    const float* br = b + static_cast<size_t>(__ldg(indices + e)) * feat;
+    float s = 0.f;
+    for (int k = lane; k < feat; k += 32) s = fmaf(__ldg(ar + k), __ldg(br + k), s);
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) c[e] = scale ? s * __ldg(scale + e) : s;
+  }
+}
+
+__global__ void __launch_bounds__(kThreads)
+edge_to_row_kernel(const int32_t* __restrict__ indptr, int32_t* __restrict__ mid, int m, int nnz) {
+  const long long p = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x;
+  if (p < nnz) mid[p] = edge_row_search(indptr, 0, m, static_cast<int>(p));
+}
+
+template <int LPR, int VPL, int VEC>
+int launch(const float* a, const float* b, float* c, const int32_t* indptr, const int32_t* indices,
+           const float* scale, int m, int feat, int nnz, cudaStream_t stream) {
+  const int warps = ceil_div(nnz, kEdgesPerWarp);
+  const int blocks = ceil_div(warps, kThreads / 32);
+  sddmm_kernel<LPR, VPL, VEC><<<blocks, kThreads, 0, stream>>>(a, b, c, indptr, indices, scale, m,
+                                                              feat, nnz);
+  SPTIR_LAUNCH_OK("sddmm_kernel");
+  return 0;
+}
+
+}  // namespace
+}  // namespace sptir
+
+extern "C" int sparsetir_sddmm_raw(const float* a, const float* b, float* c, const int32_t* indptr,
+                                   const int32_t* indices, const float* scale, int m, int n,
+                                   int feat, int nnz, int device_id, void* stream) {
+  using namespace sptir;
+  (void)n;
+  if (m < 0 || feat < 0 || nnz < 0) return fail("sparsetir_sddmm: negative size");
+  if (nnz == 0) return 0;
+  if (!c || !indptr || !indices || (feat > 0 && (!a || !b)))
+    return fail("sparsetir_sddmm: null pointer argument");
+  if (use_device(device_id) != 0) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (feat == 0) {
+    SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(nnz) * sizeof(float), st));
+    return 0;
+  }
+  const bool vec4 = (feat % 4 == 0) && aligned16(a) && aligned16(b);
+  if (vec4) {
+    const int nv = feat / 4;
+    if (nv <= 8) return launch<8, 1, 4>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+    if (nv <= 16) return launch<16, 1, 4>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+    if (nv <= 32) return launch<32, 1, 4>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+    if (nv <= 64) return launch<32, 2, 4>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+    if (nv <= 128) return launch<32, 4, 4>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+  } else {
+    if (feat <= 8) return launch<8, 1, 1>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+    if (feat <= 16) return launch<16, 1, 1>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+    if (feat <= 32) return launch<32, 1, 1>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+    if (feat <= 64) return launch<32, 2, 1>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+    if (feat <= 128) return launch<32, 4, 1>(a, b, c, indptr, indices, scale, m, feat, nnz, st);
+  }
+  const int blocks = ceil_div(ceil_div(nnz, 32), kThreads / 32);
+  sddmm_generic_kernel<<<blocks, kThreads, 0, st>>>(a, b, c, indptr, indices, scale, m, feat, nnz);
+  SPTIR_LAUNCH_OK("sddmm_generic_kernel");
+  return 0;
+}
+
+extern "C" int sparsetir_sddmm_edge_to_row_raw(const int32_t* indptr, int32_t* mid, int m, int nnz,
+                                               int device_id, void* stream) {
+  using namespace sptir;
+  if (m < 0 || nnz < 0) return fail("sparsetir_sddmm_edge_to_row: negative size");
+  if (nnz == 0) return 0;
+  if (!indptr || !mid) return fail("sparsetir_sddmm_edge_to_row: null pointer argument");
+  if (use_device(device_id) != 0) return -1;
+  edge_to_row_kernel<<<ceil_div(nnz, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      indptr, mid, m, nnz);
+  SPTIR_LAUNCH_OK("edge_to_row_kernel");
+  return 0;
+}

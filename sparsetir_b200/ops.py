@@ -1,0 +1,162 @@
+"""Python host side of the operator boundary.
+
+``PackedFunc`` mirrors how a built SparseTIR operator is called in the reference
+(``f(*args)`` on a ``tvm.runtime.Module``, python/tvm/runtime/module.py:239; timing with
+``f.time_evaluator``, src/runtime/profiling.cc:742-795): positional DLTensor / integer
+arguments in the reference's order, outputs written in place, asynchronous on the current
+stream, a raised error when the callee returns -1.  Tensors are ``torch.Tensor`` objects on a
+CUDA device; torch is used only for device memory and streams.
+
+The module-level callables ``csrmm``, ``hyb_spmm``, ``sddmm``, ``sddmm_edge_to_row``, ``bsrmm``
+and ``rgms`` are the packed entry points of ``include/sparsetir_b200.h``.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _lib as L
+
+
+class SparseTIRError(RuntimeError):
+    """Raised when an entry point returns -1 (the counterpart of tvm.TVMError)."""
+
+
+_DTYPES = {
+    torch.float32: (L.kDLFloat, 32),
+    torch.float16: (L.kDLFloat, 16),
+    torch.float64: (L.kDLFloat, 64),
+    torch.int32: (L.kDLInt, 32),
+    torch.int64: (L.kDLInt, 64),
+    torch.uint8: (L.kDLUInt, 8),
+}
+
+
+def to_dltensor(t: torch.Tensor, keepalive: List) -> L.DLTensor:
+    """Borrowed DLTensor view of a torch tensor (no copy)."""
+    if t.dtype not in _DTYPES:
+        raise TypeError(f"unsupported dtype {t.dtype}")
+    code, bits = _DTYPES[t.dtype]
+    shape = (ctypes.c_int64 * max(1, t.dim()))(*t.shape)
+    strides = None
+    if not t.is_contiguous():
+        strides = (ctypes.c_int64 * max(1, t.dim()))(*t.stride())
+    keepalive.extend([shape, strides, t])
+    if t.is_cuda:
+        dev = L.DLDevice(L.kDLCUDA, t.device.index if t.device.index is not None else
+                         torch.cuda.current_device())
+    else:
+        dev = L.DLDevice(L.kDLCPU, 0)
+    return L.DLTensor(
+        data=ctypes.c_void_p(t.data_ptr() if t.numel() > 0 else 0),
+        device=dev, ndim=t.dim(), dtype=L.DLDataType(code, bits, 1),
+        shape=ctypes.cast(shape, ctypes.POINTER(ctypes.c_int64)),
+        strides=ctypes.cast(strides, ctypes.POINTER(ctypes.c_int64)) if strides is not None else None,
+        byte_offset=0)
+
+
+def use_current_stream(device: Optional[torch.device] = None) -> None:
+    """Registers torch's current stream of ``device`` as the library's stream for it."""
+    idx = torch.cuda.current_device() if device is None or device.index is None else device.index
+    rc = L.load().sparsetir_set_stream(idx, ctypes.c_void_p(torch.cuda.current_stream(idx).cuda_stream))
+    if rc != 0:
+        raise SparseTIRError(L.last_error())
+
+
+class PackedFunc:
+    """A TVMBackendPackedCFunc symbol of the library, callable like the reference's functions."""
+
+    def __init__(self, symbol: str):
+        self.symbol = symbol
+        self._fn = None
+
+    @property
+    def entry_name(self) -> str:
+        return self.symbol
+
+    def _resolve(self):
+        if self._fn is None:
+            self._fn = getattr(L.load(), self.symbol)
+        return self._fn
+
+    def __call__(self, *args) -> None:
+        fn = self._resolve()
+        n = len(args)
+        values = (L.TVMValue * max(1, n))()
+        codes = (ctypes.c_int * max(1, n))()
+        keep: List = []
+        device = None
+        for i, a in enumerate(args):
+            if isinstance(a, torch.Tensor):
+                dl = to_dltensor(a, keep)
+                keep.append(dl)
+                values[i].v_handle = ctypes.cast(ctypes.pointer(dl), ctypes.c_void_p)
+                codes[i] = L.kTVMDLTensorHandle
+                if a.is_cuda and device is None:
+                    device = a.device
+            elif isinstance(a, L.DLTensor):
+                keep.append(a)
+                values[i].v_handle = ctypes.cast(ctypes.pointer(a), ctypes.c_void_p)
+                codes[i] = L.kTVMDLTensorHandle
+            elif isinstance(a, bool) or isinstance(a, int):
+                values[i].v_int64 = int(a)
+                codes[i] = L.kTVMArgInt
+            elif isinstance(a, float):
+                values[i].v_float64 = a
+                codes[i] = L.kTVMArgFloat
+            elif a is None:
+                values[i].v_handle = None
+                codes[i] = L.kTVMNullptr
+            else:
+                raise TypeError(f"argument {i}: unsupported type {type(a)}")
+        if device is not None:
+            use_current_stream(device)
+        ret = L.TVMValue()
+        ret_code = ctypes.c_int(0)
+        rc = fn(values, codes, n, ctypes.byref(ret), ctypes.byref(ret_code), None)
+        if rc != 0:
+            raise SparseTIRError(L.last_error())
+
+    def time_evaluator(self, number: int = 10, repeat: int = 1):
+        """Mirror of the reference's time_evaluator: one untimed call, then ``repeat`` measurements
+        of ``number`` back-to-back calls between two device events; returns a callable that
+        gives the list of per-call mean seconds."""
+
+        def run(*args) -> List[float]:
+            self(*args)
+            out = []
+            for _ in range(repeat):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(number):
+                    self(*args)
+                e1.record()
+                e1.synchronize()
+                out.append(e0.elapsed_time(e1) * 1e-3 / number)
+            return out
+
+        return run
+
+
+csrmm = PackedFunc("sparsetir_csrmm")
+hyb_spmm = PackedFunc("sparsetir_hyb_spmm")
+sddmm = PackedFunc("sparsetir_sddmm")
+sddmm_edge_to_row = PackedFunc("sparsetir_sddmm_edge_to_row")
+bsrmm = PackedFunc("sparsetir_bsrmm")
+rgms = PackedFunc("sparsetir_rgms")
+
+
+def hyb_args(x: torch.Tensor, y: torch.Tensor, buckets: Sequence[Sequence[torch.Tensor]],
+             feat_size: int, flags: int = 0) -> list:
+    """Argument list of ``hyb_spmm`` in the reference's layout
+    (examples/spmm/bench_spmm.py:207-222): ``[b, c] + [w, rows, cols] per bucket`` followed by
+    the scalars this library needs because it is not specialised at build time."""
+    args = [x.reshape(-1), y.reshape(-1)]
+    for w, rows, cols in buckets:
+        args += [w.reshape(-1), rows.reshape(-1), cols.reshape(-1)]
+    args.append(int(feat_size))
+    if flags:
+        args.append(int(flags))
+    return args

@@ -1,0 +1,391 @@
+"""Parity of the CUDA kernels with the CPU oracle, called through the packed C ABI exactly like
+the reference calls a built operator.  Tolerances are the ones stated for this path: bit-exact
+integers; fp32 rtol 1e-4 / atol 1e-5; fp16 inputs with fp32 accumulation rtol 1e-2."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import refimpl
+from oracle import oracle as orc
+from sparsetir_b200 import _lib as L
+from sparsetir_b200 import datagen as dg
+from sparsetir_b200 import format as fmt
+from sparsetir_b200 import ops
+
+pytestmark = pytest.mark.gpu
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+RTOL, ATOL = 1e-4, 1e-5
+
+
+def dev(a, device):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+
+def close(got: torch.Tensor, want: np.ndarray, rtol=RTOL, atol=ATOL):
+    np.testing.assert_allclose(got.cpu().numpy().reshape(want.shape), want, rtol=rtol, atol=atol)
+
+
+# ------------------------------------------------------------------------------ csrmm
+def run_csrmm(c: dg.CSR, x: np.ndarray, device, scalars=False, prefill=0.0):
+    feat = x.shape[1]
+    y = torch.full((c.m * feat,), prefill, dtype=torch.float32, device=device)
+    args = [dev(c.data, device), dev(x.reshape(-1), device), y, dev(c.indptr, device),
+            dev(c.indices, device)]
+    if scalars:
+        args += [c.m, c.n, feat, c.nnz]
+    ops.csrmm(*args)
+    torch.cuda.synchronize()
+    return y.reshape(c.m, feat)
+
+
+def oracle_csrmm(c: dg.CSR, x: np.ndarray):
+    y = np.zeros((c.m, x.shape[1]), np.float32)
+    return orc.csrmm(c.data, x, y, c.indptr, c.indices, c.m, c.n, x.shape[1])
+
+
+@pytest.mark.parametrize("feat", [1, 3, 4, 24, 32, 64, 100, 128, 256, 512, 640])
+def test_csrmm_matches_oracle(cuda_device, feat):
+    c = dg.csr_poisson(m=1000, n=700, mean_deg=10, seed=feat)
+    x = dg.dense_operand(1, c.n, feat)
+    close(run_csrmm(c, x, cuda_device, scalars=feat % 2 == 0), oracle_csrmm(c, x))
+
+
+def test_csrmm_config1_full_size(cuda_device):
+    c = dg.csr_poisson(seed=0)  # 4096 x 4096, Poisson(10)
+    x = dg.dense_operand(0, c.n, 64)
+    got = run_csrmm(c, x, cuda_device)
+    close(got, oracle_csrmm(c, x))
+    close(got, refimpl.spmm_f64(c.indptr, c.indices, c.data, x, c.m, c.n).astype(np.float32))
+
+
+def test_csrmm_golden(cuda_device):
+    g = np.load(os.path.join(GOLD, "csrmm.npz"))
+    c = dg.CSR(g["y"].shape[0], g["x"].shape[0], g["indptr"], g["indices"], g["data"])
+    close(run_csrmm(c, g["x"], cuda_device), g["y"].astype(np.float32))
+
+
+def test_csrmm_empty_rows_are_zeroed_and_long_rows(cuda_device):
+    # empty rows at the start, middle and end; one row far longer than the rest
+    deg = np.array([0, 0, 5, 0, 900, 1, 0, 0, 3, 0, 0], np.int64)
+    rng = np.random.default_rng(0)
+    ip = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+    ix = dg.sorted_distinct_columns(rng, deg, 1000)
+    c = dg.CSR(len(deg), 1000, ip, ix, rng.uniform(-1, 1, len(ix)).astype(np.float32))
+    x = dg.dense_operand(3, 1000, 64)
+    got = run_csrmm(c, x, cuda_device, prefill=9.0)
+    close(got, oracle_csrmm(c, x))
+    assert torch.all(got[[0, 1, 3, 6, 7, 9, 10]] == 0)
+
+
+def test_csrmm_powerlaw_rows(cuda_device):
+    c = dg.csr_powerlaw(n=20000, seed=5)
+    x = dg.dense_operand(6, c.n, 32)
+    close(run_csrmm(c, x, cuda_device), oracle_csrmm(c, x))
+
+
+def test_csrmm_unaligned_operands(cuda_device):
+    c = dg.csr_poisson(m=300, n=300, mean_deg=7, seed=8)
+    x = dg.dense_operand(9, c.n, 16)
+    base = torch.zeros(c.n * 16 + 1, dtype=torch.float32, device=cuda_device)
+    base[1:] = dev(x.reshape(-1), cuda_device)
+    y = torch.zeros(c.m * 16, dtype=torch.float32, device=cuda_device)
+    ops.csrmm(dev(c.data, cuda_device), base[1:], y, dev(c.indptr, cuda_device), dev(c.indices, cuda_device))
+    close(y, oracle_csrmm(c, x))
+
+
+def test_csrmm_all_rows_empty_and_zero_sizes(cuda_device):
+    y = torch.full((5 * 8,), 3.0, device=cuda_device)
+    e_f = torch.zeros(0, device=cuda_device)
+    e_i = torch.zeros(0, dtype=torch.int32, device=cuda_device)
+    ops.csrmm(e_f, torch.ones(4 * 8, device=cuda_device), y,
+              torch.zeros(6, dtype=torch.int32, device=cuda_device), e_i, 5, 4, 8, 0)
+    torch.cuda.synchronize()
+    assert torch.all(y == 0)
+
+
+# ------------------------------------------------------------------------------ hyb spmm
+def hyb_device_buckets(c: dg.CSR, parts, buckets, device, weights="values"):
+    rows, cols, mask, vals, pos = fmt.column_part_hyb(c.m, c.n, c.indptr, c.indices, parts, buckets,
+                                                     data=c.data)
+    host, devb = [], []
+    for p in range(parts):
+        for b in range(len(buckets)):
+            w = vals[p][b] if weights == "values" else mask[p][b].astype(np.float32)
+            host.append((w, rows[p][b], cols[p][b]))
+            devb.append((dev(w, device), dev(rows[p][b], device), dev(cols[p][b], device)))
+    return host, devb
+
+
+def oracle_hyb(host, x, m):
+    y = np.zeros((m, x.shape[1]), np.float32)
+    for w, rows, cols in host:
+        orc.ell_spmm(w, rows, cols, x, y, x.shape[1])
+    return y
+
+
+BK10 = [1, 2, 4, 8, 16, 32, 64, 128, 256, 512]
+
+
+@pytest.mark.parametrize("feat", [32, 64, 128, 256, 512])
+@pytest.mark.parametrize("parts", [1, 2, 4])
+def test_hyb_spmm_matches_oracle(cuda_device, feat, parts):
+    c = dg.csr_powerlaw(n=6000, max_deg=4000, seed=parts)
+    x = dg.dense_operand(feat, c.n, feat)
+    host, devb = hyb_device_buckets(c, parts, BK10, cuda_device)
+    y = torch.zeros(c.m * feat, device=cuda_device)
+    flags = L.HYB_ALL_ATOMIC if parts > 1 else 0
+    ops.hyb_spmm(*ops.hyb_args(dev(x, cuda_device), y, devb, feat, flags))
+    torch.cuda.synchronize()
+    want = oracle_hyb(host, x, c.m)
+    close(y, want)
+    # and the decomposition computes the same product as the CSR form
+    close(y, refimpl.spmm_f64(c.indptr, c.indices, c.data, x, c.m, c.n).astype(np.float32))
+
+
+@pytest.mark.parametrize("feat,buckets,parts", [(8, [1, 3, 5], 1), (20, [2, 7], 3), (33, [1, 2, 4], 2),
+                                                (640, [4, 64], 1), (1, [1, 2], 1)])
+def test_hyb_spmm_odd_shapes(cuda_device, feat, buckets, parts):
+    c = dg.csr_poisson(m=500, n=800, mean_deg=9, seed=feat)
+    x = dg.dense_operand(2, c.n, feat)
+    host, devb = hyb_device_buckets(c, parts, buckets, cuda_device)
+    y = torch.zeros(c.m * feat, device=cuda_device)
+    ops.hyb_spmm(*ops.hyb_args(dev(x, cuda_device), y, devb, feat, L.HYB_ALL_ATOMIC if parts > 1 else 0))
+    torch.cuda.synchronize()
+    close(y, oracle_hyb(host, x, c.m))
+
+
+def test_hyb_spmm_mask_weights_like_reference_example(cuda_device):
+    # examples/spmm/bench_spmm.py:212-214 feeds the mask as weights (unweighted copy_u_sum)
+    c = dg.csr_powerlaw(n=3000, max_deg=2000, seed=21)
+    x = dg.dense_operand(22, c.n, 64)
+    host, devb = hyb_device_buckets(c, 2, [1, 2, 4, 8], cuda_device, weights="mask")
+    y = torch.zeros(c.m * 64, device=cuda_device)
+    ops.hyb_spmm(*ops.hyb_args(dev(x, cuda_device), y, devb, 64, L.HYB_ALL_ATOMIC))
+    torch.cuda.synchronize()
+    ones = dg.CSR(c.m, c.n, c.indptr, c.indices, np.ones(c.nnz, np.float32))
+    close(y, oracle_csrmm(ones, x))
+
+
+def test_hyb_spmm_zero_and_rearm_flags(cuda_device):
+    c = dg.csr_powerlaw(n=4000, max_deg=3000, seed=23)
+    x = dg.dense_operand(24, c.n, 128)
+    host, devb = hyb_device_buckets(c, 1, [1, 2, 4, 8, 16], cuda_device)  # many split rows
+    want = oracle_hyb(host, x, c.m)
+    xd = dev(x, cuda_device)
+    # ZERO_C: garbage in C does not matter
+    y = torch.full((c.m * 128,), 5.0, device=cuda_device)
+    ops.hyb_spmm(*ops.hyb_args(xd, y, devb, 128, L.HYB_ZERO_C))
+    close(y, want)
+    # REARM: repeated calls on a C zero-filled once stay correct
+    y = torch.zeros(c.m * 128, device=cuda_device)
+    for _ in range(3):
+        ops.hyb_spmm(*ops.hyb_args(xd, y, devb, 128, L.HYB_REARM))
+    close(y, want)
+    # reference behaviour (no flag): a second call accumulates into the split rows only
+    y = torch.zeros(c.m * 128, device=cuda_device)
+    ops.hyb_spmm(*ops.hyb_args(xd, y, devb, 128))
+    ops.hyb_spmm(*ops.hyb_args(xd, y, devb, 128))
+    split = np.unique(host[-1][1][np.r_[False, host[-1][1][1:] == host[-1][1][:-1]]])
+    keep = np.setdiff1d(np.arange(c.m), split)
+    got = y.reshape(c.m, 128).cpu().numpy()
+    np.testing.assert_allclose(got[keep], want[keep], rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(got[split], 2 * want[split], rtol=RTOL, atol=ATOL)
+    # REARM with ALL_ATOMIC falls back to clearing everything
+    host4, devb4 = hyb_device_buckets(c, 4, [1, 2, 4, 8, 16], cuda_device)
+    y = torch.zeros(c.m * 128, device=cuda_device)
+    for _ in range(2):
+        ops.hyb_spmm(*ops.hyb_args(xd, y, devb4, 128, L.HYB_REARM | L.HYB_ALL_ATOMIC))
+    close(y, oracle_hyb(host4, x, c.m))
+
+
+def test_hyb_spmm_no_buckets_and_empty_buckets(cuda_device):
+    x = torch.ones(4 * 8, device=cuda_device)
+    y = torch.zeros(4 * 8, device=cuda_device)
+    ops.hyb_spmm(x, y, 8)
+    e_f = torch.zeros(0, device=cuda_device)
+    e_i = torch.zeros(0, dtype=torch.int32, device=cuda_device)
+    ops.hyb_spmm(x, y, e_f, e_i, e_i, 8)
+    torch.cuda.synchronize()
+    assert torch.all(y == 0)
+
+
+def test_hyb_spmm_raw_entry_matches_packed(cuda_device):
+    import ctypes
+    c = dg.csr_powerlaw(n=2000, max_deg=900, seed=25)
+    x = dg.dense_operand(26, c.n, 64)
+    host, devb = hyb_device_buckets(c, 1, [1, 2, 4, 8], cuda_device)
+    xd = dev(x, cuda_device)
+    y1 = torch.zeros(c.m * 64, device=cuda_device)
+    ops.hyb_spmm(*ops.hyb_args(xd, y1, devb, 64))
+    arr = (L.EllBucket * len(devb))()
+    for k, (w, r, cc) in enumerate(devb):
+        arr[k] = L.EllBucket(w.data_ptr(), r.data_ptr(), cc.data_ptr(), r.numel(),
+                             cc.numel() // max(1, r.numel()))
+    y2 = torch.zeros(c.m * 64, device=cuda_device)
+    rc = L.load().sparsetir_hyb_spmm_raw(xd.data_ptr(), y2.data_ptr(), arr, len(devb), c.m, c.n, 64, 0,
+                                         0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, L.last_error()
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2)
+
+
+# ------------------------------------------------------------------------------ sddmm
+def run_sddmm(c: dg.CSR, a, b, device, scale=None, scalars=False):
+    out = torch.full((c.nnz,), -7.0, device=device)
+    args = [dev(a.reshape(-1), device), dev(b.reshape(-1), device), out, dev(c.indptr, device),
+            dev(c.indices, device)]
+    if scalars:
+        args += [c.m, c.n, a.shape[1], c.nnz]
+    if scale is not None:
+        args.append(dev(scale, device))
+    ops.sddmm(*args)
+    torch.cuda.synchronize()
+    return out
+
+
+@pytest.mark.parametrize("feat", [1, 4, 8, 20, 32, 64, 128, 200, 256, 512, 516, 1024])
+def test_sddmm_matches_oracle(cuda_device, feat):
+    c = dg.csr_lognormal(n=900, mu=3.0, sigma=1.0, max_deg=500, seed=feat)
+    a = dg.dense_operand(1, c.m, feat)
+    b = dg.dense_operand(2, c.n, feat)
+    want = orc.sddmm(a, b, c.indptr, c.indices, c.m, c.n, feat)
+    # dot products of up to 1024 terms in [-1,1]: absolute error grows with sqrt(feat)
+    close(run_sddmm(c, a, b, cuda_device, scalars=feat % 8 == 0), want, atol=ATOL * max(1, feat // 32))
+
+
+def test_sddmm_scale_and_golden(cuda_device):
+    g = np.load(os.path.join(GOLD, "sddmm.npz"))
+    c = dg.CSR(g["a"].shape[0], g["b"].shape[0], g["indptr"], g["indices"], g["scale"])
+    close(run_sddmm(c, g["a"], g["b"], cuda_device), g["out"].astype(np.float32))
+    close(run_sddmm(c, g["a"], g["b"], cuda_device, scale=g["scale"]), g["out_scaled"].astype(np.float32))
+    close(run_sddmm(c, g["a"], g["b"], cuda_device, scale=g["scale"], scalars=True),
+          orc.sddmm(g["a"], g["b"], c.indptr, c.indices, c.m, c.n, 32, scale=g["scale"]))
+
+
+def test_sddmm_empty_rows_and_tails(cuda_device):
+    # long runs of empty rows (walk falls back to the search), chunk and batch tails
+    deg = np.zeros(3000, np.int64)
+    deg[[0, 5, 6, 700, 2999]] = [3, 1, 290, 37, 2]
+    rng = np.random.default_rng(1)
+    ip = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+    ix = dg.sorted_distinct_columns(rng, deg, 400)
+    c = dg.CSR(3000, 400, ip, ix, np.ones(len(ix), np.float32))
+    for feat in (32, 64, 128):
+        a = dg.dense_operand(3, c.m, feat)
+        b = dg.dense_operand(4, c.n, feat)
+        close(run_sddmm(c, a, b, cuda_device), orc.sddmm(a, b, c.indptr, c.indices, c.m, c.n, feat))
+
+
+def test_edge_to_row_bit_exact(cuda_device):
+    g = np.load(os.path.join(GOLD, "edge_to_row.npz"))
+    c = dg.csr_lognormal(n=5000, mu=2.0, sigma=1.5, max_deg=3000, seed=7)
+    for ip in (g["indptr"], c.indptr):
+        nnz = int(ip[-1])
+        mid = torch.full((nnz,), -1, dtype=torch.int32, device=cuda_device)
+        ops.sddmm_edge_to_row(dev(ip, cuda_device), mid)
+        torch.cuda.synchronize()
+        assert np.array_equal(mid.cpu().numpy(), orc.edge_to_row(ip, nnz))
+
+
+# ------------------------------------------------------------------------------ bsrmm
+def run_bsrmm(bs: dg.BSR, b: np.ndarray, device):
+    feat = b.shape[1]
+    c = torch.full((bs.mb * bs.blk * feat,), 3.0, device=device)
+    ops.bsrmm(dev(bs.data.reshape(-1), device), dev(b.reshape(-1), device), c, dev(bs.indptr, device),
+              dev(bs.indices, device), bs.mb, bs.nb, bs.nnzb, bs.blk, feat)
+    torch.cuda.synchronize()
+    return c
+
+
+@pytest.mark.parametrize("size,blk,feat", [(512, 32, 128), (512, 32, 512), (256, 16, 64), (384, 32, 96),
+                                           (96, 8, 40), (1024, 64, 256), (4096, 32, 512)])
+def test_bsrmm_matches_oracle(cuda_device, size, blk, feat):
+    bs = dg.bsr_mask(size=size, blk=blk, density=0.1, seed=size + feat)
+    b = dg.dense_operand_normal(1, size, feat)
+    want = orc.bsrmm_f16(bs.data, b, bs.indptr, bs.indices, bs.mb, bs.nb, blk, feat, omp=True)
+    # fp16 inputs, fp32 accumulation: rtol 1e-2; sums of ~blk*deg products of N(0,1) values
+    close(run_bsrmm(bs, b, cuda_device), want, rtol=1e-2, atol=1e-2)
+
+
+def test_bsrmm_golden_and_empty_block_rows(cuda_device):
+    g = np.load(os.path.join(GOLD, "bsrmm.npz"))
+    bs = dg.BSR(len(g["indptr"]) - 1, g["b"].shape[0] // 32, 32, g["indptr"], g["indices"], g["data"])
+    close(run_bsrmm(bs, g["b"], cuda_device), g["c"].astype(np.float32), rtol=1e-2, atol=1e-2)
+    # block-rows 0 and 2 empty -> zeros
+    ip = np.array([0, 0, 2, 2], np.int32)
+    ix = np.array([0, 2], np.int32)
+    rng = np.random.default_rng(0)
+    data = rng.standard_normal((2, 32, 32)).astype(np.float16)
+    bs = dg.BSR(3, 3, 32, ip, ix, data)
+    b = dg.dense_operand_normal(2, 96, 64)
+    got = run_bsrmm(bs, b, cuda_device)
+    close(got, orc.bsrmm_f16(data, b, ip, ix, 3, 3, 32, 64), rtol=1e-2, atol=1e-2)
+    assert torch.all(got.reshape(3, 32, 64)[[0, 2]] == 0)
+
+
+# ------------------------------------------------------------------------------ rgms
+def run_rgms(cf: dg.CSF, x, w, device, scalars=False):
+    feat = x.shape[1]
+    y = torch.zeros(cf.m * feat, device=device)
+    args = [dev(cf.data, device), dev(w.reshape(-1), device), dev(x.reshape(-1), device), y,
+            dev(cf.indptr_i, device), dev(cf.indices_i, device), dev(cf.indptr_j, device),
+            dev(cf.indices_j, device)]
+    if scalars:
+        args += [cf.m, cf.n, cf.num_rels, feat, cf.nnz_i, cf.nnz_j]
+    ops.rgms(*args)
+    torch.cuda.synchronize()
+    return y
+
+
+def oracle_rgms(cf: dg.CSF, x, w):
+    y = np.zeros((cf.m, x.shape[1]), np.float32)
+    return orc.rgms(cf.data, w, x, y, cf.indptr_i, cf.indices_i, cf.indptr_j, cf.indices_j, cf.m,
+                    cf.n, cf.num_rels, x.shape[1], omp=True)
+
+
+@pytest.mark.parametrize("feat", [8, 32, 64, 128, 48])
+def test_rgms_matches_oracle(cuda_device, feat):
+    cf = dg.csf_relational(n=3000, num_rels=11, num_edges=40000, seed=feat)
+    x = dg.dense_operand(1, cf.n, feat)
+    w = dg.relation_weights(2, cf.num_rels, feat)
+    close(run_rgms(cf, x, w, cuda_device, scalars=feat == 64), oracle_rgms(cf, x, w))
+
+
+def test_rgms_golden_many_relations_and_empty(cuda_device):
+    g = np.load(os.path.join(GOLD, "rgms.npz"))
+    cf = dg.CSF(g["y"].shape[0], g["x"].shape[0], len(g["indptr_i"]) - 1, g["indptr_i"], g["indices_i"],
+                g["indptr_j"], g["indices_j"], g["data"])
+    close(run_rgms(cf, g["x"], g["w"], cuda_device), g["y"].astype(np.float32))
+    # more relations than threads in a block, most of them tiny or empty
+    cf = dg.csf_relational(n=500, num_rels=300, num_edges=3000, zipf_a=2.5, seed=3)
+    ip = cf.indptr_i.copy()
+    x = dg.dense_operand(4, cf.n, 64)
+    w = dg.relation_weights(5, cf.num_rels, 64)
+    close(run_rgms(cf, x, w, cuda_device), oracle_rgms(cf, x, w))
+    assert np.any(np.diff(ip) <= 1)
+
+
+def test_rgms_accumulates_into_y(cuda_device):
+    cf = dg.csf_relational(n=400, num_rels=4, num_edges=3000, seed=6)
+    x = dg.dense_operand(7, cf.n, 64)
+    w = dg.relation_weights(8, cf.num_rels, 64)
+    want = oracle_rgms(cf, x, w)
+    y = torch.ones(cf.m * 64, device=cuda_device)
+    ops.rgms(dev(cf.data, cuda_device), dev(w.reshape(-1), cuda_device), dev(x.reshape(-1), cuda_device), y,
+             dev(cf.indptr_i, cuda_device), dev(cf.indices_i, cuda_device), dev(cf.indptr_j, cuda_device),
+             dev(cf.indices_j, cuda_device))
+    close(y, want + 1.0)
+
+
+# ------------------------------------------------------------------------------ streams
+def test_calls_run_on_the_current_torch_stream(cuda_device):
+    c = dg.csr_poisson(m=2000, n=2000, mean_deg=10, seed=30)
+    x = dg.dense_operand(31, c.n, 64)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        got = run_csrmm(c, x, cuda_device)
+        assert L.load().sparsetir_get_stream(0) == s.cuda_stream
+    close(got, oracle_csrmm(c, x))

@@ -1,0 +1,174 @@
+"""Pins the CPU oracle: against the committed golden fixtures (produced by independent scipy /
+numpy derivations, see tests/golden/make_golden.py) and against hand-computed known answers."""
+import os
+
+import numpy as np
+import pytest
+
+import refimpl
+from oracle import oracle as orc
+from sparsetir_b200 import datagen as dg
+
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+# fp32 results against fp64 expectations: the bar BASELINE states for fp32 operators
+RTOL, ATOL = 1e-4, 1e-5
+
+
+def gold(name):
+    return np.load(os.path.join(GOLD, name))
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_hyb_matches_reference_test_derivation(tag):
+    # tests/python/sparsetir/test_format_conversion_routine.py:104-127 compares row_indices and
+    # col_indices of ColumnPartHyb with the scipy derivation; same comparison here.
+    g = gold(f"hyb_{tag}.npz")
+    parts, buckets = int(g["parts"]), [int(b) for b in g["buckets"]]
+    rows, cols, mask = orc.column_part_hyb(1000, 1000, g["indptr"], g["indices"], parts, buckets)
+    for p in range(parts):
+        for b in range(len(buckets)):
+            k = p * len(buckets) + b
+            assert np.array_equal(rows[p][b], g[f"rows_{k}"])
+            assert np.array_equal(cols[p][b], g[f"cols_{k}"])
+    assert sum(int(m.sum()) for mp in mask for m in mp) == len(g["indices"])
+
+
+def test_hyb_known_answer():
+    # 3 x 4 matrix, 2 partitions of 2 columns, buckets [1, 2]:
+    # row0: cols 0,1,3   row1: (empty)   row2: cols 1,2,3
+    indptr = np.array([0, 3, 3, 6], np.int32)
+    indices = np.array([0, 1, 3, 1, 2, 3], np.int32)
+    rows, cols, mask, pos = orc.column_part_hyb(3, 4, indptr, indices, 2, [1, 2], with_pos=True)
+    # partition 0 (cols 0-1): row0 has degree 2 -> bucket width 2; row2 degree 1 -> width 1
+    assert rows[0][0].tolist() == [2] and cols[0][0].tolist() == [[1]]
+    assert rows[0][1].tolist() == [0] and cols[0][1].tolist() == [[0, 1]]
+    # partition 1 (cols 2-3): row0 degree 1; row2 degree 2
+    assert rows[1][0].tolist() == [0] and cols[1][0].tolist() == [[3]]
+    assert rows[1][1].tolist() == [2] and cols[1][1].tolist() == [[2, 3]]
+    assert pos[1][1].tolist() == [[4, 5]] and mask[1][1].tolist() == [[1, 1]]
+
+
+def test_hyb_split_and_padding_known_answer():
+    # one partition, buckets [2]: a row of 5 entries is cut into 3 ELL rows, the last one padded
+    indptr = np.array([0, 5, 6], np.int32)
+    indices = np.array([0, 1, 2, 3, 4, 2], np.int32)
+    rows, cols, mask = orc.column_part_hyb(2, 5, indptr, indices, 1, [2])
+    assert rows[0][0].tolist() == [0, 0, 0, 1]
+    assert cols[0][0].tolist() == [[0, 1], [2, 3], [4, 0], [2, 0]]
+    assert mask[0][0].tolist() == [[1, 1], [1, 1], [1, 0], [1, 0]]
+
+
+def test_condense_matches_reference_test_derivation():
+    # tests/python/sparsetir/test_format_conversion_routine.py:146-165 (g = 1)
+    g = gold("condense.npz")
+    gi, ti, mk = orc.condense(g["indptr"], g["indices"], int(g["t"]), 1)
+    assert np.array_equal(gi, g["out_indptr"])
+    assert np.array_equal(ti.reshape(-1), g["out_indices"])
+    assert int(mk.sum()) == len(g["indices"])
+
+
+def test_condense_grouping_known_answer():
+    # rows 0,1 form one tile (t=2); distinct columns 1,4,7 -> groups of g=2: [1,4], [7,0]
+    indptr = np.array([0, 2, 4], np.int32)
+    indices = np.array([1, 7, 4, 7], np.int32)
+    gi, ti, mk = orc.condense(indptr, indices, 2, 2)
+    assert gi.tolist() == [0, 2]
+    assert ti.tolist() == [[1, 4], [7, 0]]
+    assert mk.tolist() == [[[1, 0], [0, 1]], [[1, 0], [1, 0]]]
+
+
+def test_edge_to_row_golden_and_searchsorted():
+    g = gold("edge_to_row.npz")
+    assert np.array_equal(orc.edge_to_row(g["indptr"], len(g["mid"])), g["mid"])
+    c = dg.csr_poisson(m=500, n=100, mean_deg=0.7, seed=11)  # many empty rows... deg>=1 by design
+    ip = c.indptr.copy()
+    ip[200:] = ip[200]  # empty tail
+    nnz = int(ip[-1])
+    assert np.array_equal(orc.edge_to_row(ip, nnz), refimpl.edge_to_row(ip, nnz))
+
+
+def test_csf_to_ell3d_known_answer():
+    # 2 relations; relation 0: rows 5 (cols 1,2,3) and 6 (col 0); relation 1: row 5 (cols 4,5)
+    ip0 = np.array([0, 2, 3], np.int32)
+    ix0 = np.array([5, 6, 5], np.int32)
+    ip1 = np.array([0, 3, 4, 6], np.int32)
+    ix1 = np.array([1, 2, 3, 0, 4, 5], np.int32)
+    indptr, rows, cols, mask = orc.csf_to_ell3d(ip0, ix0, ip1, ix1, [2, 1], [1, 2])
+    # bucket 0: width 1, groups of 2 rows: rel0 has row 6 -> padded to [6, 6]; rel1 none
+    assert indptr[0].tolist() == [0, 1, 1]
+    assert rows[0].tolist() == [[6, 6]] and cols[0].tolist() == [[[0], [0]]]
+    assert mask[0].tolist() == [[[1], [0]]]
+    # bucket 1: width 2, groups of 1 row: rel0 row 5 split into [1,2],[3,pad]; rel1 row 5 [4,5]
+    assert indptr[1].tolist() == [0, 2, 3]
+    assert rows[1].tolist() == [[5], [5], [5]]
+    assert cols[1].tolist() == [[[1, 2]], [[3, 0]], [[4, 5]]]
+    assert mask[1].tolist() == [[[1, 1]], [[1, 0]], [[1, 1]]]
+
+
+def test_csrmm_golden_and_empty_rows_untouched():
+    g = gold("csrmm.npz")
+    m, n, feat = g["y"].shape[0], g["x"].shape[0], g["x"].shape[1]
+    c = np.zeros((m, feat), np.float32)
+    orc.csrmm(g["data"], g["x"], c, g["indptr"], g["indices"], m, n, feat)
+    np.testing.assert_allclose(c, g["y"], rtol=RTOL, atol=ATOL)
+    # the CPU lowering initialises an element at its first reduction step, so rows without
+    # entries keep what the caller put there (src/tir/transforms/lower_init_block.cc:47-50)
+    c2 = np.full((2, 3), 7.0, np.float32)
+    orc.csrmm(np.array([2.0], np.float32), np.ones((2, 3), np.float32), c2,
+              np.array([0, 0, 1], np.int32), np.array([1], np.int32), 2, 2, 3)
+    assert c2.tolist() == [[7.0, 7.0, 7.0], [2.0, 2.0, 2.0]]
+    c3 = np.zeros((m, feat), np.float32)
+    orc.csrmm(g["data"], g["x"], c3, g["indptr"], g["indices"], m, n, feat, omp=True)
+    assert np.array_equal(c, c3)
+
+
+def test_sddmm_golden():
+    g = gold("sddmm.npz")
+    m, feat = g["a"].shape
+    out = orc.sddmm(g["a"], g["b"], g["indptr"], g["indices"], m, g["b"].shape[0], feat)
+    np.testing.assert_allclose(out, g["out"], rtol=RTOL, atol=ATOL)
+    out = orc.sddmm(g["a"], g["b"], g["indptr"], g["indices"], m, g["b"].shape[0], feat,
+                    scale=g["scale"], omp=True)
+    np.testing.assert_allclose(out, g["out_scaled"], rtol=RTOL, atol=ATOL)
+
+
+def test_bsrmm_golden():
+    g = gold("bsrmm.npz")
+    blk = g["data"].shape[1]
+    nb = len(g["indptr"]) - 1
+    feat = g["b"].shape[1]
+    out = orc.bsrmm_f16(g["data"], g["b"], g["indptr"], g["indices"], nb, g["b"].shape[0] // blk,
+                        blk, feat)
+    # fp16 inputs, fp32 accumulation: BASELINE's bar for this operator is rtol 1e-2
+    np.testing.assert_allclose(out.reshape(-1, feat), g["c"], rtol=1e-2, atol=1e-3)
+    out2 = orc.bsrmm_f16(g["data"], g["b"], g["indptr"], g["indices"], nb, g["b"].shape[0] // blk,
+                         blk, feat, omp=True)
+    assert np.array_equal(out, out2)
+
+
+def test_rgms_golden():
+    g = gold("rgms.npz")
+    m, feat = g["y"].shape
+    y = np.zeros((m, feat), np.float32)
+    orc.rgms(g["data"], g["w"], g["x"], y, g["indptr_i"], g["indices_i"], g["indptr_j"],
+             g["indices_j"], m, g["x"].shape[0], len(g["indptr_i"]) - 1, feat)
+    np.testing.assert_allclose(y, g["y"], rtol=RTOL, atol=ATOL)
+    y2 = np.zeros((m, feat), np.float32)
+    orc.rgms(g["data"], g["w"], g["x"], y2, g["indptr_i"], g["indices_i"], g["indptr_j"],
+             g["indices_j"], m, g["x"].shape[0], len(g["indptr_i"]) - 1, feat, omp=True)
+    assert np.array_equal(y, y2)
+
+
+def test_ell_spmm_sums_to_csrmm():
+    c = dg.csr_powerlaw(n=400, max_deg=300, seed=4)
+    x = dg.dense_operand(5, c.n, 16)
+    rows, cols, mask, pos = orc.column_part_hyb(c.m, c.n, c.indptr, c.indices, 2, [1, 2, 4, 8],
+                                                with_pos=True)
+    y = np.zeros((c.m, 16), np.float32)
+    for p in range(2):
+        for b in range(4):
+            w = np.where(pos[p][b] >= 0, c.data[np.maximum(pos[p][b], 0)], 0).astype(np.float32)
+            orc.ell_spmm(w, rows[p][b], cols[p][b], x, y, 16)
+    np.testing.assert_allclose(y, refimpl.spmm_f64(c.indptr, c.indices, c.data, x, c.m, c.n),
+                               rtol=RTOL, atol=ATOL)

@@ -1,0 +1,399 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-operator hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--no-ops]
+
+Workload (``config.workload``): hybrid-format SpMM Y = A X on the synthetic power-law graph
+(169,343 nodes, row degrees Zipf(2.1) clipped to [1, 13000], preferential-attachment columns,
+values 1/deg), decomposed into ELL buckets of width 1..512.  One step is one pass over the five
+feature sizes F = 32, 64, 128, 256, 512: five calls of ``sparsetir_hyb_spmm``, each on its own
+X / Y buffers (1.3 GB touched per step, ten times the L2, so no call finds its operands cached).
+
+``value`` is GFLOP/s (2 * nnz * F summed over the five F, divided by the step time) with every
+operand resident in HBM.  ``e2e`` is the same work with X in pinned host memory copied in and Y
+copied back to pinned host memory inside the timed region.  With N > 1 the rows are cut into
+nnz-balanced contiguous shards, one per rank (strong scaling on the same graph); ``value`` times
+the shard kernels (max over ranks), ``e2e`` additionally broadcasts X from rank 0 and all-gathers
+the output rows over NCCL.
+
+``--impl reference`` times the CPU restatement of the reference's lowered loop nest (the
+oracle's OpenMP csrmm — what the reference's ``llvm`` target would run, parallel over rows)
+on the same graph and feature sizes, on the host cores of rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FEATS = (32, 64, 128, 256, 512)
+BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256, 512)
+WORKLOAD = "hyb_spmm_powerlaw_169343_F32-512"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def log(*a):
+    print(*a, file=sys.stderr, flush=True)
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        d["source"] = "measured"
+        return d
+    d = dict(FALLBACK_PEAKS)
+    d["source"] = "fallback"
+    return d
+
+
+def spmm_bytes(n_rows, n_cols, nnz, feat):
+    """Compulsory traffic of one SpMM: indptr + (index, value) per entry + X once + Y once."""
+    return 4 * (n_rows + 1) + 8 * nnz + 4 * n_cols * feat + 4 * n_rows * feat
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------------------------
+def reference_arm(args, rank, world):
+    """CPU implementation of the path on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    from oracle import oracle as orc
+    from sparsetir_b200 import datagen as dg
+
+    g = dg.csr_powerlaw(seed=0)
+    xs = {f: dg.dense_operand(100 + f, g.n, f) for f in FEATS}
+    ys = {f: np.zeros((g.m, f), np.float32) for f in FEATS}
+    cores = orc.num_threads()
+    flops = sum(2.0 * g.nnz * f for f in FEATS)
+
+    def step():
+        for f in FEATS:
+            orc.csrmm(g.data, xs[f], ys[f], g.indptr, g.indices, g.m, g.n, f, omp=True)
+
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    val = flops / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "hyb_spmm_gflops", "value": val, "unit": "GFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "nnz": g.nnz, "feats": list(FEATS),
+                   "note": "CPU restatement of the reference's lowered csrmm loop nest, OpenMP over rows"},
+        "cpu_baseline": {"value": val, "unit": "GFLOP/s", "cores": cores, "kind": "port",
+                         "sample": "whole workload: all five feature sizes on the full graph"},
+        "e2e": {"value": val, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------------
+def ours_arm(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+
+    from sparsetir_b200 import _lib as L
+    from sparsetir_b200 import datagen as dg
+    from sparsetir_b200 import format as fmt
+    from sparsetir_b200 import ops
+
+    L.load()  # fails loudly if the CUDA library is missing
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    peaks = load_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def dev(a):
+        return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+    # ---- workload: same seeded graph on every rank, row shard per rank
+    g = dg.csr_powerlaw(seed=0)
+    cuts = fmt.row_partition(g.indptr, world)
+    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
+    ip = (g.indptr[r0:r1 + 1] - g.indptr[r0]).astype(np.int32)
+    ix = g.indices[g.indptr[r0]:g.indptr[r1]]
+    vals_csr = g.data[g.indptr[r0]:g.indptr[r1]]
+    m_loc, nnz_loc = r1 - r0, len(ix)
+    parts = args.parts
+    t0 = time.perf_counter()
+    rows, cols, mask, vals, _ = fmt.column_part_hyb(m_loc, g.n, ip, ix, parts, BUCKETS, data=vals_csr)
+    decompose_ms = (time.perf_counter() - t0) * 1e3
+    flags = L.HYB_REARM | (L.HYB_ALL_ATOMIC if parts > 1 else 0)
+    devb = [(dev(vals[p][b]), dev(rows[p][b]), dev(cols[p][b]))
+            for p in range(parts) for b in range(len(BUCKETS))]
+    slots = sum(int(c[2].numel()) for c in devb)
+
+    x_host = {f: torch.from_numpy(dg.dense_operand(100 + f, g.n, f)).pin_memory() for f in FEATS}
+    x_dev = {f: x_host[f].to(device) for f in FEATS}
+    y_dev = {f: torch.zeros(m_loc * f, device=device) for f in FEATS}
+    call_args = {f: ops.hyb_args(x_dev[f], y_dev[f], devb, f, flags) for f in FEATS}
+    launches_per_call = 2 if parts == 1 else 2  # re-arm (kernel or memset) + the bucket kernel
+
+    def step(events=None):
+        for f in FEATS:
+            if events is not None:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            ops.hyb_spmm(*call_args[f])
+            if events is not None:
+                e1.record()
+                events[f].append((e0, e1))
+
+    # ---- device-resident timing
+    for _ in range(max(3, args.warmup)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    events = {f: [] for f in FEATS}
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    start.record()
+    for _ in range(args.steps):
+        step(events)
+    stop.record()
+    barrier()
+    ms_total = start.elapsed_time(stop)
+    # keep the GPU busy a little longer so the clock sampler sees the loaded state
+    t_end = time.perf_counter() + (1.0 if rank == 0 else 0.0)
+    extra = 0
+    while time.perf_counter() < t_end:
+        step()
+        extra += 1
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    per_f_ms = {f: statistics.mean(a.elapsed_time(b) for a, b in events[f]) for f in FEATS}
+    ms_step = ms_total / args.steps
+    if world > 1:
+        t = torch.tensor([ms_step], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item())
+        tf = torch.tensor([per_f_ms[f] for f in FEATS], device=device)
+        dist.all_reduce(tf, op=dist.ReduceOp.MAX)
+        per_f_ms = {f: float(v) for f, v in zip(FEATS, tf.tolist())}
+    total_flops = sum(2.0 * g.nnz * f for f in FEATS)
+    value = total_flops / (ms_step * 1e-3) / 1e9
+
+    # ---- end to end: X from pinned host memory, Y back to pinned host memory
+    y_host = {f: torch.empty(g.m * f, dtype=torch.float32).pin_memory() for f in FEATS} if rank == 0 else None
+    y_full = {f: torch.empty(g.m * f, device=device) for f in FEATS} if world > 1 else None
+    shard_rows = [int(cuts[k + 1] - cuts[k]) for k in range(world)]
+
+    def e2e_step():
+        for f in FEATS:
+            if rank == 0:
+                x_dev[f].copy_(x_host[f], non_blocking=True)
+            if world > 1:
+                dist.broadcast(x_dev[f], src=0)
+            ops.hyb_spmm(*call_args[f])
+            if world > 1:
+                outs = list(torch.split(y_full[f], [r * f for r in shard_rows]))
+                dist.all_gather(outs, y_dev[f])
+                if rank == 0:
+                    y_host[f].copy_(y_full[f], non_blocking=True)
+            elif rank == 0:
+                y_host[f].copy_(y_dev[f], non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e_start, e_stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e_steps = max(3, min(args.steps, 10))
+    e_start.record()
+    for _ in range(e_steps):
+        e2e_step()
+    e_stop.record()
+    barrier()
+    e2e_ms = e_start.elapsed_time(e_stop) / e_steps
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    h2d = sum(4 * g.n * f for f in FEATS)
+    d2h = sum(4 * g.m * f for f in FEATS)
+
+    if rank != 0:
+        return
+
+    # ---- sanity: the timed result is the right one (device result vs CPU oracle, one F)
+    from oracle import oracle as orc
+    f_chk = 64
+    want = np.zeros((g.m, f_chk), np.float32)
+    orc.csrmm(g.data, x_host[f_chk].numpy(), want, g.indptr, g.indices, g.m, g.n, f_chk, omp=True)
+    got = y_host[f_chk].numpy().reshape(g.m, f_chk)
+    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5)
+
+    # ---- roofline of the dominant launch (F = 512)
+    f_dom = FEATS[-1]
+    alg_bytes = spmm_bytes(m_loc, g.n, nnz_loc, f_dom)
+    achieved = alg_bytes / (per_f_ms[f_dom] * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "kernel": "hyb_spmm_kernel<32,4,4> F=512",
+                "algorithmic_bytes": alg_bytes, "launch_ms": per_f_ms[f_dom]}
+    per_f = {}
+    for f in FEATS:
+        byts = spmm_bytes(m_loc, g.n, nnz_loc, f)
+        per_f[str(f)] = {"ms": per_f_ms[f], "gflops": 2.0 * g.nnz * f / (per_f_ms[f] * 1e-3) / 1e9,
+                         "alg_gbs": byts / (per_f_ms[f] * 1e-3) / 1e9,
+                         "hbm_frac": byts / (per_f_ms[f] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+
+    # ---- CPU baseline on the host cores (bounded sample)
+    cpu = None
+    if world == 1 or True:
+        cores = orc.num_threads()
+        ys = {f: np.zeros((g.m, f), np.float32) for f in FEATS}
+        xs = {f: x_host[f].numpy() for f in FEATS}
+
+        def cpu_step():
+            for f in FEATS:
+                orc.csrmm(g.data, xs[f], ys[f], g.indptr, g.indices, g.m, g.n, f, omp=True)
+
+        cpu_step()
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or (time.perf_counter() - t0 < 5.0 and reps < 50):
+            cpu_step()
+            reps += 1
+        cdt = (time.perf_counter() - t0) / reps
+        cpu = {"value": total_flops / cdt / 1e9, "unit": "GFLOP/s", "cores": cores, "kind": "port",
+               "sample": f"whole workload ({reps} passes over all five feature sizes, OpenMP csrmm)"}
+
+    line = {
+        "metric": "hyb_spmm_gflops", "value": value, "unit": "GFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": max(3, args.warmup), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
+        "config": {"workload": WORKLOAD, "nodes": g.m, "nnz": g.nnz, "feats": list(FEATS),
+                   "col_parts": parts, "buckets": list(BUCKETS), "ell_slots_rank0": slots,
+                   "l2": "inputs larger than L2: each step touches 1.3 GB over five X/Y pairs",
+                   "sharding": "nnz-balanced contiguous row shards, one per GPU",
+                   "host_decompose_ms_rank0": decompose_ms},
+        "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
+                "includes": "H2D of X, kernels, D2H of Y" + (", NCCL broadcast of X and all-gather of Y" if world > 1 else "")},
+        "gpu_launches": launches_per_call * len(FEATS) * args.steps,
+        "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "per_feat": per_f,
+        "alg_gbs": sum(spmm_bytes(m_loc, g.n, nnz_loc, f) for f in FEATS) / (ms_step * 1e-3) / 1e9,
+    }
+    if args.ops and world == 1:
+        try:
+            from sparsetir_b200 import opbench
+            line["ops"] = opbench.run_all(device, peaks, log)
+        except Exception as e:  # the headline line must still be printed
+            line["ops"] = {"error": repr(e)}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--parts", type=int, default=1, help="column partitions of the hyb format")
+    ap.add_argument("--no-ops", dest="ops", action="store_false",
+                    help="skip the per-operator table (CSR SpMM, SDDMM, BSR, RGMS)")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        reference_arm(args, rank, world)
+        return
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        try:
+            ours_arm(args, rank, world, local_rank)
+        finally:
+            dist.barrier()
+            dist.destroy_process_group()
+    else:
+        if args.gpus > 1:
+            log("bench.py: --gpus > 1 needs torchrun; running on one GPU")
+        ours_arm(args, rank, 1, local_rank)
+
+
+if __name__ == "__main__":
+    main()

@@ -66,7 +66,7 @@ sddmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __
     valid[v] = off[v] < row_vecs;
   }
 
-  int warp_row = edge_row_search(indptr, 0, m, static_cast<int>(e_begin));
+  int warp_row = max(0, min(m - 1, edge_row_search(indptr, 0, m, static_cast<int>(e_begin))));
   int cur_row = -1;
   V arow[VPL];
 #pragma unroll
@@ -79,10 +79,11 @@ sddmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __
     if (live) {
       col = __ldg(indices + e);
       int steps = 0;
-      while (__ldg(indptr + row + 1) <= e) {
+      // row < m - 1 keeps every read inside indptr even if nnz disagrees with indptr[m]
+      while (row < m - 1 && __ldg(indptr + row + 1) <= e) {
         ++row;
         if (++steps == 8) {  // long run of empty rows: finish with a search
-          row = edge_row_search(indptr, row, m, e);
+          row = min(m - 1, edge_row_search(indptr, row, m, e));
           break;
         }
       }
@@ -153,9 +154,9 @@ sddmm_generic_kernel(const float* __restrict__ a, const float* __restrict__ b,
   const long long e_begin = warp * 32;
   if (e_begin >= nnz) return;
   const int e_end = static_cast<int>(min(static_cast<long long>(nnz), e_begin + 32));
-  int row = edge_row_search(indptr, 0, m, static_cast<int>(e_begin));
+  int row = max(0, min(m - 1, edge_row_search(indptr, 0, m, static_cast<int>(e_begin))));
   for (int e = static_cast<int>(e_begin); e < e_end; ++e) {
-    while (__ldg(indptr + row + 1) <= e) ++row;
+    while (row < m - 1 && __ldg(indptr + row + 1) <= e) ++row;
     const float* ar = a + static_cast<size_t>(row) * feat;
     const float* br = b + static_cast<size_t>(__ldg(indices + e)) * feat;
     float s = 0.f;
@@ -193,6 +194,7 @@ extern "C" int sparsetir_sddmm_raw(const float* a, const float* b, float* c, con
   (void)n;
   if (m < 0 || feat < 0 || nnz < 0) return fail("sparsetir_sddmm: negative size");
   if (nnz == 0) return 0;
+  if (m < 1) return fail("sparsetir_sddmm: %d stored entries but no rows", nnz);
   if (!c || !indptr || !indices || (feat > 0 && (!a || !b)))
     return fail("sparsetir_sddmm: null pointer argument");
   if (use_device(device_id) != 0) return -1;

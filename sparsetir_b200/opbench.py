@@ -1,0 +1,199 @@
+"""Per-operator measurements of the other benchmark configurations (CSR SpMM, SDDMM, BSR SpMM,
+RGMS) on one GPU, reported beside the headline hyb-SpMM line by ``bench.py``.
+
+Protocol: the reference's time_evaluator (one untimed call, ``number`` back-to-back calls between
+two device events, src/runtime/profiling.cc:742-795), preceded by extra warm-up calls; for the
+microsecond-scale operators an L2 flush (a write of a buffer larger than the L2) separates the
+repeats and both the cold and the back-to-back (warm) figures are given.
+"""
+from __future__ import annotations
+
+import math
+import statistics
+from typing import Callable, Dict
+
+import numpy as np
+import torch
+
+from . import datagen as dg
+from . import ops
+
+L2_BYTES = 126 * 1024 * 1024
+
+
+def _time(fn: Callable[[], None], number: int, repeat: int = 3, warmup: int = 3) -> float:
+    """Mean milliseconds per call over ``number`` back-to-back calls, median of ``repeat``."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(repeat):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(number):
+            fn()
+        e1.record()
+        e1.synchronize()
+        out.append(e0.elapsed_time(e1) / number)
+    return statistics.median(out)
+
+
+def _time_cold(fn: Callable[[], None], flush: torch.Tensor, repeat: int = 10) -> float:
+    """Milliseconds of single calls, each after an L2 flush; median."""
+    out = []
+    for _ in range(repeat):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        out.append(e0.elapsed_time(e1))
+    return statistics.median(out)
+
+
+def _entry(ms: float, flops: float, byts: float, peaks: dict, **extra) -> dict:
+    d = {"ms": ms, "gflops": flops / (ms * 1e-3) / 1e9, "alg_gbs": byts / (ms * 1e-3) / 1e9,
+         "hbm_frac": byts / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}
+    d.update(extra)
+    return d
+
+
+def bench_csrmm(device, peaks, flush) -> dict:
+    c = dg.csr_poisson(seed=0)
+    feat = 64
+    dv = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)  # noqa: E731
+    x = dv(dg.dense_operand(0, c.n, feat).reshape(-1))
+    y = torch.zeros(c.m * feat, device=device)
+    args = (dv(c.data), x, y, dv(c.indptr), dv(c.indices))
+    fn = lambda: ops.csrmm(*args)  # noqa: E731
+    flops = 2.0 * c.nnz * feat
+    byts = 4 * (c.m + 1) + 8 * c.nnz + 4 * c.n * feat + 4 * c.m * feat
+    warm = _time(fn, number=1000)
+    cold = _time_cold(fn, flush)
+    return {"workload": "csr_spmm_4096_poisson10_F64", "nnz": c.nnz,
+            "warm": _entry(warm, flops, byts, peaks), "cold_l2": _entry(cold, flops, byts, peaks),
+            "bound": "launch latency (ideal 0.4 us at the HBM peak)"}
+
+
+def sddmm_graph_on_device(device, n=232_965, mu=5.5, sigma=1.2, max_deg=21_000, seed=0):
+    """Config-3 graph built on the GPU: same distributions as datagen.csr_lognormal (degrees
+    from the same numpy stream; column draws from a torch generator, because 1.2e8 draws and a
+    segmented sort take a minute on the host)."""
+    rng = np.random.Generator(np.random.PCG64(seed))
+    deg_np = np.clip(np.rint(rng.lognormal(mu, sigma, size=n)), 1, min(max_deg, n)).astype(np.int64)
+    deg = torch.from_numpy(deg_np).to(device)
+    indptr = torch.zeros(n + 1, dtype=torch.int64, device=device)
+    indptr[1:] = torch.cumsum(deg, 0)
+    nnz = int(indptr[-1].item())
+    assert nnz < 2**31
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed)
+    rows = torch.repeat_interleave(torch.arange(n, device=device), deg)
+    span = (n - deg + 1)[rows]
+    draw = (torch.rand(nnz, device=device, generator=gen, dtype=torch.float64) * span).long()
+    draw = torch.minimum(draw, span - 1)
+    del span
+    key = rows * (n + 1) + draw
+    del draw
+    key, _ = torch.sort(key)
+    draw = key - rows * (n + 1)
+    del key
+    rank = torch.arange(nnz, device=device) - indptr[:-1][rows]
+    indices = (draw + rank).int()
+    del draw, rank, rows
+    scale = torch.rand(nnz, device=device, generator=gen)
+    return indptr.int(), indices, scale, nnz
+
+
+def bench_sddmm(device, peaks, feats=(32, 64, 128, 256)) -> dict:
+    n = 232_965
+    indptr, indices, scale, nnz = sddmm_graph_on_device(device)
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1)
+    out = {"workload": "sddmm_lognormal_232965", "nnz": nnz, "per_feat": {}}
+    c = torch.empty(nnz, device=device)
+    for f in feats:
+        a = torch.rand(n * f, device=device, generator=gen) * 2 - 1
+        b = torch.rand(n * f, device=device, generator=gen) * 2 - 1
+        fn = lambda: ops.sddmm(a, b, c, indptr, indices, scale)  # noqa: E731
+        ms = _time(fn, number=3, repeat=3, warmup=2)
+        flops = 2.0 * nnz * f + nnz
+        byts = 4 * (n + 1) + 12 * nnz + 8 * n * f
+        out["per_feat"][str(f)] = _entry(ms, flops, byts, peaks,
+                                         gather_gbs=(4.0 * nnz * f) / (ms * 1e-3) / 1e9)
+        del a, b
+    # spot check of the full-size result against a float64 recomputation of 4096 random edges
+    f = feats[0]
+    gen.manual_seed(1)
+    a = torch.rand(n * f, device=device, generator=gen) * 2 - 1
+    b = torch.rand(n * f, device=device, generator=gen) * 2 - 1
+    ops.sddmm(a, b, c, indptr, indices, scale)
+    e = torch.randint(0, nnz, (4096,), device=device)
+    row = torch.searchsorted(indptr.long(), e, right=True) - 1
+    want = (a.view(n, f)[row].double() * b.view(n, f)[indices[e].long()].double()).sum(1) * scale[e].double()
+    err = (c[e].double() - want).abs().max().item()
+    out["spot_check_max_abs_err"] = err
+    assert err < 1e-4, err
+    return out
+
+
+def bench_bsrmm(device, peaks, flush) -> dict:
+    bs = dg.bsr_mask(seed=0)
+    feat = 512
+    dv = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)  # noqa: E731
+    b = dv(dg.dense_operand_normal(1, bs.nb * bs.blk, feat).reshape(-1))
+    c = torch.zeros(bs.mb * bs.blk * feat, device=device)
+    args = (dv(bs.data.reshape(-1)), b, c, dv(bs.indptr), dv(bs.indices), bs.mb, bs.nb, bs.nnzb,
+            bs.blk, feat)
+    fn = lambda: ops.bsrmm(*args)  # noqa: E731
+    flops = 2.0 * bs.nnzb * bs.blk * bs.blk * feat
+    byts = (2 * bs.nnzb * bs.blk * bs.blk + 4 * bs.nnzb + 4 * (bs.mb + 1)
+            + 2 * bs.nb * bs.blk * feat + 4 * bs.mb * bs.blk * feat)
+    warm = _time(fn, number=200)
+    cold = _time_cold(fn, flush)
+    tc_peak = peaks["bf16_tflops"] * 1e3  # GFLOP/s; fp16 taken equal to bf16
+    return {"workload": "bsr_spmm_4096_blk32_10pct_F512_f16", "nnzb": bs.nnzb,
+            "warm": _entry(warm, flops, byts, peaks, tensor_frac=flops / (warm * 1e-3) / 1e9 / tc_peak),
+            "cold_l2": _entry(cold, flops, byts, peaks, tensor_frac=flops / (cold * 1e-3) / 1e9 / tc_peak),
+            "bound": "HBM / launch latency (arithmetic intensity 114 flop/B is below the ridge)"}
+
+
+def bench_rgms(device, peaks, flush) -> dict:
+    cf = dg.csf_relational(seed=0)
+    feat = 64
+    dv = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)  # noqa: E731
+    x = dv(dg.dense_operand(1, cf.n, feat).reshape(-1))
+    w = dv(dg.relation_weights(2, cf.num_rels, feat).reshape(-1))
+    y = torch.zeros(cf.m * feat, device=device)
+    args = (dv(cf.data), w, x, y, dv(cf.indptr_i), dv(cf.indices_i), dv(cf.indptr_j), dv(cf.indices_j))
+
+    def fn():
+        y.zero_()  # the operator accumulates: clearing Y is part of every call
+        ops.rgms(*args)
+
+    flops_ref = 2.0 * cf.nnz_j * feat * feat + 2.0 * cf.nnz_j * feat   # per-edge formulation
+    flops_done = 2.0 * cf.nnz_j * feat + 2.0 * cf.nnz_i * feat * feat  # aggregate, then transform
+    byts = 12 * cf.nnz_j + 4 * cf.num_rels * feat * feat + 8 * cf.n * feat
+    warm = _time(fn, number=20)
+    cold = _time_cold(fn, flush)
+    return {"workload": "rgms_100k_46rel_1.5M_F64", "nnz_i": cf.nnz_i, "nnz_j": cf.nnz_j,
+            "warm": _entry(warm, flops_ref, byts, peaks, gflops_executed=flops_done / (warm * 1e-3) / 1e9),
+            "cold_l2": _entry(cold, flops_ref, byts, peaks, gflops_executed=flops_done / (cold * 1e-3) / 1e9),
+            "note": "gflops counts the reference's per-edge formulation; the kernel aggregates first"}
+
+
+def run_all(device, peaks, log=print) -> Dict[str, dict]:
+    flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
+    out = {}
+    for name, fn in (("csrmm", lambda: bench_csrmm(device, peaks, flush)),
+                     ("bsrmm", lambda: bench_bsrmm(device, peaks, flush)),
+                     ("rgms", lambda: bench_rgms(device, peaks, flush)),
+                     ("sddmm", lambda: bench_sddmm(device, peaks))):
+        try:
+            out[name] = fn()
+        except Exception as e:  # keep the other operators' numbers
+            out[name] = {"error": repr(e)}
+        log(f"[opbench] {name}: {out[name]}")
+        torch.cuda.empty_cache()
+    return out

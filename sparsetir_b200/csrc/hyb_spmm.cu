@@ -7,16 +7,19 @@
 // passed by value in the kernel parameters — no device-side scratch, no host->device copy.
 //
 // Differences from the reference schedule, all invisible in the results:
-//  - work per sub-warp is a fixed number of slots (~kSlotsPerItem), i.e. several ELL rows of a
-//    narrow bucket or one ELL row of a wide one; wide buckets are scheduled first so the long
-//    items do not form the tail of the launch;
-//  - whether an ELL row must be accumulated atomically is decided per ELL row, from the data:
-//    a row id that equals its neighbour's id in the same array is a row that was split into
-//    several ELL rows (src/sparse/format.cc:110-116) and is reduced with one 16-byte vector
-//    atomic per lane; every other ELL row is the only writer of its output row and is stored.
-//    The reference marks whole buckets atomic instead (bench_spmm.py:170,174-177).
-//    With several column partitions the same output row appears in several arrays, which the
-//    kernel cannot see; the caller says so with SPARSETIR_HYB_ALL_ATOMIC.
+//  - a work item (one sub-warp) covers about kSlotsPerItem stored slots whatever the bucket:
+//    several ELL rows of a narrow bucket, or one kWideChunk-slot piece of an ELL row of a wide
+//    bucket.  Equal-sized items keep every SM busy until the end of the launch; the reference
+//    equalises per block instead (8 * maxBucket slots per block, bench_spmm.py:187-189).
+//    Wide buckets are scheduled first.
+//  - whether an ELL row must be accumulated atomically is decided from the data: pieces of a
+//    chunked wide ELL row, and ELL rows whose row id equals a neighbour's id in the same array
+//    (a row that the format split into several ELL rows, src/sparse/format.cc:110-116), are
+//    reduced with one 16-byte vector atomic per lane; every other ELL row is the only writer of
+//    its output row and is stored.  The reference marks whole buckets atomic
+//    (bench_spmm.py:170,174-177).  With several column partitions the same output row appears
+//    in several arrays, which the kernel cannot see; the caller says so with
+//    SPARSETIR_HYB_ALL_ATOMIC.
 #include <algorithm>
 #include <vector>
 
@@ -27,7 +30,8 @@ namespace sptir {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kSlotsPerItem = 32;
+constexpr int kSlotsPerItem = 32;  // narrow buckets: ELL rows per item = kSlotsPerItem / width
+constexpr int kWideChunk = 64;     // wide buckets: slots per piece of an ELL row
 constexpr int kMaxB = SPARSETIR_HYB_MAX_BUCKETS;
 
 struct HybTable {
@@ -36,7 +40,8 @@ struct HybTable {
   const int32_t* cols[kMaxB];
   int32_t nrows[kMaxB];
   int32_t width[kMaxB];
-  int32_t rows_per_item[kMaxB];
+  int32_t rows_per_item[kMaxB];    // >= 1; 1 for chunked buckets
+  int32_t chunks_per_row[kMaxB];   // 1 unless width > kWideChunk
   int32_t block_start[kMaxB + 1];
   int32_t nb;
 };
@@ -61,28 +66,45 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
   const int lane = threadIdx.x % LPR;
   const unsigned mask = group_mask<LPR>();
   const int q = find_bucket(tb, blockIdx.x);
-  const int width = tb.width[q], nrows = tb.nrows[q], rpi = tb.rows_per_item[q];
+  const int width = tb.width[q], nrows = tb.nrows[q];
+  const int rpi = tb.rows_per_item[q], cpr = tb.chunks_per_row[q];
   const long long item =
       static_cast<long long>(blockIdx.x - tb.block_start[q]) * SUBS + threadIdx.x / LPR;
-  const long long r0l = item * rpi;
-  if (r0l >= nrows) return;
-  const int r0 = static_cast<int>(r0l);
-  const int r1 = min(nrows, r0 + rpi);
+  // slot range [first, first + nslots) of the bucket's flat slot array; `per_row` slots
+  // complete one output contribution
+  long long r0l;
+  int nslots, per_row;
+  size_t first;
+  if (cpr == 1) {
+    r0l = item * rpi;
+    if (r0l >= nrows) return;
+    const int r1 = min(static_cast<long long>(nrows), r0l + rpi);
+    nslots = (r1 - static_cast<int>(r0l)) * width;
+    per_row = width;
+    first = static_cast<size_t>(r0l) * width;
+  } else {
+    r0l = item / cpr;
+    if (r0l >= nrows) return;
+    const int s0 = static_cast<int>(item % cpr) * kWideChunk;
+    nslots = min(kWideChunk, width - s0);
+    per_row = nslots;
+    first = static_cast<size_t>(r0l) * width + s0;
+  }
   const int32_t* __restrict__ rows = tb.rows[q];
   const FeatLane<LPR, VPL, VEC> fl(feat, blockIdx.y, lane);
   V* cv = reinterpret_cast<V*>(c);
+  const bool always_atomic = all_atomic || cpr > 1;
 
   V acc[VPL];
 #pragma unroll
   for (int v = 0; v < VPL; ++v) acc[v] = Vec<VEC>::zero();
-  int r = r0, left = width;
-  const size_t first = static_cast<size_t>(r0) * width;
+  int r = static_cast<int>(r0l), left = per_row;
   stream_slots<LPR, VPL, VEC>(
-      tb.cols[q] + first, tb.w[q] + first, (r1 - r0) * width, reinterpret_cast<const V*>(b), fl,
-      lane, mask, acc, [&](V(&)[VPL]) {
+      tb.cols[q] + first, tb.w[q] + first, nslots, reinterpret_cast<const V*>(b), fl, lane, mask,
+      acc, [&](V(&)[VPL]) {
         if (--left != 0) return;
         const int row = __ldg(rows + r);
-        const bool atomic = all_atomic || is_split_row(rows, r, nrows, row);
+        const bool atomic = always_atomic || is_split_row(rows, r, nrows, row);
         V* dst = cv + static_cast<size_t>(row) * fl.row_vecs;
 #pragma unroll
         for (int v = 0; v < VPL; ++v) {
@@ -93,12 +115,12 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
           acc[v] = Vec<VEC>::zero();
         }
         ++r;
-        left = width;
+        left = per_row;
       });
 }
 
-// Zeroes the output rows that the main kernel will accumulate into atomically (split rows),
-// so that repeated calls on the same C stay correct without a full memset.
+// Zeroes the output rows that the main kernel accumulates into atomically (chunked wide rows
+// and split rows), so that repeated calls on the same C stay correct without a full memset.
 __global__ void __launch_bounds__(kThreads)
 hyb_rearm_kernel(const __grid_constant__ HybTable tb, float* __restrict__ c, int feat) {
   const int q = find_bucket(tb, blockIdx.x);
@@ -109,9 +131,16 @@ hyb_rearm_kernel(const __grid_constant__ HybTable tb, float* __restrict__ c, int
                       threadIdx.x / 32;
   if (r >= nrows) return;
   const int row = __ldg(rows + r);
-  if (!is_split_row(rows, static_cast<int>(r), nrows, row)) return;
+  if (tb.chunks_per_row[q] == 1 && !is_split_row(rows, static_cast<int>(r), nrows, row)) return;
   float* dst = c + static_cast<size_t>(row) * feat;
   for (int f = threadIdx.x % 32; f < feat; f += 32) dst[f] = 0.f;
+}
+
+void plan_items(HybTable& tb) {
+  for (int q = 0; q < tb.nb; ++q) {
+    tb.rows_per_item[q] = std::max(1, kSlotsPerItem / tb.width[q]);
+    tb.chunks_per_row[q] = tb.width[q] > kWideChunk ? ceil_div(tb.width[q], kWideChunk) : 1;
+  }
 }
 
 template <int LPR, int VPL, int VEC>
@@ -119,12 +148,14 @@ int launch(HybTable& tb, const float* b, float* c, int feat, int all_atomic, cud
   constexpr int SUBS = kThreads / LPR;
   long long blocks = 0;
   for (int q = 0; q < tb.nb; ++q) {
-    tb.rows_per_item[q] = std::max(1, kSlotsPerItem / tb.width[q]);
     tb.block_start[q] = static_cast<int32_t>(blocks);
-    blocks += ceil_div(ceil_div(tb.nrows[q], tb.rows_per_item[q]), SUBS);
+    const long long items = tb.chunks_per_row[q] > 1
+                                ? static_cast<long long>(tb.nrows[q]) * tb.chunks_per_row[q]
+                                : ceil_div(tb.nrows[q], tb.rows_per_item[q]);
+    blocks += (items + SUBS - 1) / SUBS;
+    if (blocks > INT32_MAX) return fail("sparsetir_hyb_spmm: too many thread blocks");
   }
   tb.block_start[tb.nb] = static_cast<int32_t>(blocks);
-  if (blocks > INT32_MAX) return fail("sparsetir_hyb_spmm: too many thread blocks");
   const int tile_feat = LPR * VPL * VEC;
   dim3 grid(static_cast<unsigned>(blocks), ceil_div(feat, tile_feat));
   hyb_spmm_kernel<LPR, VPL, VEC><<<grid, kThreads, 0, stream>>>(tb, b, c, feat, all_atomic);
@@ -169,6 +200,7 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
     tb.w[k] = bk.w; tb.rows[k] = bk.rows; tb.cols[k] = bk.cols;
     tb.nrows[k] = bk.nrows; tb.width[k] = bk.width;
   }
+  plan_items(tb);
 
   if (flags & SPARSETIR_HYB_ZERO_C) {
     SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(m) * feat * sizeof(float), st));

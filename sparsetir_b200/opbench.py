@@ -38,6 +38,31 @@ def _time(fn: Callable[[], None], number: int, repeat: int = 3, warmup: int = 3)
     return statistics.median(out)
 
 
+def _time_graph(fn: Callable[[], None], number: int, repeat: int = 5) -> float:
+    """Mean milliseconds per call with ``number`` calls captured in one CUDA graph and replayed:
+    the device-side cost of back-to-back launches without per-call host work."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(number):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    out = []
+    for _ in range(repeat):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        e1.synchronize()
+        out.append(e0.elapsed_time(e1) / number)
+    return statistics.median(out)
+
+
 def _time_cold(fn: Callable[[], None], flush: torch.Tensor, repeat: int = 10) -> float:
     """Milliseconds of single calls, each after an L2 flush; median."""
     out = []
@@ -66,13 +91,15 @@ def bench_csrmm(device, peaks, flush) -> dict:
     x = dv(dg.dense_operand(0, c.n, feat).reshape(-1))
     y = torch.zeros(c.m * feat, device=device)
     args = (dv(c.data), x, y, dv(c.indptr), dv(c.indices))
-    fn = lambda: ops.csrmm(*args)  # noqa: E731
+    fn = ops.csrmm.prepare(*args)
     flops = 2.0 * c.nnz * feat
     byts = 4 * (c.m + 1) + 8 * c.nnz + 4 * c.n * feat + 4 * c.m * feat
     warm = _time(fn, number=1000)
     cold = _time_cold(fn, flush)
+    graph = _time_graph(fn, number=200)
     return {"workload": "csr_spmm_4096_poisson10_F64", "nnz": c.nnz,
             "warm": _entry(warm, flops, byts, peaks), "cold_l2": _entry(cold, flops, byts, peaks),
+            "graph_replay": _entry(graph, flops, byts, peaks),
             "bound": "launch latency (ideal 0.4 us at the HBM peak)"}
 
 
@@ -116,7 +143,7 @@ def bench_sddmm(device, peaks, feats=(32, 64, 128, 256)) -> dict:
     for f in feats:
         a = torch.rand(n * f, device=device, generator=gen) * 2 - 1
         b = torch.rand(n * f, device=device, generator=gen) * 2 - 1
-        fn = lambda: ops.sddmm(a, b, c, indptr, indices, scale)  # noqa: E731
+        fn = ops.sddmm.prepare(a, b, c, indptr, indices, scale)
         ms = _time(fn, number=3, repeat=3, warmup=2)
         flops = 2.0 * nnz * f + nnz
         byts = 4 * (n + 1) + 12 * nnz + 8 * n * f
@@ -146,14 +173,16 @@ def bench_bsrmm(device, peaks, flush) -> dict:
     c = torch.zeros(bs.mb * bs.blk * feat, device=device)
     args = (dv(bs.data.reshape(-1)), b, c, dv(bs.indptr), dv(bs.indices), bs.mb, bs.nb, bs.nnzb,
             bs.blk, feat)
-    fn = lambda: ops.bsrmm(*args)  # noqa: E731
+    fn = ops.bsrmm.prepare(*args)
     flops = 2.0 * bs.nnzb * bs.blk * bs.blk * feat
     byts = (2 * bs.nnzb * bs.blk * bs.blk + 4 * bs.nnzb + 4 * (bs.mb + 1)
             + 2 * bs.nb * bs.blk * feat + 4 * bs.mb * bs.blk * feat)
     warm = _time(fn, number=200)
     cold = _time_cold(fn, flush)
+    graph = _time_graph(fn, number=100)
     tc_peak = peaks["bf16_tflops"] * 1e3  # GFLOP/s; fp16 taken equal to bf16
     return {"workload": "bsr_spmm_4096_blk32_10pct_F512_f16", "nnzb": bs.nnzb,
+            "graph_replay": _entry(graph, flops, byts, peaks, tensor_frac=flops / (graph * 1e-3) / 1e9 / tc_peak),
             "warm": _entry(warm, flops, byts, peaks, tensor_frac=flops / (warm * 1e-3) / 1e9 / tc_peak),
             "cold_l2": _entry(cold, flops, byts, peaks, tensor_frac=flops / (cold * 1e-3) / 1e9 / tc_peak),
             "bound": "HBM / launch latency (arithmetic intensity 114 flop/B is below the ridge)"}
@@ -168,9 +197,11 @@ def bench_rgms(device, peaks, flush) -> dict:
     y = torch.zeros(cf.m * feat, device=device)
     args = (dv(cf.data), w, x, y, dv(cf.indptr_i), dv(cf.indices_i), dv(cf.indptr_j), dv(cf.indices_j))
 
+    call = ops.rgms.prepare(*args)
+
     def fn():
         y.zero_()  # the operator accumulates: clearing Y is part of every call
-        ops.rgms(*args)
+        call()
 
     flops_ref = 2.0 * cf.nnz_j * feat * feat + 2.0 * cf.nnz_j * feat   # per-edge formulation
     flops_done = 2.0 * cf.nnz_j * feat + 2.0 * cf.nnz_i * feat * feat  # aggregate, then transform

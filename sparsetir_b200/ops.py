@@ -65,6 +65,31 @@ def use_current_stream(device: Optional[torch.device] = None) -> None:
         raise SparseTIRError(L.last_error())
 
 
+class PreparedCall:
+    """One packed call with its argument arrays already built (see PackedFunc.prepare)."""
+
+    __slots__ = ("_fn", "_values", "_codes", "_n", "_keep", "_dev_index", "_ret", "_ret_code",
+                 "_set_stream")
+
+    def __init__(self, fn, values, codes, n, keep, device):
+        self._fn, self._values, self._codes, self._n, self._keep = fn, values, codes, n, keep
+        self._dev_index = None
+        if device is not None:
+            self._dev_index = device.index if device.index is not None else torch.cuda.current_device()
+        self._ret = L.TVMValue()
+        self._ret_code = ctypes.c_int(0)
+        self._set_stream = L.load().sparsetir_set_stream
+
+    def __call__(self) -> None:
+        if self._dev_index is not None:
+            self._set_stream(self._dev_index,
+                             ctypes.c_void_p(torch.cuda.current_stream(self._dev_index).cuda_stream))
+        rc = self._fn(self._values, self._codes, self._n, ctypes.byref(self._ret),
+                      ctypes.byref(self._ret_code), None)
+        if rc != 0:
+            raise SparseTIRError(L.last_error())
+
+
 class PackedFunc:
     """A TVMBackendPackedCFunc symbol of the library, callable like the reference's functions."""
 
@@ -82,6 +107,11 @@ class PackedFunc:
         return self._fn
 
     def __call__(self, *args) -> None:
+        self.prepare(*args)()
+
+    def prepare(self, *args) -> "PreparedCall":
+        """Packs the arguments once; the returned object repeats the call without rebuilding
+        the DLTensor descriptors (the tensors must stay alive and keep their storage)."""
         fn = self._resolve()
         n = len(args)
         values = (L.TVMValue * max(1, n))()
@@ -111,13 +141,7 @@ class PackedFunc:
                 codes[i] = L.kTVMNullptr
             else:
                 raise TypeError(f"argument {i}: unsupported type {type(a)}")
-        if device is not None:
-            use_current_stream(device)
-        ret = L.TVMValue()
-        ret_code = ctypes.c_int(0)
-        rc = fn(values, codes, n, ctypes.byref(ret), ctypes.byref(ret_code), None)
-        if rc != 0:
-            raise SparseTIRError(L.last_error())
+        return PreparedCall(fn, values, codes, n, keep, device)
 
     def time_evaluator(self, number: int = 10, repeat: int = 1):
         """Mirror of the reference's time_evaluator: one untimed call, then ``repeat`` measurements
@@ -125,13 +149,14 @@ class PackedFunc:
         gives the list of per-call mean seconds."""
 
         def run(*args) -> List[float]:
-            self(*args)
+            call = self.prepare(*args)
+            call()
             out = []
             for _ in range(repeat):
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 e0.record()
                 for _ in range(number):
-                    self(*args)
+                    call()
                 e1.record()
                 e1.synchronize()
                 out.append(e0.elapsed_time(e1) * 1e-3 / number)

@@ -229,7 +229,8 @@ def test_hyb_spmm_raw_entry_matches_packed(cuda_device):
                                          0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc == 0, L.last_error()
     torch.cuda.synchronize()
-    assert torch.equal(y1, y2)
+    # split rows are reduced with atomics, whose order differs between launches
+    close(y2, y1.cpu().numpy())
 
 
 # ------------------------------------------------------------------------------ sddmm

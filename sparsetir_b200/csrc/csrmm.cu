@@ -49,7 +49,7 @@ csrmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __
       V* dst = cv + static_cast<size_t>(row) * fl.row_vecs;
 #pragma unroll
       for (int v = 0; v < VPL; ++v) {
-        if (fl.valid[v]) dst[fl.off[v]] = acc[v];
+        if (fl.valid[v]) __stcs(dst + fl.off[v], acc[v]);  // written once: keep B rows in L2
         acc[v] = Vec<VEC>::zero();
       }
       ++row;
@@ -83,7 +83,6 @@ extern "C" int sparsetir_csrmm_raw(const float* a, const float* b, float* c, con
                                    const int32_t* indices, int m, int n, int feat, int nnz,
                                    int device_id, void* stream) {
   using namespace sptir;
-  (void)n;
   if (m < 0 || feat < 0 || nnz < 0) return fail("sparsetir_csrmm: negative size");
   if (m == 0 || feat == 0) return 0;
   if (!b || !c || !indptr || (nnz > 0 && (!a || !indices)))
@@ -96,8 +95,14 @@ extern "C" int sparsetir_csrmm_raw(const float* a, const float* b, float* c, con
     if (nv <= 8) return launch<8, 1, 4>(a, b, c, indptr, indices, m, feat, st);
     if (nv <= 16) return launch<16, 1, 4>(a, b, c, indptr, indices, m, feat, st);
     if (nv <= 32) return launch<32, 1, 4>(a, b, c, indptr, indices, m, feat, st);
-    if (nv <= 64) return launch<32, 2, 4>(a, b, c, indptr, indices, m, feat, st);
-    return launch<32, 4, 4>(a, b, c, indptr, indices, m, feat, st);  // tiles of 512 features
+    // Wider rows go feature tile by feature tile (blockIdx.y, the slowest grid dimension), the
+    // tile chosen so that the n x tile slice of B a pass gathers from stays resident in L2.
+    const size_t l2_budget = 96u << 20;
+    const size_t slice_128 = static_cast<size_t>(n) * 128 * sizeof(float);
+    if (nv > 64 && 4 * slice_128 <= l2_budget)
+      return launch<32, 4, 4>(a, b, c, indptr, indices, m, feat, st);
+    if (2 * slice_128 <= l2_budget) return launch<32, 2, 4>(a, b, c, indptr, indices, m, feat, st);
+    return launch<32, 1, 4>(a, b, c, indptr, indices, m, feat, st);
   }
   if (feat <= 8) return launch<8, 1, 1>(a, b, c, indptr, indices, m, feat, st);
   if (feat <= 16) return launch<16, 1, 1>(a, b, c, indptr, indices, m, feat, st);

@@ -7,8 +7,8 @@
 // passed by value in the kernel parameters — no device-side scratch, no host->device copy.
 //
 // Differences from the reference schedule, all invisible in the results:
-//  - a work item (one sub-warp) covers about kSlotsPerItem stored slots whatever the bucket:
-//    several ELL rows of a narrow bucket, or one kWideChunk-slot piece of an ELL row of a wide
+//  - a work item (one sub-warp) covers about item_slots() stored slots whatever the bucket:
+//    several ELL rows of a narrow bucket, or one item_slots()-slot piece of an ELL row of a wide
 //    bucket.  Equal-sized items keep every SM busy until the end of the launch; the reference
 //    equalises per block instead (8 * maxBucket slots per block, bench_spmm.py:187-189).
 //    Wide buckets are scheduled first.
@@ -29,10 +29,15 @@
 namespace sptir {
 namespace {
 
+#ifndef SPTIR_HYB_MIN_BLOCKS
+#define SPTIR_HYB_MIN_BLOCKS 3  // resident blocks per SM the register budget is sized for
+#endif
 constexpr int kThreads = 256;
-constexpr int kSlotsPerItem = 32;  // narrow buckets: ELL rows per item = kSlotsPerItem / width
-constexpr int kWideChunk = 64;     // wide buckets: slots per piece of an ELL row
 constexpr int kMaxB = SPARSETIR_HYB_MAX_BUCKETS;
+
+// Stored slots covered by one work item (one sub-warp of `lpr` lanes): four id batches, so that
+// the per-item set-up is amortised and the id prefetch of spmm_core.cuh has something to hide.
+constexpr int item_slots(int lpr) { return 4 * lpr; }
 
 struct HybTable {
   const float* w[kMaxB];
@@ -41,7 +46,7 @@ struct HybTable {
   int32_t nrows[kMaxB];
   int32_t width[kMaxB];
   int32_t rows_per_item[kMaxB];    // >= 1; 1 for chunked buckets
-  int32_t chunks_per_row[kMaxB];   // 1 unless width > kWideChunk
+  int32_t chunks_per_row[kMaxB];   // 1 unless width > item_slots
   int32_t block_start[kMaxB + 1];
   int32_t nb;
 };
@@ -58,39 +63,50 @@ __device__ __forceinline__ bool is_split_row(const int32_t* __restrict__ rows, i
 }
 
 template <int LPR, int VPL, int VEC>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, SPTIR_HYB_MIN_BLOCKS)
 hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b,
                 float* __restrict__ c, int feat, int all_atomic) {
   using V = typename Vec<VEC>::type;
   constexpr int SUBS = kThreads / LPR;
+  constexpr int ITEM = item_slots(LPR);
+  // row ids of the item's ELL rows and of the two neighbouring ELL rows (-1 outside the
+  // bucket): read at every row end, so they must not cost a trip to global memory there
+  __shared__ int32_t s_rows[SUBS][ITEM + 2];
   const int lane = threadIdx.x % LPR;
+  const int sub = threadIdx.x / LPR;
   const unsigned mask = group_mask<LPR>();
   const int q = find_bucket(tb, blockIdx.x);
   const int width = tb.width[q], nrows = tb.nrows[q];
   const int rpi = tb.rows_per_item[q], cpr = tb.chunks_per_row[q];
-  const long long item =
-      static_cast<long long>(blockIdx.x - tb.block_start[q]) * SUBS + threadIdx.x / LPR;
+  const long long item = static_cast<long long>(blockIdx.x - tb.block_start[q]) * SUBS + sub;
   // slot range [first, first + nslots) of the bucket's flat slot array; `per_row` slots
   // complete one output contribution
   long long r0l;
-  int nslots, per_row;
+  int nslots, per_row, nr;
   size_t first;
   if (cpr == 1) {
     r0l = item * rpi;
     if (r0l >= nrows) return;
-    const int r1 = min(static_cast<long long>(nrows), r0l + rpi);
-    nslots = (r1 - static_cast<int>(r0l)) * width;
+    nr = static_cast<int>(min(static_cast<long long>(nrows), r0l + rpi) - r0l);
+    nslots = nr * width;
     per_row = width;
     first = static_cast<size_t>(r0l) * width;
   } else {
     r0l = item / cpr;
     if (r0l >= nrows) return;
-    const int s0 = static_cast<int>(item % cpr) * kWideChunk;
-    nslots = min(kWideChunk, width - s0);
+    const int s0 = static_cast<int>(item % cpr) * ITEM;
+    nr = 1;
+    nslots = min(ITEM, width - s0);
     per_row = nslots;
     first = static_cast<size_t>(r0l) * width + s0;
   }
+  const int r0 = static_cast<int>(r0l);
   const int32_t* __restrict__ rows = tb.rows[q];
+  for (int j = lane; j < nr + 2; j += LPR) {
+    const int idx = r0 - 1 + j;
+    s_rows[sub][j] = (idx >= 0 && idx < nrows) ? __ldg(rows + idx) : -1;
+  }
+  __syncwarp(mask);
   const FeatLane<LPR, VPL, VEC> fl(feat, blockIdx.y, lane);
   V* cv = reinterpret_cast<V*>(c);
   const bool always_atomic = all_atomic || cpr > 1;
@@ -98,49 +114,68 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
   V acc[VPL];
 #pragma unroll
   for (int v = 0; v < VPL; ++v) acc[v] = Vec<VEC>::zero();
-  int r = static_cast<int>(r0l), left = per_row;
+  int j = 1, left = per_row;  // s_rows[sub][j] is the id of the ELL row being accumulated
   stream_slots<LPR, VPL, VEC>(
       tb.cols[q] + first, tb.w[q] + first, nslots, reinterpret_cast<const V*>(b), fl, lane, mask,
       acc, [&](V(&)[VPL]) {
         if (--left != 0) return;
-        const int row = __ldg(rows + r);
-        const bool atomic = always_atomic || is_split_row(rows, r, nrows, row);
+        const int row = s_rows[sub][j];
+        const bool atomic =
+            always_atomic || s_rows[sub][j - 1] == row || s_rows[sub][j + 1] == row;
         V* dst = cv + static_cast<size_t>(row) * fl.row_vecs;
 #pragma unroll
         for (int v = 0; v < VPL; ++v) {
           if (fl.valid[v]) {
             if (atomic) Vec<VEC>::atomic_add(dst + fl.off[v], acc[v]);
-            else dst[fl.off[v]] = acc[v];
+            else __stcs(dst + fl.off[v], acc[v]);  // written once: do not displace B rows in L2
           }
           acc[v] = Vec<VEC>::zero();
         }
-        ++r;
+        ++j;
         left = per_row;
       });
 }
 
 // Zeroes the output rows that the main kernel accumulates into atomically (chunked wide rows
 // and split rows), so that repeated calls on the same C stay correct without a full memset.
+// One thread inspects one ELL row (coalesced reads of the row ids); the rows that need clearing
+// are rare, and each is then cleared by the whole warp.
 __global__ void __launch_bounds__(kThreads)
 hyb_rearm_kernel(const __grid_constant__ HybTable tb, float* __restrict__ c, int feat) {
   const int q = find_bucket(tb, blockIdx.x);
   const int nrows = tb.nrows[q];
   const int32_t* __restrict__ rows = tb.rows[q];
-  const int warps = kThreads / 32;
-  const long long r = static_cast<long long>(blockIdx.x - tb.block_start[q]) * warps +
-                      threadIdx.x / 32;
-  if (r >= nrows) return;
-  const int row = __ldg(rows + r);
-  if (tb.chunks_per_row[q] == 1 && !is_split_row(rows, static_cast<int>(r), nrows, row)) return;
-  float* dst = c + static_cast<size_t>(row) * feat;
-  for (int f = threadIdx.x % 32; f < feat; f += 32) dst[f] = 0.f;
+  const long long r = static_cast<long long>(blockIdx.x - tb.block_start[q]) * kThreads + threadIdx.x;
+  int row = -1;
+  bool clear = false;
+  if (r < nrows) {
+    row = __ldg(rows + r);
+    clear = tb.chunks_per_row[q] > 1 || is_split_row(rows, static_cast<int>(r), nrows, row);
+    // of a run of equal ids only the first ELL row clears
+    if (clear && r > 0 && __ldg(rows + r - 1) == row) clear = false;
+  }
+  unsigned todo = __ballot_sync(0xffffffffu, clear);
+  const int lane = threadIdx.x & 31;
+  while (todo != 0) {
+    const int src = __ffs(todo) - 1;
+    todo &= todo - 1;
+    const int rr = __shfl_sync(0xffffffffu, row, src);
+    float* dst = c + static_cast<size_t>(rr) * feat;
+    for (int f = lane; f < feat; f += 32) dst[f] = 0.f;
+  }
 }
 
-void plan_items(HybTable& tb) {
+void plan_items(HybTable& tb, int item) {
   for (int q = 0; q < tb.nb; ++q) {
-    tb.rows_per_item[q] = std::max(1, kSlotsPerItem / tb.width[q]);
-    tb.chunks_per_row[q] = tb.width[q] > kWideChunk ? ceil_div(tb.width[q], kWideChunk) : 1;
+    tb.rows_per_item[q] = std::max(1, item / tb.width[q]);
+    tb.chunks_per_row[q] = tb.width[q] > item ? ceil_div(tb.width[q], item) : 1;
   }
+}
+
+// Lanes per dense row for a feature size, the first template argument of the kernel used.
+int lanes_per_row(int feat, bool vec4) {
+  const int units = vec4 ? feat / 4 : feat;
+  return units <= 8 ? 8 : (units <= 16 ? 16 : 32);
 }
 
 template <int LPR, int VPL, int VEC>
@@ -170,7 +205,6 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
                                       int num_buckets, int m, int n, int feat, int flags,
                                       int device_id, void* stream) {
   using namespace sptir;
-  (void)n;
   if (num_buckets < 0 || num_buckets > kMaxB)
     return fail("sparsetir_hyb_spmm: %d buckets exceed the maximum of %d", num_buckets, kMaxB);
   if (m < 0 || feat < 0) return fail("sparsetir_hyb_spmm: negative size");
@@ -200,7 +234,8 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
     tb.w[k] = bk.w; tb.rows[k] = bk.rows; tb.cols[k] = bk.cols;
     tb.nrows[k] = bk.nrows; tb.width[k] = bk.width;
   }
-  plan_items(tb);
+  const bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
+  plan_items(tb, item_slots(lanes_per_row(feat, vec4)));
 
   if (flags & SPARSETIR_HYB_ZERO_C) {
     SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(m) * feat * sizeof(float), st));
@@ -211,7 +246,7 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
       long long blocks = 0;
       for (int q = 0; q < tb.nb; ++q) {
         tb.block_start[q] = static_cast<int32_t>(blocks);
-        blocks += ceil_div(tb.nrows[q], kThreads / 32);
+        blocks += ceil_div(tb.nrows[q], kThreads);
       }
       tb.block_start[tb.nb] = static_cast<int32_t>(blocks);
       if (blocks > INT32_MAX) return fail("sparsetir_hyb_spmm: too many thread blocks");
@@ -221,14 +256,20 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
   }
   if (tb.nb == 0) return 0;
 
-  bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
   if (vec4) {
     const int nv = feat / 4;
     if (nv <= 8) return launch<8, 1, 4>(tb, b, c, feat, all_atomic, st);
     if (nv <= 16) return launch<16, 1, 4>(tb, b, c, feat, all_atomic, st);
     if (nv <= 32) return launch<32, 1, 4>(tb, b, c, feat, all_atomic, st);
-    if (nv <= 64) return launch<32, 2, 4>(tb, b, c, feat, all_atomic, st);
-    return launch<32, 4, 4>(tb, b, c, feat, all_atomic, st);
+    // Wider rows are covered feature tile by feature tile (blockIdx.y, the slowest grid
+    // dimension): a pass gathers from an n x tile slice of B, and the tile is chosen so that
+    // this slice stays resident in the 126 MB L2 while the pass runs.  Re-reading the index
+    // arrays once per tile costs little next to re-fetching B rows from HBM.
+    const size_t l2_budget = 96u << 20;
+    const size_t slice_128 = static_cast<size_t>(n) * 128 * sizeof(float);
+    if (nv > 64 && 4 * slice_128 <= l2_budget) return launch<32, 4, 4>(tb, b, c, feat, all_atomic, st);
+    if (2 * slice_128 <= l2_budget) return launch<32, 2, 4>(tb, b, c, feat, all_atomic, st);
+    return launch<32, 1, 4>(tb, b, c, feat, all_atomic, st);
   }
   if (feat <= 8) return launch<8, 1, 1>(tb, b, c, feat, all_atomic, st);
   if (feat <= 16) return launch<16, 1, 1>(tb, b, c, feat, all_atomic, st);

@@ -58,11 +58,15 @@ csrmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __
   };
 
   flush_finished_rows();  // leading empty rows
-  stream_slots<LPR, VPL, VEC>(indices + p0, a + p0, p1 - p0, reinterpret_cast<const V*>(b), fl,
-                              lane, mask, acc, [&](V(&)[VPL]) {
-                                ++p;
-                                flush_finished_rows();
-                              });
+  auto on_done = [&](V(&)[VPL], int n) {
+    p += n;
+    flush_finished_rows();
+  };
+  const V* bv = reinterpret_cast<const V*>(b);
+  if (feat % (LPR * VPL * VEC) == 0)
+    stream_slots<LPR, VPL, VEC, true, true>(indices + p0, a + p0, p1 - p0, bv, fl, lane, mask, acc, on_done);
+  else
+    stream_slots<LPR, VPL, VEC, true, false>(indices + p0, a + p0, p1 - p0, bv, fl, lane, mask, acc, on_done);
 }
 
 template <int LPR, int VPL, int VEC>
@@ -97,7 +101,7 @@ extern "C" int sparsetir_csrmm_raw(const float* a, const float* b, float* c, con
     if (nv <= 32) return launch<32, 1, 4>(a, b, c, indptr, indices, m, feat, st);
     // Wider rows go feature tile by feature tile (blockIdx.y, the slowest grid dimension), the
     // tile chosen so that the n x tile slice of B a pass gathers from stays resident in L2.
-    const size_t l2_budget = 96u << 20;
+    const size_t l2_budget = 56u << 20;  // what stays resident of data that every SM reads
     const size_t slice_128 = static_cast<size_t>(n) * 128 * sizeof(float);
     if (nv > 64 && 4 * slice_128 <= l2_budget)
       return launch<32, 4, 4>(a, b, c, indptr, indices, m, feat, st);

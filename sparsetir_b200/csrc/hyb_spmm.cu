@@ -115,25 +115,37 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
 #pragma unroll
   for (int v = 0; v < VPL; ++v) acc[v] = Vec<VEC>::zero();
   int j = 1, left = per_row;  // s_rows[sub][j] is the id of the ELL row being accumulated
-  stream_slots<LPR, VPL, VEC>(
-      tb.cols[q] + first, tb.w[q] + first, nslots, reinterpret_cast<const V*>(b), fl, lane, mask,
-      acc, [&](V(&)[VPL]) {
-        if (--left != 0) return;
-        const int row = s_rows[sub][j];
-        const bool atomic =
-            always_atomic || s_rows[sub][j - 1] == row || s_rows[sub][j + 1] == row;
-        V* dst = cv + static_cast<size_t>(row) * fl.row_vecs;
+  auto on_done = [&](V(&)[VPL], int n) {
+    left -= n;
+    if (left != 0) return;
+    const int row = s_rows[sub][j];
+    const bool atomic = always_atomic || s_rows[sub][j - 1] == row || s_rows[sub][j + 1] == row;
+    V* dst = cv + static_cast<size_t>(row) * fl.row_vecs;
 #pragma unroll
-        for (int v = 0; v < VPL; ++v) {
-          if (fl.valid[v]) {
-            if (atomic) Vec<VEC>::atomic_add(dst + fl.off[v], acc[v]);
-            else __stcs(dst + fl.off[v], acc[v]);  // written once: do not displace B rows in L2
-          }
-          acc[v] = Vec<VEC>::zero();
-        }
-        ++j;
-        left = per_row;
-      });
+    for (int v = 0; v < VPL; ++v) {
+      if (fl.valid[v]) {
+        if (atomic) Vec<VEC>::atomic_add(dst + fl.off[v], acc[v]);
+        else __stcs(dst + fl.off[v], acc[v]);  // written once: do not displace B rows in L2
+      }
+      acc[v] = Vec<VEC>::zero();
+    }
+    ++j;
+    left = per_row;
+  };
+  const int32_t* cols = tb.cols[q] + first;
+  const float* wts = tb.w[q] + first;
+  const V* bv = reinterpret_cast<const V*>(b);
+  // Row ends fall on chunk boundaries when the row length is a multiple of the chunk: then the
+  // row-end test runs once per chunk instead of once per slot.
+  const bool per_slot = per_row % ChunkOf<LPR, VPL>::value != 0;
+  const bool full = feat % (LPR * VPL * VEC) == 0;
+  if (per_slot) {
+    if (full) stream_slots<LPR, VPL, VEC, true, true>(cols, wts, nslots, bv, fl, lane, mask, acc, on_done);
+    else stream_slots<LPR, VPL, VEC, true, false>(cols, wts, nslots, bv, fl, lane, mask, acc, on_done);
+  } else {
+    if (full) stream_slots<LPR, VPL, VEC, false, true>(cols, wts, nslots, bv, fl, lane, mask, acc, on_done);
+    else stream_slots<LPR, VPL, VEC, false, false>(cols, wts, nslots, bv, fl, lane, mask, acc, on_done);
+  }
 }
 
 // Zeroes the output rows that the main kernel accumulates into atomically (chunked wide rows
@@ -263,9 +275,10 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
     if (nv <= 32) return launch<32, 1, 4>(tb, b, c, feat, all_atomic, st);
     // Wider rows are covered feature tile by feature tile (blockIdx.y, the slowest grid
     // dimension): a pass gathers from an n x tile slice of B, and the tile is chosen so that
-    // this slice stays resident in the 126 MB L2 while the pass runs.  Re-reading the index
+    // this slice stays resident in L2 while the pass runs (data read by all SMs is held once per
+    // die, so about half of the 126 MB counts).  Re-reading the index
     // arrays once per tile costs little next to re-fetching B rows from HBM.
-    const size_t l2_budget = 96u << 20;
+    const size_t l2_budget = 56u << 20;  // what stays resident of data that every SM reads
     const size_t slice_128 = static_cast<size_t>(n) * 128 * sizeof(float);
     if (nv > 64 && 4 * slice_128 <= l2_budget) return launch<32, 4, 4>(tb, b, c, feat, all_atomic, st);
     if (2 * slice_128 <= l2_budget) return launch<32, 2, 4>(tb, b, c, feat, all_atomic, st);

@@ -117,9 +117,9 @@ rgms_tile_kernel(const float* __restrict__ a, const float* __restrict__ w,
       float4 acc[1] = {make_float4(0.f, 0.f, 0.f, 0.f)};
       if (t < nrows) {
         const int p0 = __ldg(indptr_j + row0 + t), p1 = __ldg(indptr_j + row0 + t + 1);
-        stream_slots<LPR, 1, 4>(indices_j + p0, a + p0, p1 - p0,
-                                reinterpret_cast<const float4*>(x), fl, lane, mask, acc,
-                                [](float4(&)[1]) {});
+        stream_slots<LPR, 1, 4, false, true>(indices_j + p0, a + p0, p1 - p0,
+                                             reinterpret_cast<const float4*>(x), fl, lane, mask,
+                                             acc, [](float4(&)[1], int) {});
       }
       float* dst = zt + t * ZS + lane * 4;
       dst[0] = acc[0].x; dst[1] = acc[0].y; dst[2] = acc[0].z; dst[3] = acc[0].w;

@@ -2,15 +2,18 @@
 // aggregation phase.
 //
 // A group of LPR lanes ("sub-warp") walks a contiguous stream of stored slots
-// (column id, weight).  The lanes read LPR slots at a time with one coalesced load each for ids
-// and weights — the ids of the NEXT batch are requested before the current batch is consumed,
-// so the id latency is off the critical path — then broadcast them one by one with shuffles;
-// for every slot each lane loads its VPL feature vectors of the dense row B[col] and
-// multiplies-accumulates.  Loads are issued U slots ahead of the arithmetic so that U*VPL
-// 16-byte requests per lane are in flight: the kernels are bound by memory latency x
-// bandwidth, not by arithmetic.  After every slot the caller's functor decides whether a row
-// of the output is complete; it must not wait on global memory (row ids come from shared
-// memory or registers), or the wait would serialise with the next batch of loads.
+// (column id, weight).  The lanes read LPR slots at a time ("batch") with one coalesced load
+// each for ids and weights, then broadcast them slot by slot with shuffles; for every slot each
+// lane loads its VPL feature vectors of the dense row B[col] and multiplies-accumulates.
+//
+// The loop is software-pipelined so that a lane always has memory requests in flight — the
+// kernels are bound by memory latency x bandwidth, not by arithmetic:
+//  - the ids of batch i+1 are requested at the start of batch i;
+//  - slots are handled in chunks of U; the B rows of chunk j+1 are requested before chunk j is
+//    consumed (two register buffers), across batch boundaries too.
+// After the slots of a chunk the caller's functor is told how many slots were consumed and
+// decides whether an output row is complete.  It must not wait on global memory (row ids come
+// from shared memory or registers), or that wait would serialise with the loads in flight.
 #ifndef SPARSETIR_B200_SPMM_CORE_CUH_
 #define SPARSETIR_B200_SPMM_CORE_CUH_
 
@@ -34,63 +37,112 @@ struct FeatLane {
   }
 };
 
+// Slots per chunk: 4 vectors per lane and buffer.
+template <int LPR, int VPL>
+struct ChunkOf {
+  static constexpr int kRaw = VPL >= 4 ? 1 : 4 / VPL;
+  static constexpr int value = kRaw < LPR ? kRaw : LPR;
+};
+
 // cols/wts point at the first slot of the stream, nslots is its length.
-// on_slot(acc) is called once per consumed slot, in order.
-template <int LPR, int VPL, int VEC, class OnSlot>
+// PER_SLOT = true : on_done(acc) is called after every slot.
+// PER_SLOT = false: on_done(acc, n) is called after every chunk with the n <= U slots it
+//                   consumed; the caller guarantees that no output row ends inside a chunk.
+// FULL = true promises that every lane's vectors lie inside the feature dimension.
+template <int LPR, int VPL, int VEC, bool PER_SLOT, bool FULL, class OnDone>
 __device__ __forceinline__ void stream_slots(const int32_t* __restrict__ cols,
                                              const float* __restrict__ wts, int nslots,
                                              const typename Vec<VEC>::type* __restrict__ B,
                                              const FeatLane<LPR, VPL, VEC>& fl, int lane,
                                              unsigned mask, typename Vec<VEC>::type (&acc)[VPL],
-                                             OnSlot&& on_slot) {
+                                             OnDone&& on_done) {
   using V = typename Vec<VEC>::type;
-  constexpr int U = (8 / VPL) < LPR ? (8 / VPL) : LPR;  // slots loaded ahead
-  int c_next = 0;
-  float a_next = 0.f;
+  constexpr int U = ChunkOf<LPR, VPL>::value;
+  constexpr int CH = LPR / U;  // chunks per batch (a power of two)
+  if (nslots <= 0) return;
+
+  const V* bl[VPL];  // this lane's column of B
+#pragma unroll
+  for (int v = 0; v < VPL; ++v) bl[v] = B + fl.off[v];
+  const size_t stride = static_cast<size_t>(fl.row_vecs);
+
+  auto request = [&](V(&dst)[U][VPL], int ids, int first) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      // slots past the end carry column 0: the load is harmless and never consumed
+      const int ck = __shfl_sync(mask, ids, first + u, LPR);
+#pragma unroll
+      for (int v = 0; v < VPL; ++v)
+        dst[u][v] = (FULL || fl.valid[v]) ? __ldg(bl[v] + ck * stride) : Vec<VEC>::zero();
+    }
+  };
+  auto consume = [&](V(&src)[U][VPL], float w, int first, int live) {
+    // live = slots of this chunk that exist (>= U for a full chunk)
+    if (PER_SLOT) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float ak = __shfl_sync(mask, w, first + u, LPR);
+        if (u < live) {
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) Vec<VEC>::fma(acc[v], ak, src[u][v]);
+          on_done(acc, 1);
+        }
+      }
+    } else if (live >= U) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float ak = __shfl_sync(mask, w, first + u, LPR);
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) Vec<VEC>::fma(acc[v], ak, src[u][v]);
+      }
+      on_done(acc, U);
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float ak = __shfl_sync(mask, w, first + u, LPR);
+        if (u < live) {
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) Vec<VEC>::fma(acc[v], ak, src[u][v]);
+        }
+      }
+      on_done(acc, live);
+    }
+  };
+
+  int c = 0, c_next = 0;
+  float a = 0.f, a_next = 0.f;
   if (lane < nslots) {
-    c_next = __ldg(cols + lane);
-    a_next = __ldg(wts + lane);
+    c = __ldg(cols + lane);
+    a = __ldg(wts + lane);
   }
+  V buf0[U][VPL], buf1[U][VPL];
+  request(buf0, c, 0);
   for (int s0 = 0; s0 < nslots; s0 += LPR) {
-    const int c = c_next;
-    const float a = a_next;
+    const bool more = s0 + LPR < nslots;
     c_next = 0;
     a_next = 0.f;
-    if (s0 + LPR + lane < nslots) {  // request the next batch's ids now
+    if (s0 + LPR + lane < nslots) {  // ids of the next batch
       c_next = __ldg(cols + s0 + LPR + lane);
       a_next = __ldg(wts + s0 + LPR + lane);
     }
     const int cnt = min(LPR, nslots - s0);
-    for (int k0 = 0; k0 < cnt; k0 += U) {
-      V x[U][VPL];
 #pragma unroll
-      for (int u = 0; u < U; ++u) {
-        // slots past cnt carry column 0 / weight 0: the load is harmless and never consumed
-        const int ck = __shfl_sync(mask, c, k0 + u, LPR);
-        const V* src = B + static_cast<size_t>(ck) * fl.row_vecs;
-#pragma unroll
-        for (int v = 0; v < VPL; ++v) x[u][v] = fl.valid[v] ? __ldg(src + fl.off[v]) : Vec<VEC>::zero();
+    for (int ch = 0; ch < CH; ++ch) {
+      const int first = ch * U;
+      // request the chunk after this one, then consume this one
+      if (ch + 1 < CH) {
+        if (first + U < cnt) {
+          if (ch % 2 == 0) request(buf1, c, first + U); else request(buf0, c, first + U);
+        }
+      } else if (more) {
+        if (ch % 2 == 0) request(buf1, c_next, 0); else request(buf0, c_next, 0);
       }
-      if (k0 + U <= cnt) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const float ak = __shfl_sync(mask, a, k0 + u, LPR);
-#pragma unroll
-          for (int v = 0; v < VPL; ++v) Vec<VEC>::fma(acc[v], ak, x[u][v]);
-          on_slot(acc);
-        }
-      } else {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const float ak = __shfl_sync(mask, a, k0 + u, LPR);
-          if (k0 + u < cnt) {
-#pragma unroll
-            for (int v = 0; v < VPL; ++v) Vec<VEC>::fma(acc[v], ak, x[u][v]);
-            on_slot(acc);
-          }
-        }
+      if (first < cnt) {
+        if (ch % 2 == 0) consume(buf0, a, first, cnt - first); else consume(buf1, a, first, cnt - first);
       }
     }
+    c = c_next;
+    a = a_next;
   }
 }
 

@@ -148,6 +148,106 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
   }
 }
 
+// The main kernel for 16-byte aligned operands: B rows are staged through per-lane rings in
+// shared memory by asynchronous copies (see stream_slots_async), ids / weights / row ids of the
+// item are read into shared memory once, with coalesced loads, before the pipeline starts.
+// One lane covers one 16-byte vector of a 4*LPR-float feature tile; blockIdx.y walks the tiles.
+constexpr int kRing = 12;  // slots in flight per lane
+
+template <int LPR>
+struct AsyncSmem {
+  static constexpr int SUBS = kThreads / LPR;
+  static constexpr int ITEM = item_slots(LPR);
+  static constexpr size_t ring_bytes = sizeof(float4) * SUBS * kRing * LPR;
+  static constexpr size_t bytes = ring_bytes + sizeof(int32_t) * SUBS * (ITEM + ITEM + ITEM + 2);
+};
+
+template <int LPR>
+__global__ void __launch_bounds__(kThreads, 3)
+hyb_spmm_async_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b,
+                      float* __restrict__ c, int feat, int all_atomic) {
+  using S = AsyncSmem<LPR>;
+  constexpr int SUBS = S::SUBS, ITEM = S::ITEM;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int lane = threadIdx.x % LPR;
+  const int sub = threadIdx.x / LPR;
+  float4* ring = reinterpret_cast<float4*>(smem_raw) + sub * (kRing * LPR) + lane;
+  int32_t* s_ids = reinterpret_cast<int32_t*>(smem_raw + S::ring_bytes) + sub * ITEM;
+  float* s_wts = reinterpret_cast<float*>(smem_raw + S::ring_bytes) + SUBS * ITEM + sub * ITEM;
+  int32_t* s_rows = reinterpret_cast<int32_t*>(smem_raw + S::ring_bytes) + 2 * SUBS * ITEM +
+                    sub * (ITEM + 2);
+  const unsigned mask = group_mask<LPR>();
+  const int q = find_bucket(tb, blockIdx.x);
+  const int width = tb.width[q], nrows = tb.nrows[q];
+  const int rpi = tb.rows_per_item[q], cpr = tb.chunks_per_row[q];
+  const long long item = static_cast<long long>(blockIdx.x - tb.block_start[q]) * SUBS + sub;
+  long long r0l;
+  int nslots, per_row, nr;
+  size_t first;
+  if (cpr == 1) {
+    r0l = item * rpi;
+    if (r0l >= nrows) return;
+    nr = static_cast<int>(min(static_cast<long long>(nrows), r0l + rpi) - r0l);
+    nslots = nr * width;
+    per_row = width;
+    first = static_cast<size_t>(r0l) * width;
+  } else {
+    r0l = item / cpr;
+    if (r0l >= nrows) return;
+    const int s0 = static_cast<int>(item % cpr) * ITEM;
+    nr = 1;
+    nslots = min(ITEM, width - s0);
+    per_row = nslots;
+    first = static_cast<size_t>(r0l) * width + s0;
+  }
+  const int r0 = static_cast<int>(r0l);
+  {
+    const int32_t* __restrict__ cols = tb.cols[q] + first;
+    const float* __restrict__ wts = tb.w[q] + first;
+    const int32_t* __restrict__ rows = tb.rows[q];
+    for (int s = lane; s < nslots; s += LPR) {
+      s_ids[s] = __ldg(cols + s);
+      s_wts[s] = __ldg(wts + s);
+    }
+    for (int j = lane; j < nr + 2; j += LPR) {
+      const int idx = r0 - 1 + j;
+      s_rows[j] = (idx >= 0 && idx < nrows) ? __ldg(rows + idx) : -1;
+    }
+  }
+  __syncwarp(mask);
+  const int row_vecs = feat / 4;
+  const int off = blockIdx.y * LPR + lane;
+  const bool valid = off < row_vecs;
+  float4* cv = reinterpret_cast<float4*>(c) + off;
+  const bool always_atomic = all_atomic || cpr > 1;
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  int j = 1, left = per_row;
+  auto on_done = [&](float4&, int n) {
+    left -= n;
+    if (left != 0) return;
+    const int row = s_rows[j];
+    const bool atomic = always_atomic || s_rows[j - 1] == row || s_rows[j + 1] == row;
+    float4* dst = cv + static_cast<size_t>(row) * row_vecs;
+    if (valid) {
+      if (atomic) atomicAdd(dst, acc);
+      else __stcs(dst, acc);  // written once: do not displace B rows in L2
+    }
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    ++j;
+    left = per_row;
+  };
+  const float4* bl = reinterpret_cast<const float4*>(b) + off;
+  // Row ends fall on group boundaries when the row length is a multiple of 4: then the row-end
+  // test runs once per group instead of once per slot.
+  if (per_row % 4 != 0)
+    stream_slots_async<LPR, kRing, true>(s_ids, s_wts, nslots, bl, static_cast<size_t>(row_vecs),
+                                         valid, ring, acc, on_done);
+  else
+    stream_slots_async<LPR, kRing, false>(s_ids, s_wts, nslots, bl, static_cast<size_t>(row_vecs),
+                                          valid, ring, acc, on_done);
+}
+
 // Zeroes the output rows that the main kernel accumulates into atomically (chunked wide rows
 // and split rows), so that repeated calls on the same C stay correct without a full memset.
 // One thread inspects one ELL row (coalesced reads of the row ids); the rows that need clearing
@@ -190,19 +290,46 @@ int lanes_per_row(int feat, bool vec4) {
   return units <= 8 ? 8 : (units <= 16 ? 16 : 32);
 }
 
-template <int LPR, int VPL, int VEC>
-int launch(HybTable& tb, const float* b, float* c, int feat, int all_atomic, cudaStream_t stream) {
-  constexpr int SUBS = kThreads / LPR;
+// Fills block_start for SUBS items per block; returns the number of blocks or -1.
+long long plan_blocks(HybTable& tb, int subs) {
   long long blocks = 0;
   for (int q = 0; q < tb.nb; ++q) {
     tb.block_start[q] = static_cast<int32_t>(blocks);
     const long long items = tb.chunks_per_row[q] > 1
                                 ? static_cast<long long>(tb.nrows[q]) * tb.chunks_per_row[q]
                                 : ceil_div(tb.nrows[q], tb.rows_per_item[q]);
-    blocks += (items + SUBS - 1) / SUBS;
-    if (blocks > INT32_MAX) return fail("sparsetir_hyb_spmm: too many thread blocks");
+    blocks += (items + subs - 1) / subs;
+    if (blocks > INT32_MAX) return -1;
   }
   tb.block_start[tb.nb] = static_cast<int32_t>(blocks);
+  return blocks;
+}
+
+template <int LPR>
+int launch_async(HybTable& tb, const float* b, float* c, int feat, int all_atomic,
+                 cudaStream_t stream) {
+  using S = AsyncSmem<LPR>;
+  const long long blocks = plan_blocks(tb, S::SUBS);
+  if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  SPTIR_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(hyb_spmm_async_kernel<LPR>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(S::bytes)));
+    configured_device = dev;
+  }
+  dim3 grid(static_cast<unsigned>(blocks), ceil_div(feat / 4, LPR));
+  hyb_spmm_async_kernel<LPR><<<grid, kThreads, S::bytes, stream>>>(tb, b, c, feat, all_atomic);
+  SPTIR_LAUNCH_OK("hyb_spmm_async_kernel");
+  return 0;
+}
+
+template <int LPR, int VPL, int VEC>
+int launch(HybTable& tb, const float* b, float* c, int feat, int all_atomic, cudaStream_t stream) {
+  const long long blocks = plan_blocks(tb, kThreads / LPR);
+  if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
   const int tile_feat = LPR * VPL * VEC;
   dim3 grid(static_cast<unsigned>(blocks), ceil_div(feat, tile_feat));
   hyb_spmm_kernel<LPR, VPL, VEC><<<grid, kThreads, 0, stream>>>(tb, b, c, feat, all_atomic);
@@ -269,20 +396,15 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
   if (tb.nb == 0) return 0;
 
   if (vec4) {
+    // One lane per 16-byte vector; rows wider than 128 floats are covered feature tile by
+    // feature tile (blockIdx.y, the slowest grid dimension): a pass gathers from an
+    // n x 128-float slice of B, which is far more likely to stay resident in L2 while the pass
+    // runs than whole rows are.  Re-reading the index arrays once per tile costs little next to
+    // re-fetching B rows from HBM.
     const int nv = feat / 4;
-    if (nv <= 8) return launch<8, 1, 4>(tb, b, c, feat, all_atomic, st);
-    if (nv <= 16) return launch<16, 1, 4>(tb, b, c, feat, all_atomic, st);
-    if (nv <= 32) return launch<32, 1, 4>(tb, b, c, feat, all_atomic, st);
-    // Wider rows are covered feature tile by feature tile (blockIdx.y, the slowest grid
-    // dimension): a pass gathers from an n x tile slice of B, and the tile is chosen so that
-    // this slice stays resident in L2 while the pass runs (data read by all SMs is held once per
-    // die, so about half of the 126 MB counts).  Re-reading the index
-    // arrays once per tile costs little next to re-fetching B rows from HBM.
-    const size_t l2_budget = 56u << 20;  // what stays resident of data that every SM reads
-    const size_t slice_128 = static_cast<size_t>(n) * 128 * sizeof(float);
-    if (nv > 64 && 4 * slice_128 <= l2_budget) return launch<32, 4, 4>(tb, b, c, feat, all_atomic, st);
-    if (2 * slice_128 <= l2_budget) return launch<32, 2, 4>(tb, b, c, feat, all_atomic, st);
-    return launch<32, 1, 4>(tb, b, c, feat, all_atomic, st);
+    if (nv <= 8) return launch_async<8>(tb, b, c, feat, all_atomic, st);
+    if (nv <= 16) return launch_async<16>(tb, b, c, feat, all_atomic, st);
+    return launch_async<32>(tb, b, c, feat, all_atomic, st);
   }
   if (feat <= 8) return launch<8, 1, 1>(tb, b, c, feat, all_atomic, st);
   if (feat <= 16) return launch<16, 1, 1>(tb, b, c, feat, all_atomic, st);

@@ -146,5 +146,70 @@ __device__ __forceinline__ void stream_slots(const int32_t* __restrict__ cols,
   }
 }
 
+// The same walk with the B rows staged through shared memory by asynchronous copies
+// (16-byte feature vectors, one per lane and slot, VPL = 1).
+//
+// Every lane owns a private ring of R 16-byte entries in shared memory: entry e of lane l is
+// ring[e * LPR + l].  A lane only ever reads back what it copied itself, so the only
+// synchronisation is cp.async.wait_group — the ring is an extension of the register file that
+// asynchronous loads can target.  Up to R slots (R * 16 bytes per lane) are in flight, which
+// is what hides HBM latency here; a register-resident pipeline of that depth would not fit.
+//
+// s_cols / s_wts: ids and weights of the stream, already in shared memory.
+// bl: this lane's column of B (B + lane offset, in float4 units); stride = vectors per row.
+// copy = false makes the lane skip its copies (its features lie past the end of the row).
+template <int LPR, int R, bool PER_SLOT, class OnDone>
+__device__ __forceinline__ void stream_slots_async(const int32_t* s_cols, const float* s_wts,
+                                                   int nslots, const float4* __restrict__ bl,
+                                                   size_t stride, bool copy, float4* ring,
+                                                   float4& acc, OnDone&& on_done) {
+  constexpr int U = 4;        // slots per commit group
+  constexpr int NCH = R / U;  // groups the ring holds
+  static_assert(R % U == 0 && NCH >= 2, "ring must hold at least two groups");
+  const int nchunks = (nslots + U - 1) / U;
+
+  auto issue = [&](int chunk, int ring_chunk) {
+    const int s0 = chunk * U;
+    if (copy) {
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        if (s0 + u < nslots)
+          cp_async16(ring + (ring_chunk * U + u) * LPR, bl + s_cols[s0 + u] * stride);
+    }
+    cp_async_commit();  // committed even when empty: keeps the group count uniform
+  };
+
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) issue(i, i);
+  int rc = 0;  // ring position of the chunk being consumed
+  for (int i = 0; i < nchunks; ++i) {
+    cp_async_wait<NCH - 1>();
+    const int s0 = i * U;
+    const int live = min(U, nslots - s0);
+    if (PER_SLOT) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (u < live) {
+          const float4 x = copy ? ring[(rc * U + u) * LPR] : make_float4(0.f, 0.f, 0.f, 0.f);
+          Vec<4>::fma(acc, s_wts[s0 + u], x);
+          on_done(acc, 1);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (u < live) {
+          const float4 x = copy ? ring[(rc * U + u) * LPR] : make_float4(0.f, 0.f, 0.f, 0.f);
+          Vec<4>::fma(acc, s_wts[s0 + u], x);
+        }
+      }
+      on_done(acc, live);
+    }
+    issue(i + NCH, rc);
+    rc = (rc + 1 == NCH) ? 0 : rc + 1;
+  }
+  cp_async_wait<0>();  // nothing of this stream may still land in the ring after we return
+}
+
 }  // namespace sptir
 #endif  // SPARSETIR_B200_SPMM_CORE_CUH_

@@ -51,5 +51,20 @@ inline int pow2_clamp(int x, int lo, int hi) {
   return p;
 }
 
+// Asynchronous 16-byte copy global -> shared (LDGSTS).  The data does not pass through
+// registers, so the number of copies a thread keeps in flight is bounded by shared memory, not
+// by its register budget.
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  const unsigned dst = static_cast<unsigned>(__cvta_generic_to_shared(smem_dst));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;\n" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
 }  // namespace sptir
 #endif  // SPARSETIR_B200_VEC_CUH_

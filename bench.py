@@ -263,20 +263,45 @@ def ours_arm(args, rank, world, local_rank):
     y_full = {f: torch.empty(g.m * f, device=device) for f in FEATS} if world > 1 else None
     shard_rows = [int(cuts[k + 1] - cuts[k]) for k in range(world)]
 
+    # Three streams so that the PCIe link runs in both directions while kernels execute: the
+    # copy-in of feature size k+1 and the copy-out of k-1 overlap the kernels of k.  Events order
+    # every buffer's copy-in -> kernel -> copy-out, and the reuse of the buffers by the next step.
+    main = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    ev_in = {f: torch.cuda.Event() for f in FEATS}
+    ev_done = {f: torch.cuda.Event() for f in FEATS}
+    ev_out = {f: torch.cuda.Event() for f in FEATS}
+    for f in FEATS:
+        ev_done[f].record(main)
+        ev_out[f].record(main)
+
     def e2e_step():
+        if world == 1:
+            for f in FEATS:
+                s_in.wait_event(ev_done[f])       # previous step's kernels have read x_dev[f]
+                with torch.cuda.stream(s_in):
+                    x_dev[f].copy_(x_host[f], non_blocking=True)
+                    ev_in[f].record(s_in)
+            for f in FEATS:
+                main.wait_event(ev_in[f])
+                main.wait_event(ev_out[f])        # previous step's copy-out has read y_dev[f]
+                calls[f]()
+                ev_done[f].record(main)
+                s_out.wait_event(ev_done[f])
+                with torch.cuda.stream(s_out):
+                    y_host[f].copy_(y_dev[f], non_blocking=True)
+                    ev_out[f].record(s_out)
+            main.wait_event(ev_out[FEATS[-1]])    # the step ends when its last result is on the host
+            return
         for f in FEATS:
             if rank == 0:
                 x_dev[f].copy_(x_host[f], non_blocking=True)
-            if world > 1:
-                dist.broadcast(x_dev[f], src=0)
+            dist.broadcast(x_dev[f], src=0)
             calls[f]()
-            if world > 1:
-                outs = list(torch.split(y_full[f], [r * f for r in shard_rows]))
-                dist.all_gather(outs, y_dev[f])
-                if rank == 0:
-                    y_host[f].copy_(y_full[f], non_blocking=True)
-            elif rank == 0:
-                y_host[f].copy_(y_dev[f], non_blocking=True)
+            outs = list(torch.split(y_full[f], [r * f for r in shard_rows]))
+            dist.all_gather(outs, y_dev[f])
+            if rank == 0:
+                y_host[f].copy_(y_full[f], non_blocking=True)
 
     for _ in range(2):
         e2e_step()

@@ -96,6 +96,12 @@ SPARSETIR_API void* sparsetir_get_stream(int device_id);
 SPARSETIR_API int sparsetir_version(void);
 SPARSETIR_API int sparsetir_sm_arch(void);
 
+/* Health check of the tensor-core kernels (no counterpart in the reference): every wait on a
+ * hardware barrier inside them is bounded, and a wait that runs out is counted instead of
+ * hanging the GPU.  Synchronises `device_id` and stores the count since the library was loaded
+ * (0 in a healthy run). */
+SPARSETIR_API int sparsetir_tc_timeouts(int device_id, unsigned int* count);
+
 /* ---- operators (TVMBackendPackedCFunc symbols) ---------------------------------------- */
 
 /* CSR SpMM, fp32.  C[i,:] = sum_{p in row i} A[p] * B[indices[p],:]; rows without entries are

@@ -83,6 +83,7 @@ PLAIN_SYMBOLS = {
     "sparsetir_get_stream": (_vp, [_i]),
     "sparsetir_version": (_i, []),
     "sparsetir_sm_arch": (_i, []),
+    "sparsetir_tc_timeouts": (_i, [_i, ctypes.POINTER(ctypes.c_uint)]),
     "sparsetir_csrmm_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_hyb_spmm_raw": (_i, [_vp, _vp, ctypes.POINTER(EllBucket), _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_sddmm_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),

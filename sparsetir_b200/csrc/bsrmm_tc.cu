@@ -1,12 +1,187 @@
-// Tensor-core (tcgen05) BSR SpMM path.  Placeholder until the kernel lands: reports every shape
-// as unsupported so that the caller takes the CUDA-core kernel.
+// Tensor-core BSR SpMM for 32 x 32 blocks (fp16 blocks and dense operand, fp32 accumulate/out):
+//   C[i*32+bi, f] = sum_{p in block-row i} sum_bj A[p,bi,bj] * B[indices[p]*32+bj, f]
+// Semantics as bsrmm.cu; replaces the wmma kernel of examples/blocksparse/bsr_spmm.py:359-425.
+//
+// A block-row is 32 rows tall but the 5th-generation tensor core multiplies M = 64 or 128 rows,
+// so the product is computed transposed: one thread block owns (block-row i, 128 features) and
+//   D^T[f, bi] (128 x 32, fp32 in TMEM)  +=  Bt[f, bj] (128 x 32)  *  A_p[bi, bj]^T (32 x 32)
+// for every stored block p of the row — M = 128 features, N = 32 block rows, K = 32 block
+// columns = two tcgen05.mma.kind::f16 of K = 16.  The feature-contiguous B rows are an MN-major
+// operand, the row-major A block a K-major operand; neither needs a transpose in memory.
+//
+// Pipeline: 4 shared-memory stages; all 128 threads copy the next block's operands with
+// cp.async straight into the un-swizzled core-matrix layout the tensor core reads
+// (tc05.cuh), one elected thread issues the MMAs, tcgen05.commit arrives on the stage's
+// mbarrier when the tensor core has finished reading it.  Epilogue: TMEM -> registers
+// (lane = feature, 32 columns = 32 block rows) -> 32 coalesced row stores per warp.
+// Every mbarrier wait is bounded; a timeout is counted in a device-side status word and the block
+// gives up cleanly (TMEM freed), so a protocol error cannot hang the GPU.
 #include <cuda_fp16.h>
 
 #include "common.h"
+#include "tc05.cuh"
+#include "vec.cuh"
 
 namespace sptir {
-int bsrmm_tc_launch(const __half*, const __half*, float*, const int32_t*, const int32_t*, int, int,
-                    int, int, int, cudaStream_t) {
-  return 1;
+
+__device__ unsigned int g_tc_timeouts = 0;  // bounded waits that ran out, since module load
+
+namespace {
+
+constexpr int kThreads = 128;
+constexpr int kBlk = 32;
+constexpr int kTileF = 128;
+constexpr int kStages = 4;
+constexpr int kBBytes = kBlk * kTileF * 2;  // B tile of one block: 32 x 128 fp16 = 8 KB
+constexpr int kABytes = kBlk * kBlk * 2;    // A block: 2 KB
+constexpr int kStageBytes = kBBytes + kABytes;
+constexpr uint32_t kTmemCols = 32;
+
+// B tile stage layout (MN-major operand): core matrix (kc = bj/8, fc = f/8) at (kc*16+fc)*128,
+// inside it K-step bj%8 at 16-byte stride, 8 features contiguous.
+constexpr uint32_t kB_SBO = 128;        // next 8 features
+constexpr uint32_t kB_LBO = 16 * 128;   // next 8 block columns
+// A block stage layout (K-major operand): core matrix (kc = bj/8, ng = bi/8) at (kc*4+ng)*128,
+// inside it row bi%8 at 16-byte stride, 8 block columns contiguous.
+constexpr uint32_t kA_SBO = 128;        // next 8 block rows
+constexpr uint32_t kA_LBO = 4 * 128;    // next 8 block columns
+
+__global__ void __launch_bounds__(kThreads)
+bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, float* __restrict__ c,
+                const int32_t* __restrict__ indptr, const int32_t* __restrict__ indices, int feat) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bar_free[kStages];  // stage may be overwritten
+  __shared__ __align__(8) uint64_t bar_done;           // all MMAs of the row have finished
+  __shared__ uint32_t s_tmem;
+  const int i = blockIdx.x;
+  const int f0 = blockIdx.y * kTileF;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int p0 = __ldg(indptr + i), nblk = __ldg(indptr + i + 1) - p0;
+
+  float* crow = c + (static_cast<size_t>(i) * kBlk) * feat + f0 + warp * 32 + lane;
+  if (nblk <= 0) {  // empty block-row: zeros, no tensor-core work
+#pragma unroll 4
+    for (int bi = 0; bi < kBlk; ++bi) crow[static_cast<size_t>(bi) * feat] = 0.f;
+    return;
+  }
+
+  if (tid == 0) {
+    for (int s = 0; s < kStages; ++s) tc05::mbar_init(&bar_free[s], 1);
+    tc05::mbar_init(&bar_done, 1);
+    tc05::fence_mbar_init();
+  }
+  if (warp == 0) tc05::tmem_alloc(&s_tmem, kTmemCols);
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tmem = s_tmem;
+
+  // this thread's share of a stage: 4 chunks of the B tile, 1 chunk of the A block (16 bytes each)
+  const int b_fc = tid >> 3, b_bjlo = tid & 7;  // B: feature chunk 0..15, block column bj%8
+  const int a_bi = tid >> 2, a_kc = tid & 3;    // A: block row, 8-column chunk
+  auto load_stage = [&](int it) {
+    unsigned char* st = smem + (it % kStages) * kStageBytes;
+    const int p = p0 + it;
+    const size_t brow0 = static_cast<size_t>(__ldg(indices + p)) * kBlk;
+#pragma unroll
+    for (int kc = 0; kc < 4; ++kc) {
+      const __half* src = b + (brow0 + kc * 8 + b_bjlo) * feat + f0 + b_fc * 8;
+      cp_async16(st + (kc * 16 + b_fc) * 128 + b_bjlo * 16, src);
+    }
+    const __half* asrc = a + static_cast<size_t>(p) * (kBlk * kBlk) + a_bi * kBlk + a_kc * 8;
+    cp_async16(st + kBBytes + (a_kc * 4 + (a_bi >> 3)) * 128 + (a_bi & 7) * 16, asrc);
+  };
+
+  constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtF16, kTileF, kBlk, /*a_mn=*/1, /*b_mn=*/0);
+  bool ok = true;
+
+  // prologue: blocks 0 .. kStages-2 in flight
+#pragma unroll
+  for (int it = 0; it < kStages - 1; ++it) {
+    if (it < nblk) load_stage(it);
+    cp_async_commit();
+  }
+  for (int it = 0; it < nblk; ++it) {
+    cp_async_wait<kStages - 2>();  // block `it` has landed (for this thread's copies)
+    tc05::fence_async_smem();
+    __syncthreads();               // ... and for everybody's
+    if (warp == 0 && lane == 0) {
+      tc05::fence_after_sync();
+      const uint32_t sb = tc05::smem_u32(smem + (it % kStages) * kStageBytes);
+      const uint32_t sa = sb + kBBytes;
+#pragma unroll
+      for (int ks = 0; ks < 2; ++ks) {  // K = 32 block columns = 2 x 16
+        const uint64_t da = tc05::smem_desc(sb + ks * 2 * kB_LBO, kB_LBO, kB_SBO);
+        const uint64_t db = tc05::smem_desc(sa + ks * 2 * kA_LBO, kA_LBO, kA_SBO);
+        tc05::mma_f16(tmem, da, db, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+      }
+      tc05::mma_commit(&bar_free[it % kStages]);
+      if (it == nblk - 1) tc05::mma_commit(&bar_done);
+    }
+    // refill the stage that block it-1 used with block it+kStages-1
+    const int nxt = it + kStages - 1;
+    if (nxt < nblk) {
+      if (it >= 1) {
+        // the MMAs of block it-1 are the ((it-1)/kStages)-th use of that stage
+        if (!tc05::mbar_wait(&bar_free[(it - 1) % kStages], ((it - 1) / kStages) & 1)) ok = false;
+      }
+      if (__syncthreads_or(!ok)) { ok = false; break; }
+      load_stage(nxt);
+    }
+    cp_async_commit();
+  }
+  cp_async_wait<0>();
+
+  if (ok && !tc05::mbar_wait(&bar_done, 0)) ok = false;
+  ok = !__syncthreads_or(!ok);
+  tc05::fence_after_sync();
+  if (ok) {
+    uint32_t r[32];
+    tc05::tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16), r);
+#pragma unroll
+    for (int bi = 0; bi < kBlk; ++bi) __stcs(crow + static_cast<size_t>(bi) * feat, __uint_as_float(r[bi]));
+  } else if (tid == 0) {
+    atomicAdd(&g_tc_timeouts, 1u);
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc05::tmem_dealloc(tmem, kTmemCols);
 }
+
+}  // namespace
+
+// Returns 0 when launched, 1 when the shape is not handled here, -1 on error.
+int bsrmm_tc_launch(const __half* a, const __half* b, float* c, const int32_t* indptr,
+                    const int32_t* indices, int nb, int mb, int nnzb, int blk, int feat,
+                    cudaStream_t stream) {
+  (void)mb; (void)nnzb;
+  if (blk != kBlk || feat % kTileF != 0) return 1;
+  if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return 1;
+  if (feat / kTileF > 65535) return 1;
+  const size_t smem = static_cast<size_t>(kStages) * kStageBytes;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  SPTIR_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(bsrmm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(smem)));
+    configured_device = dev;
+  }
+  dim3 grid(nb, feat / kTileF);
+  bsrmm_tc_kernel<<<grid, kThreads, smem, stream>>>(a, b, c, indptr, indices, feat);
+  SPTIR_LAUNCH_OK("bsrmm_tc_kernel");
+  return 0;
+}
+
 }  // namespace sptir
+
+// Number of bounded tensor-core waits that ran out on `device_id` since the library was loaded
+// (0 in a healthy run).  Synchronises the device.
+extern "C" int sparsetir_tc_timeouts(int device_id, unsigned int* count) {
+  using namespace sptir;
+  if (!count) return fail("sparsetir_tc_timeouts: null pointer argument");
+  if (use_device(device_id) != 0) return -1;
+  SPTIR_CUDA_OK(cudaDeviceSynchronize());
+  SPTIR_CUDA_OK(cudaMemcpyFromSymbol(count, g_tc_timeouts, sizeof(unsigned int)));
+  return 0;
+}

@@ -390,3 +390,12 @@ def test_calls_run_on_the_current_torch_stream(cuda_device):
         got = run_csrmm(c, x, cuda_device)
         assert L.load().sparsetir_get_stream(0) == s.cuda_stream
     close(got, oracle_csrmm(c, x))
+
+
+def test_tensor_core_waits_never_ran_out(cuda_device):
+    """Runs after the BSR / RGMS tests above: no bounded barrier wait of the tensor-core kernels
+    may have hit its limit."""
+    import ctypes
+    n = ctypes.c_uint(123)
+    assert L.load().sparsetir_tc_timeouts(0, ctypes.byref(n)) == 0, L.last_error()
+    assert n.value == 0

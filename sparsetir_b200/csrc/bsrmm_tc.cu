@@ -25,6 +25,7 @@
 namespace sptir {
 
 __device__ unsigned int g_tc_timeouts = 0;  // bounded waits that ran out, since module load
+int rgms_tc_timeouts(unsigned int* count);  // the same counter of rgms_tc.cu
 
 namespace {
 
@@ -182,6 +183,9 @@ extern "C" int sparsetir_tc_timeouts(int device_id, unsigned int* count) {
   if (!count) return fail("sparsetir_tc_timeouts: null pointer argument");
   if (use_device(device_id) != 0) return -1;
   SPTIR_CUDA_OK(cudaDeviceSynchronize());
-  SPTIR_CUDA_OK(cudaMemcpyFromSymbol(count, g_tc_timeouts, sizeof(unsigned int)));
+  unsigned int bsr = 0, rgms = 0;
+  SPTIR_CUDA_OK(cudaMemcpyFromSymbol(&bsr, g_tc_timeouts, sizeof(unsigned int)));
+  if (rgms_tc_timeouts(&rgms) != 0) return -1;
+  *count = bsr + rgms;
   return 0;
 }

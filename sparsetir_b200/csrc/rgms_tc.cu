@@ -1,10 +1,181 @@
-// Tensor-core (tcgen05) RGMS path.  Placeholder until the kernel lands: reports every shape as
-// unsupported so that the caller takes the CUDA-core kernel.
+// Tensor-core RGMS for feat_size 64, fp32 in and out:
+//   Y[I[i], fo] += sum_{p in CSF row i of relation r} A[p] * sum_fi W[r,fo,fi] * X[J[p],fi]
+// Semantics and formulation (aggregate first, transform once per (relation, row)) as rgms.cu;
+// replaces the wmma kernel of examples/rgms/rgcn/bench_rgcn_tensorcore.py:651-858, which
+// multiplies fp16 copies of X and W.
+//
+// One thread block owns a tile of up to 128 CSF rows of one relation:
+//   phase 1  sub-warps gather-aggregate Z[t,:] = sum_p A[p] X[J[p],:] in fp32 registers and
+//            write it to shared memory directly in the core-matrix layout the tensor core
+//            reads (tc05.cuh), split into a TF32-exact high part and a low remainder;
+//   phase 2  D[t,fo] (128 x 64 fp32 in TMEM) = Z[t,fi] * W_r[fo,fi]^T with tcgen05.mma.kind::tf32,
+//            M = 128 tile rows, N = 64, K = 64 = 8 steps of 8.  Plain TF32 (10-bit mantissa)
+//            would miss the fp32 tolerance of this operator (rtol 1e-4), so every step runs the
+//            three products Zhi*Whi + Zlo*Whi + Zhi*Wlo ("3xTF32"), which carries ~21 bits;
+//   phase 3  TMEM -> registers (lane = tile row, 32 columns per thread) -> 16-byte vector
+//            atomics into Y[I[t], :].
+// The one mbarrier wait (tensor core done) is bounded; a timeout is counted and the block gives
+// up cleanly.
 #include "common.h"
+#include "rgms_common.cuh"
+#include "spmm_core.cuh"
+#include "tc05.cuh"
 
 namespace sptir {
-int rgms_tc_launch(const float*, const float*, const float*, float*, const int32_t*, const int32_t*,
-                   const int32_t*, const int32_t*, int, int, int, cudaStream_t) {
-  return 1;
+
+__device__ unsigned int g_rgms_tc_timeouts = 0;
+
+namespace {
+
+constexpr int kF = 64;
+constexpr int kTM = 128;
+constexpr int kLPR = kF / 4;                   // 16 lanes cover a feature row
+constexpr int kSubs = kRgmsThreads / kLPR;     // 16 rows in flight per block
+constexpr int kZBytes = kTM * kF * 4;          // 32 KB per Z part
+constexpr int kWBytes = kF * kF * 4;           // 16 KB per W part
+constexpr size_t kSmemBytes = 2 * kZBytes + 2 * kWBytes;
+// K-major operands, no swizzle: core matrix (kc = fi/4, g = row/8) at (kc*groups + g)*128,
+// row%8 at 16-byte stride inside it, 4 floats of K contiguous.
+constexpr uint32_t kZ_SBO = 128, kZ_LBO = (kTM / 8) * 128;  // 16 row groups
+constexpr uint32_t kW_SBO = 128, kW_LBO = (kF / 8) * 128;   // 8 row groups
+
+__device__ __forceinline__ float tf32_hi(float x) {
+  return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);  // what the tensor core keeps
 }
+
+__global__ void __launch_bounds__(kRgmsThreads)
+rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
+               const float* __restrict__ x, float* __restrict__ y,
+               const int32_t* __restrict__ indptr_i, const int32_t* __restrict__ indices_i,
+               const int32_t* __restrict__ indptr_j, const int32_t* __restrict__ indices_j,
+               int num_rels) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(8) uint64_t bar_done;
+  __shared__ uint32_t s_tmem;
+  unsigned char* z_hi = smem;
+  unsigned char* z_lo = smem + kZBytes;
+  unsigned char* w_hi = smem + 2 * kZBytes;
+  unsigned char* w_lo = w_hi + kWBytes;
+
+  int rel, row0, row1;
+  if (!locate_tile(indptr_i, num_rels, kTM, blockIdx.x, &rel, &row0, &row1)) return;
+  const int nrows = row1 - row0;
+  const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
+
+  if (tid == 0) {
+    tc05::mbar_init(&bar_done, 1);
+    tc05::fence_mbar_init();
+  }
+  if (warp == 0) tc05::tmem_alloc(&s_tmem, kF);
+
+  // W_r[fo, fi] -> core matrices, split hi/lo.  One 16-byte chunk = (fo, kc = fi/4).
+  const float4* wr = reinterpret_cast<const float4*>(w + static_cast<size_t>(rel) * kF * kF);
+  for (int ch = tid; ch < kF * kF / 4; ch += kRgmsThreads) {
+    const int fo = ch / (kF / 4), kc = ch % (kF / 4);
+    const float4 v = __ldg(wr + ch);
+    const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+    const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+    const int off = (kc * (kF / 8) + (fo >> 3)) * 128 + (fo & 7) * 16;
+    *reinterpret_cast<float4*>(w_hi + off) = h;
+    *reinterpret_cast<float4*>(w_lo + off) = l;
+  }
+
+  // phase 1: gather-aggregate; lane = kc (its 4 features are one core-matrix row chunk)
+  {
+    const int lane = tid % kLPR;
+    const unsigned mask = group_mask<kLPR>();
+    const FeatLane<kLPR, 1, 4> fl(kF, 0, lane);
+    for (int t = tid / kLPR; t < kTM; t += kSubs) {
+      float4 acc[1] = {make_float4(0.f, 0.f, 0.f, 0.f)};
+      if (t < nrows) {
+        const int p0 = __ldg(indptr_j + row0 + t), p1 = __ldg(indptr_j + row0 + t + 1);
+        stream_slots<kLPR, 1, 4, false, true>(indices_j + p0, a + p0, p1 - p0,
+                                              reinterpret_cast<const float4*>(x), fl, lane, mask,
+                                              acc, [](float4(&)[1], int) {});
+      }
+      const float4 v = acc[0];
+      const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+      const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+      const int off = (lane * (kTM / 8) + (t >> 3)) * 128 + (t & 7) * 16;
+      *reinterpret_cast<float4*>(z_hi + off) = h;
+      *reinterpret_cast<float4*>(z_lo + off) = l;
+    }
+  }
+  tc05::fence_async_smem();   // shared-memory writes above -> visible to the tensor core
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tmem = s_tmem;
+
+  // phase 2: one thread issues 8 K-steps x 3 products
+  if (tid == 0) {
+    constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtTF32, kTM, kF, /*a_mn=*/0, /*b_mn=*/0);
+    const uint32_t zh = tc05::smem_u32(z_hi), zl = tc05::smem_u32(z_lo);
+    const uint32_t wh = tc05::smem_u32(w_hi), wl = tc05::smem_u32(w_lo);
+#pragma unroll
+    for (int ks = 0; ks < kF / 8; ++ks) {  // K = 8 floats = two core matrices per step
+      const uint64_t dzh = tc05::smem_desc(zh + ks * 2 * kZ_LBO, kZ_LBO, kZ_SBO);
+      const uint64_t dzl = tc05::smem_desc(zl + ks * 2 * kZ_LBO, kZ_LBO, kZ_SBO);
+      const uint64_t dwh = tc05::smem_desc(wh + ks * 2 * kW_LBO, kW_LBO, kW_SBO);
+      const uint64_t dwl = tc05::smem_desc(wl + ks * 2 * kW_LBO, kW_LBO, kW_SBO);
+      tc05::mma_tf32(tmem, dzl, dwh, idesc, ks > 0 ? 1u : 0u);  // small terms first
+      tc05::mma_tf32(tmem, dzh, dwl, idesc, 1u);
+      tc05::mma_tf32(tmem, dzh, dwh, idesc, 1u);
+    }
+    tc05::mma_commit(&bar_done);
+  }
+  bool ok = tc05::mbar_wait(&bar_done, 0);
+  ok = !__syncthreads_or(!ok);
+  tc05::fence_after_sync();
+
+  // phase 3: warps w and w+4 share TMEM lanes 32*(w%4)..+31 and take 32 columns each
+  if (ok) {
+    const int t = (warp & 3) * 32 + lane32;
+    const int col0 = (warp >> 2) * 32;
+    uint32_t r[32];
+    tc05::tmem_ld32(tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + col0, r);
+    if (t < nrows) {
+      float4* dst = reinterpret_cast<float4*>(y + static_cast<size_t>(__ldg(indices_i + row0 + t)) * kF + col0);
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        atomicAdd(dst + k, make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]),
+                                       __uint_as_float(r[4 * k + 2]), __uint_as_float(r[4 * k + 3])));
+    }
+  } else if (tid == 0) {
+    atomicAdd(&g_rgms_tc_timeouts, 1u);
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc05::tmem_dealloc(tmem, kF);
+}
+
+}  // namespace
+
+// Returns 0 when launched, 1 when the shape is not handled here, -1 on error.
+int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,
+                   const int32_t* indptr_i, const int32_t* indices_i, const int32_t* indptr_j,
+                   const int32_t* indices_j, int num_rels, int feat, int nnz_i,
+                   cudaStream_t stream) {
+  if (feat != kF) return 1;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  SPTIR_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(rgms_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       static_cast<int>(kSmemBytes)));
+    configured_device = dev;
+  }
+  // upper bound on the number of tiles: every relation can add one partly filled tile
+  const long long blocks = static_cast<long long>(nnz_i) / kTM + num_rels;
+  rgms_tc_kernel<<<static_cast<unsigned>(blocks), kRgmsThreads, kSmemBytes, stream>>>(
+      a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels);
+  SPTIR_LAUNCH_OK("rgms_tc_kernel");
+  return 0;
+}
+
+int rgms_tc_timeouts(unsigned int* count) {
+  SPTIR_CUDA_OK(cudaMemcpyFromSymbol(count, g_rgms_tc_timeouts, sizeof(unsigned int)));
+  return 0;
+}
+
 }  // namespace sptir

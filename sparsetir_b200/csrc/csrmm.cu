@@ -3,7 +3,7 @@
 // like the reference's scheduled GPU kernel (examples/spmm/bench_spmm_naive.py:102-119) rows
 // without entries are written as zeros.
 //
-// Mapping: a group of LPR lanes owns ROWS_PER_ITEM consecutive rows and streams their stored
+// Mapping: a group of LPR lanes owns 1, 2 or 4 consecutive rows and streams their stored
 // entries as one contiguous slot stream (see spmm_core.cuh); each lane keeps VPL 16-byte
 // pieces of the output row in registers and stores them when the row's last entry has been
 // consumed.  One writer per output row: no atomics, deterministic summation in CSR order.
@@ -14,22 +14,21 @@ namespace sptir {
 namespace {
 
 constexpr int kThreads = 256;
-constexpr int kRowsPerItem = 4;
 
 template <int LPR, int VPL, int VEC>
 __global__ void __launch_bounds__(kThreads)
 csrmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
              const int32_t* __restrict__ indptr, const int32_t* __restrict__ indices, int m,
-             int feat) {
+             int feat, int rows_per_item) {
   using V = typename Vec<VEC>::type;
   constexpr int SUBS = kThreads / LPR;
   const int lane = threadIdx.x % LPR;
   const unsigned mask = group_mask<LPR>();
   const long long item = static_cast<long long>(blockIdx.x) * SUBS + threadIdx.x / LPR;
-  const long long r0l = item * kRowsPerItem;
+  const long long r0l = item * rows_per_item;
   if (r0l >= m) return;
   const int r0 = static_cast<int>(r0l);
-  const int r1 = min(m, r0 + kRowsPerItem);
+  const int r1 = min(m, r0 + rows_per_item);
   const FeatLane<LPR, VPL, VEC> fl(feat, blockIdx.y, lane);
   V* cv = reinterpret_cast<V*>(c);
 
@@ -74,8 +73,13 @@ int launch(const float* a, const float* b, float* c, const int32_t* indptr, cons
            int m, int feat, cudaStream_t stream) {
   constexpr int SUBS = kThreads / LPR;
   const int tile_feat = LPR * VPL * VEC;
-  dim3 grid(ceil_div(ceil_div(m, kRowsPerItem), SUBS), ceil_div(feat, tile_feat));
-  csrmm_kernel<LPR, VPL, VEC><<<grid, kThreads, 0, stream>>>(a, b, c, indptr, indices, m, feat);
+  // Several consecutive rows per sub-warp amortise the pipeline start-up, but only once there
+  // are enough rows to fill the machine a few times over; small matrices get one row each.
+  const long long resident_subs = static_cast<long long>(kNumSMs) * 8 * SUBS;
+  const int rows_per_item = m >= 4 * resident_subs ? 4 : (m >= 2 * resident_subs ? 2 : 1);
+  dim3 grid(ceil_div(ceil_div(m, rows_per_item), SUBS), ceil_div(feat, tile_feat));
+  csrmm_kernel<LPR, VPL, VEC><<<grid, kThreads, 0, stream>>>(a, b, c, indptr, indices, m, feat,
+                                                              rows_per_item);
   SPTIR_LAUNCH_OK("csrmm_kernel");
   return 0;
 }

@@ -66,19 +66,10 @@ rgms_tile_kernel(const float* __restrict__ a, const float* __restrict__ w,
   // phase 1: gather-aggregate
   {
     const int lane = threadIdx.x % LPR;
-    const unsigned mask = group_mask<LPR>();
-    const FeatLane<LPR, 1, 4> fl(F, 0, lane);
-    for (int t = threadIdx.x / LPR; t < kTM; t += SUBS) {
-      float4 acc[1] = {make_float4(0.f, 0.f, 0.f, 0.f)};
-      if (t < nrows) {
-        const int p0 = __ldg(indptr_j + row0 + t), p1 = __ldg(indptr_j + row0 + t + 1);
-        stream_slots<LPR, 1, 4, false, true>(indices_j + p0, a + p0, p1 - p0,
-                                             reinterpret_cast<const float4*>(x), fl, lane, mask,
-                                             acc, [](float4(&)[1], int) {});
-      }
+    gather_tile_rows<F, kTM>(a, x, indptr_j, indices_j, row0, nrows, [&](int t, float4 v) {
       float* dst = zt + t * ZS + lane * 4;
-      dst[0] = acc[0].x; dst[1] = acc[0].y; dst[2] = acc[0].z; dst[3] = acc[0].w;
-    }
+      dst[0] = v.x; dst[1] = v.y; dst[2] = v.z; dst[3] = v.w;
+    });
   }
   __syncthreads();
 

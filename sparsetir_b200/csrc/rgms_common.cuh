@@ -5,6 +5,8 @@
 #include <cuda_runtime.h>
 #include <cstdint>
 
+#include "spmm_core.cuh"
+
 namespace sptir {
 
 constexpr int kRgmsThreads = 256;
@@ -54,6 +56,55 @@ __device__ inline bool locate_tile(const int32_t* __restrict__ indptr_i, int num
   *row_begin = s_found[1];
   *row_end = s_found[2];
   return s_found[0] >= 0;
+}
+
+// Phase 1 of both RGMS kernels: Z[t,:] = sum_{p in CSF row row0+t} A[p] * X[J[p],:] for the
+// TILE_ROWS rows of a tile (rows >= nrows give zeros).
+// The stored entries of a tile are contiguous, so every sub-warp of LPR = F/4 lanes takes
+// TILE_ROWS / SUBS consecutive rows and walks their entries as ONE stream (ids prefetched,
+// gathers double-buffered across row boundaries, see spmm_core.cuh) instead of paying the
+// pointer -> id -> row latency chain once per row; row ends come from the tile's row pointers,
+// staged in shared memory.  write_row(t, acc) receives every finished row exactly once.
+// Must be called by all threads of the block (it synchronises).
+template <int F, int TILE_ROWS, class WriteRow>
+__device__ __forceinline__ void gather_tile_rows(const float* __restrict__ a,
+                                                 const float* __restrict__ x,
+                                                 const int32_t* __restrict__ indptr_j,
+                                                 const int32_t* __restrict__ indices_j, int row0,
+                                                 int nrows, WriteRow&& write_row) {
+  constexpr int LPR = F / 4;
+  constexpr int SUBS = kRgmsThreads / LPR;
+  constexpr int RPS = TILE_ROWS / SUBS;  // rows per sub-warp
+  static_assert(TILE_ROWS % SUBS == 0, "tile rows must divide evenly over the sub-warps");
+  __shared__ int32_t s_ptr[TILE_ROWS + 1];
+  for (int t = threadIdx.x; t <= nrows; t += kRgmsThreads) s_ptr[t] = __ldg(indptr_j + row0 + t);
+  __syncthreads();
+  const int lane = threadIdx.x % LPR;
+  const unsigned mask = group_mask<LPR>();
+  const FeatLane<LPR, 1, 4> fl(F, 0, lane);
+  const int r_lo = (threadIdx.x / LPR) * RPS;
+  const int r_hi = min(nrows, r_lo + RPS);
+  float4 acc[1] = {make_float4(0.f, 0.f, 0.f, 0.f)};
+  if (r_lo < r_hi) {
+    const int p_begin = s_ptr[r_lo], p_end = s_ptr[r_hi];
+    int cur = r_lo, p = p_begin, row_end = s_ptr[r_lo + 1];
+    auto flush = [&]() {
+      while (cur < r_hi && p >= row_end) {
+        write_row(cur, acc[0]);
+        acc[0] = make_float4(0.f, 0.f, 0.f, 0.f);
+        ++cur;
+        if (cur < r_hi) row_end = s_ptr[cur + 1];
+      }
+    };
+    flush();  // rows without entries at the front
+    stream_slots<LPR, 1, 4, true, true>(indices_j + p_begin, a + p_begin, p_end - p_begin,
+                                        reinterpret_cast<const float4*>(x), fl, lane, mask, acc,
+                                        [&](float4(&)[1], int n) {
+                                          p += n;
+                                          flush();
+                                        });
+  }
+  for (int t = max(r_lo, nrows); t < r_lo + RPS; ++t) write_row(t, make_float4(0.f, 0.f, 0.f, 0.f));
 }
 
 }  // namespace sptir

@@ -30,7 +30,6 @@ namespace {
 constexpr int kF = 64;
 constexpr int kTM = 128;
 constexpr int kLPR = kF / 4;                   // 16 lanes cover a feature row
-constexpr int kSubs = kRgmsThreads / kLPR;     // 16 rows in flight per block
 constexpr int kZBytes = kTM * kF * 4;          // 32 KB per Z part
 constexpr int kWBytes = kF * kF * 4;           // 16 KB per W part
 constexpr size_t kSmemBytes = 2 * kZBytes + 2 * kWBytes;
@@ -83,23 +82,13 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
   // phase 1: gather-aggregate; lane = kc (its 4 features are one core-matrix row chunk)
   {
     const int lane = tid % kLPR;
-    const unsigned mask = group_mask<kLPR>();
-    const FeatLane<kLPR, 1, 4> fl(kF, 0, lane);
-    for (int t = tid / kLPR; t < kTM; t += kSubs) {
-      float4 acc[1] = {make_float4(0.f, 0.f, 0.f, 0.f)};
-      if (t < nrows) {
-        const int p0 = __ldg(indptr_j + row0 + t), p1 = __ldg(indptr_j + row0 + t + 1);
-        stream_slots<kLPR, 1, 4, false, true>(indices_j + p0, a + p0, p1 - p0,
-                                              reinterpret_cast<const float4*>(x), fl, lane, mask,
-                                              acc, [](float4(&)[1], int) {});
-      }
-      const float4 v = acc[0];
+    gather_tile_rows<kF, kTM>(a, x, indptr_j, indices_j, row0, nrows, [&](int t, float4 v) {
       const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
       const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
       const int off = (lane * (kTM / 8) + (t >> 3)) * 128 + (t & 7) * 16;
       *reinterpret_cast<float4*>(z_hi + off) = h;
       *reinterpret_cast<float4*>(z_lo + off) = l;
-    }
+    });
   }
   tc05::fence_async_smem();   // shared-memory writes above -> visible to the tensor core
   tc05::fence_before_sync();

@@ -406,10 +406,25 @@ def main():
                     help="comma-separated feature sizes (default: the workload's 32,64,128,256,512)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the device-resident steps and stop (for profiler captures)")
+    ap.add_argument("--only-op", default=None, choices=["csrmm", "bsrmm", "rgms", "sddmm"],
+                    help="measure one of the other operators alone and stop (for profiler captures)")
     args = ap.parse_args()
     if args.feats:
         global FEATS
         FEATS = tuple(int(x) for x in args.feats.split(","))
+    if args.only_op:
+        import torch
+        from sparsetir_b200 import opbench
+        dev = torch.device("cuda", 0)
+        peaks = load_peaks()
+        if args.only_op == "sddmm":
+            feats = FEATS if args.feats else (32,)
+            print(json.dumps(opbench.bench_sddmm(dev, peaks, feats=feats)), flush=True)
+        else:
+            flush = torch.empty(2 * opbench.L2_BYTES, dtype=torch.uint8, device=dev)
+            fn = getattr(opbench, "bench_" + args.only_op)
+            print(json.dumps(fn(dev, peaks, flush)), flush=True)
+        return
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -148,6 +148,177 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Lean kernel: the fast path for 16-byte aligned operands, whole feature tiles and ELL widths
+// of 1, 2, 4 or a multiple of 8 (every power-of-two bucket list).  Same work items and the
+// same results as the kernels above, but written for instruction economy — the gathers come
+// from L2 at well over 10 TB/s if, and only if, the warp spends its issue slots on loads:
+// per stored slot the loop executes one shuffle + one address + one 16-byte load, then one
+// shuffle + four FMAs; row ends sit at compile-time positions of the unrolled batch (narrow
+// rows) or are tested once per 8 slots (wide rows); row ids travel in registers with the
+// "accumulate atomically" flag in the sign bit, so a row end costs one shuffle and a store.
+template <int LPR, int WM>  // WM = 1, 2, 4: the ELL width itself; WM = 8: a multiple of 8
+__device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
+                                          const float* __restrict__ wts,
+                                          const int32_t* __restrict__ rows, int nrows, int r0,
+                                          int nr, int nslots, int per_row,
+                                          const float4* __restrict__ bl, unsigned row_bytes,
+                                          float4* __restrict__ cl, bool always_atomic, int lane,
+                                          unsigned mask) {
+  constexpr int U = 8;
+  // address of this lane's vector in dense row `col`: one 32x32->64 multiply-add
+  auto vec_of = [&](const float4* base, int col) -> const float4* {
+    return reinterpret_cast<const float4*>(reinterpret_cast<const char*>(base) +
+                                           static_cast<unsigned long long>(static_cast<unsigned>(col)) * row_bytes);
+  };
+  static_assert(LPR % U == 0, "a batch is a whole number of chunks");
+  constexpr int RPB = WM < 8 ? LPR / WM : 0;  // ELL rows that end inside one batch (narrow rows)
+
+  // row id of ELL row g of the bucket, sign bit set when it must be accumulated atomically
+  auto row_flag = [&](int g) -> int {
+    if (g >= nrows) return 0;
+    const int rid = __ldg(rows + g);
+    const bool split = (g > 0 && __ldg(rows + g - 1) == rid) ||
+                       (g + 1 < nrows && __ldg(rows + g + 1) == rid);
+    return rid | ((always_atomic || split) ? 0x80000000 : 0);
+  };
+  auto row_end = [&](float4& acc, int rf) {
+    float4* dst = const_cast<float4*>(vec_of(cl, rf & 0x7fffffff));
+    if (rf < 0) atomicAdd(dst, acc);
+    else __stcs(dst, acc);  // written once: do not displace B rows in L2
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  };
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  int c = 0, rf = 0;
+  float a = 0.f;
+  if (lane < nslots) {
+    c = __ldg(cols + lane);
+    a = __ldg(wts + lane);
+  }
+  if (WM < 8) {
+    if (lane < RPB) rf = row_flag(r0 + lane);   // rows ending in batch 0
+  } else {
+    if (lane < nr) rf = row_flag(r0 + lane);    // all rows of the item (nr <= LPR / 2)
+  }
+  int left = per_row, jrow = 0;  // wide rows only
+
+  for (int s0 = 0; s0 < nslots; s0 += LPR) {
+    int cn = 0, rfn = 0;
+    float an = 0.f;
+    if (s0 + LPR + lane < nslots) {  // ids, weights (and row ids) of the next batch
+      cn = __ldg(cols + s0 + LPR + lane);
+      an = __ldg(wts + s0 + LPR + lane);
+    }
+    if (WM < 8 && s0 + LPR < nslots && lane < RPB) rfn = row_flag(r0 + (s0 + LPR) / WM + lane);
+    const int cnt = nslots - s0;  // live slots of this batch if < LPR
+    if (cnt >= LPR) {
+#pragma unroll
+      for (int k0 = 0; k0 < LPR; k0 += U) {
+        float4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          x[u] = __ldg(vec_of(bl, __shfl_sync(mask, c, k0 + u, LPR)));
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          Vec<4>::fma(acc, __shfl_sync(mask, a, k0 + u, LPR), x[u]);
+          if (WM < 8 && (k0 + u + 1) % WM == 0)
+            row_end(acc, __shfl_sync(mask, rf, (k0 + u) / WM, LPR));
+        }
+        if (WM == 8) {
+          left -= U;
+          if (left == 0) {
+            row_end(acc, __shfl_sync(mask, rf, jrow, LPR));
+            ++jrow;
+            left = per_row;
+          }
+        }
+      }
+    } else {  // last, partly filled batch: slots past the end are neither added nor stored
+#pragma unroll
+      for (int k0 = 0; k0 < LPR; k0 += U) {
+        if (k0 < cnt) {
+          float4 x[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u)
+            x[u] = __ldg(vec_of(bl, __shfl_sync(mask, c, k0 + u, LPR)));  // dead slots: column 0
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const float ak = __shfl_sync(mask, a, k0 + u, LPR);
+            const int rfe = (WM < 8) ? __shfl_sync(mask, rf, (k0 + u) / WM, LPR) : 0;
+            if (k0 + u < cnt) {
+              Vec<4>::fma(acc, ak, x[u]);
+              if (WM < 8 && (k0 + u + 1) % WM == 0) row_end(acc, rfe);
+            }
+          }
+          if (WM == 8) {  // wide rows: nslots is a multiple of 8, so the chunk was whole
+            left -= U;
+            if (left == 0) {
+              row_end(acc, __shfl_sync(mask, rf, jrow, LPR));
+              ++jrow;
+              left = per_row;
+            }
+          }
+        }
+      }
+    }
+    c = cn;
+    a = an;
+    if (WM < 8) rf = rfn;
+  }
+}
+
+template <int LPR>
+__global__ void __launch_bounds__(kThreads, 4)
+hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b,
+                     float* __restrict__ c, int feat, int all_atomic) {
+  constexpr int SUBS = kThreads / LPR;
+  constexpr int ITEM = item_slots(LPR);
+  const int lane = threadIdx.x % LPR;
+  const int sub = threadIdx.x / LPR;
+  const unsigned mask = group_mask<LPR>();
+  const int q = find_bucket(tb, blockIdx.x);
+  const int width = tb.width[q], nrows = tb.nrows[q];
+  const int rpi = tb.rows_per_item[q], cpr = tb.chunks_per_row[q];
+  const long long item = static_cast<long long>(blockIdx.x - tb.block_start[q]) * SUBS + sub;
+  long long r0l;
+  int nslots, per_row, nr;
+  size_t first;
+  if (cpr == 1) {
+    r0l = item * rpi;
+    if (r0l >= nrows) return;
+    nr = static_cast<int>(min(static_cast<long long>(nrows), r0l + rpi) - r0l);
+    nslots = nr * width;
+    per_row = width;
+    first = static_cast<size_t>(r0l) * width;
+  } else {
+    r0l = item / cpr;
+    if (r0l >= nrows) return;
+    const int s0 = static_cast<int>(item % cpr) * ITEM;
+    nr = 1;
+    nslots = min(ITEM, width - s0);
+    per_row = nslots;
+    first = static_cast<size_t>(r0l) * width + s0;
+  }
+  const int r0 = static_cast<int>(r0l);
+  const unsigned stride = static_cast<unsigned>(feat) * 4u;  // bytes per dense row
+  const int off = blockIdx.y * LPR + lane;
+  const float4* bl = reinterpret_cast<const float4*>(b) + off;
+  float4* cl = reinterpret_cast<float4*>(c) + off;
+  const int32_t* cols = tb.cols[q] + first;
+  const float* wts = tb.w[q] + first;
+  const int32_t* rows = tb.rows[q];
+  const bool always_atomic = all_atomic || cpr > 1;
+  if (width == 1)
+    lean_item<LPR, 1>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
+  else if (width == 2)
+    lean_item<LPR, 2>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
+  else if (width == 4)
+    lean_item<LPR, 4>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
+  else
+    lean_item<LPR, 8>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
+}
+
 // The main kernel for 16-byte aligned operands: B rows are staged through per-lane rings in
 // shared memory by asynchronous copies (see stream_slots_async), ids / weights / row ids of the
 // item are read into shared memory once, with coalesced loads, before the pipeline starts.
@@ -284,10 +455,20 @@ void plan_items(HybTable& tb, int item) {
   }
 }
 
-// Lanes per dense row for a feature size, the first template argument of the kernel used.
-int lanes_per_row(int feat, bool vec4) {
+// Lanes per dense row, the first template argument of the kernel used: one lane per 16-byte
+// vector, at most a warp.  Rows wider than the lanes cover are walked feature tile by feature
+// tile (blockIdx.y, the slowest grid dimension).  A pass gathers from an n x tile slice of B; the
+// tile is narrowed until that slice fits the part of L2 that stays resident for data every SM
+// reads (measured: about half of the 126 MB), because re-reading the index arrays once per tile
+// costs little next to re-fetching B rows from HBM.
+int lanes_per_row(int feat, bool vec4, int n) {
   const int units = vec4 ? feat / 4 : feat;
-  return units <= 8 ? 8 : (units <= 16 ? 16 : 32);
+  int lanes = units <= 8 ? 8 : (units <= 16 ? 16 : 32);
+  if (vec4) {
+    const size_t l2_budget = 96u << 20;
+    while (lanes > 8 && static_cast<size_t>(n) * lanes * 16 > l2_budget) lanes /= 2;
+  }
+  return lanes;
 }
 
 // Fills block_start for SUBS items per block; returns the number of blocks or -1.
@@ -303,6 +484,17 @@ long long plan_blocks(HybTable& tb, int subs) {
   }
   tb.block_start[tb.nb] = static_cast<int32_t>(blocks);
   return blocks;
+}
+
+template <int LPR>
+int launch_lean(HybTable& tb, const float* b, float* c, int feat, int all_atomic,
+                cudaStream_t stream) {
+  const long long blocks = plan_blocks(tb, kThreads / LPR);
+  if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
+  dim3 grid(static_cast<unsigned>(blocks), feat / (4 * LPR));
+  hyb_spmm_lean_kernel<LPR><<<grid, kThreads, 0, stream>>>(tb, b, c, feat, all_atomic);
+  SPTIR_LAUNCH_OK("hyb_spmm_lean_kernel");
+  return 0;
 }
 
 template <int LPR>
@@ -374,7 +566,8 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
     tb.nrows[k] = bk.nrows; tb.width[k] = bk.width;
   }
   const bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
-  plan_items(tb, item_slots(lanes_per_row(feat, vec4)));
+  const int lanes = lanes_per_row(feat, vec4, n);
+  plan_items(tb, item_slots(lanes));
 
   if (flags & SPARSETIR_HYB_ZERO_C) {
     SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(m) * feat * sizeof(float), st));
@@ -396,14 +589,18 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
   if (tb.nb == 0) return 0;
 
   if (vec4) {
-    // One lane per 16-byte vector; rows wider than 128 floats are covered feature tile by
-    // feature tile (blockIdx.y, the slowest grid dimension): a pass gathers from an
-    // n x 128-float slice of B, which is far more likely to stay resident in L2 while the pass
-    // runs than whole rows are.  Re-reading the index arrays once per tile costs little next to
-    // re-fetching B rows from HBM.
-    const int nv = feat / 4;
-    if (nv <= 8) return launch_async<8>(tb, b, c, feat, all_atomic, st);
-    if (nv <= 16) return launch_async<16>(tb, b, c, feat, all_atomic, st);
+    bool lean = feat % (4 * lanes) == 0 && static_cast<long long>(feat) * 4 < (1ll << 32);
+    for (int q = 0; q < tb.nb; ++q) {
+      const int w = tb.width[q];
+      lean = lean && (w == 1 || w == 2 || w == 4 || w % 8 == 0);
+    }
+    if (lean) {
+      if (lanes == 8) return launch_lean<8>(tb, b, c, feat, all_atomic, st);
+      if (lanes == 16) return launch_lean<16>(tb, b, c, feat, all_atomic, st);
+      return launch_lean<32>(tb, b, c, feat, all_atomic, st);
+    }
+    if (lanes == 8) return launch_async<8>(tb, b, c, feat, all_atomic, st);
+    if (lanes == 16) return launch_async<16>(tb, b, c, feat, all_atomic, st);
     return launch_async<32>(tb, b, c, feat, all_atomic, st);
   }
   if (feat <= 8) return launch<8, 1, 1>(tb, b, c, feat, all_atomic, st);

@@ -21,6 +21,7 @@
 //    in several arrays, which the kernel cannot see; the caller says so with
 //    SPARSETIR_HYB_ALL_ATOMIC.
 #include <algorithm>
+#include <cstdlib>
 #include <vector>
 
 #include "common.h"
@@ -465,7 +466,12 @@ int lanes_per_row(int feat, bool vec4, int n) {
   const int units = vec4 ? feat / 4 : feat;
   int lanes = units <= 8 ? 8 : (units <= 16 ? 16 : 32);
   if (vec4) {
-    const size_t l2_budget = 96u << 20;
+    // SPARSETIR_L2_BUDGET_MB overrides the default for tuning on other parts
+    static const size_t l2_budget = [] {
+      const char* e = std::getenv("SPARSETIR_L2_BUDGET_MB");
+      const long mb = e ? std::atol(e) : 0;
+      return static_cast<size_t>(mb > 0 ? mb : 48) << 20;
+    }();
     while (lanes > 8 && static_cast<size_t>(n) * lanes * 16 > l2_budget) lanes /= 2;
   }
   return lanes;

@@ -165,6 +165,7 @@ def ours_arm(args, rank, world, local_rank):
 
     from sparsetir_b200 import _lib as L
     from sparsetir_b200 import datagen as dg
+    from sparsetir_b200 import dist as sdist
     from sparsetir_b200 import format as fmt
     from sparsetir_b200 import ops
 
@@ -184,12 +185,9 @@ def ours_arm(args, rank, world, local_rank):
 
     # ---- workload: same seeded graph on every rank, row shard per rank
     g = dg.csr_powerlaw(seed=0)
-    cuts = fmt.row_partition(g.indptr, world)
-    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
-    ip = (g.indptr[r0:r1 + 1] - g.indptr[r0]).astype(np.int32)
-    ix = g.indices[g.indptr[r0]:g.indptr[r1]]
-    vals_csr = g.data[g.indptr[r0]:g.indptr[r1]]
-    m_loc, nnz_loc = r1 - r0, len(ix)
+    shard = sdist.shard_csr(g.indptr, g.indices, g.data, g.n, world, rank)
+    cuts, ip, ix, vals_csr = shard.cuts, shard.indptr, shard.indices, shard.data
+    m_loc, nnz_loc = shard.num_rows, shard.nnz
     parts = args.parts
     t0 = time.perf_counter()
     rows, cols, mask, vals, _ = fmt.column_part_hyb(m_loc, g.n, ip, ix, parts, BUCKETS, data=vals_csr)
@@ -298,8 +296,7 @@ def ours_arm(args, rank, world, local_rank):
                 x_dev[f].copy_(x_host[f], non_blocking=True)
             dist.broadcast(x_dev[f], src=0)
             calls[f]()
-            outs = list(torch.split(y_full[f], [r * f for r in shard_rows]))
-            dist.all_gather(outs, y_dev[f])
+            sdist.all_gather_rows(y_dev[f], shard_rows, f, out=y_full[f])
             if rank == 0:
                 y_host[f].copy_(y_full[f], non_blocking=True)
 

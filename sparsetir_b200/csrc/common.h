@@ -24,6 +24,14 @@ int use_device(int device_id);
 
 cudaStream_t stream_for(int device_id);
 
+// Scratch memory for kernels that need an intermediate buffer: one grow-only allocation per
+// (device, stream), kept until the library is unloaded, so that steady-state calls allocate
+// nothing.  Calls that use it on the same stream are ordered by the stream; calls on different
+// streams get different buffers.  Returns nullptr (after recording the error) when the device
+// cannot provide `bytes`.  Growing an existing buffer frees the old one, which synchronises the
+// device once.
+void* workspace(int device_id, cudaStream_t stream, size_t bytes);
+
 constexpr int kNumSMs = 148;  // B200
 
 inline int ceil_div(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }

@@ -20,6 +20,8 @@
 //            scattered with 16-byte vector atomics over contiguous addresses.
 // Tiles are numbered relation by relation; a block finds its (relation, tile) with a block-wide
 // prefix scan over the relation sizes, so no tile table has to be built or stored anywhere.
+#include <cstdlib>
+
 #include "common.h"
 #include "rgms_common.cuh"
 #include "spmm_core.cuh"
@@ -30,7 +32,7 @@ namespace sptir {
 int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,
                    const int32_t* indptr_i, const int32_t* indices_i, const int32_t* indptr_j,
                    const int32_t* indices_j, int num_rels, int feat, int nnz_i,
-                   cudaStream_t stream);
+                   const float* z, cudaStream_t stream);
 
 namespace {
 
@@ -175,7 +177,7 @@ extern "C" int sparsetir_rgms_raw(const float* a, const float* w, const float* x
                                   int num_rels, int feat, int nnz_i, int nnz_j, int device_id,
                                   void* stream) {
   using namespace sptir;
-  (void)m; (void)n;
+  (void)m;
   if (num_rels < 0 || feat < 0 || nnz_i < 0 || nnz_j < 0) return fail("sparsetir_rgms: negative size");
   if (nnz_i == 0 || feat == 0 || num_rels == 0) return 0;
   if (!w || !x || !y || !indptr_i || !indices_i || !indptr_j || (nnz_j > 0 && (!a || !indices_j)))
@@ -184,9 +186,27 @@ extern "C" int sparsetir_rgms_raw(const float* a, const float* w, const float* x
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool al = aligned16(x) && aligned16(y) && aligned16(w);
   if (al) {
-    int rc = rgms_tc_launch(a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, feat,
-                            nnz_i, st);
-    if (rc <= 0) return rc;
+    if (feat == 64) {
+      // Two launches: (1) Z = A_csf * X, one row per (relation, destination) pair, with the CSR
+      // SpMM kernel — thousands of independent short rows in flight instead of one latency chain
+      // per tile; (2) the tensor-core tile product and scatter, reading Z tiles with coalesced
+      // loads.  Z (nnz_i x 64 floats) lives in the library's per-stream scratch buffer.
+      // SPARSETIR_RGMS_FUSED=1 selects the single fused kernel instead (no scratch).
+      static const bool fused = [] {
+        const char* e = std::getenv("SPARSETIR_RGMS_FUSED");
+        return e != nullptr && e[0] == '1';
+      }();
+      float* z = nullptr;
+      if (!fused)
+        z = static_cast<float*>(workspace(device_id, st, static_cast<size_t>(nnz_i) * 64 * sizeof(float)));
+      if (z != nullptr) {
+        if (sparsetir_csrmm_raw(a, x, z, indptr_j, indices_j, nnz_i, n, 64, nnz_j, device_id, stream) != 0)
+          return -1;
+      }
+      int rc = rgms_tc_launch(a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, feat,
+                              nnz_i, z, st);
+      if (rc <= 0) return rc;
+    }
     if (feat == 32)
       return launch_tile<32>(a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, nnz_i, st);
     if (feat == 64)

@@ -47,7 +47,7 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
                const float* __restrict__ x, float* __restrict__ y,
                const int32_t* __restrict__ indptr_i, const int32_t* __restrict__ indices_i,
                const int32_t* __restrict__ indptr_j, const int32_t* __restrict__ indices_j,
-               int num_rels) {
+               int num_rels, const float* __restrict__ z) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t bar_done;
   __shared__ uint32_t s_tmem;
@@ -79,7 +79,23 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
     *reinterpret_cast<float4*>(w_lo + off) = l;
   }
 
-  // phase 1: gather-aggregate; lane = kc (its 4 features are one core-matrix row chunk)
+  // phase 1, two-kernel form: the aggregated rows were written to `z` by a CSR SpMM launch that
+  // ran before this kernel; the tile's rows are contiguous there, so they are read with fully
+  // coalesced 16-byte loads (chunk = (row t, kc)) and split on the way to shared memory
+  if (z != nullptr) {
+    const float4* zt = reinterpret_cast<const float4*>(z + static_cast<size_t>(row0) * kF);
+    for (int ch = tid; ch < kTM * kLPR; ch += kRgmsThreads) {
+      const int t = ch / kLPR, kc = ch % kLPR;
+      const float4 v = t < nrows ? __ldg(zt + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+      const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+      const int off = (kc * (kTM / 8) + (t >> 3)) * 128 + (t & 7) * 16;
+      *reinterpret_cast<float4*>(z_hi + off) = h;
+      *reinterpret_cast<float4*>(z_lo + off) = l;
+    }
+  } else
+  // phase 1, fused form: gather-aggregate here; lane = kc (its 4 features are one core-matrix
+  // row chunk)
   {
     const int lane = tid % kLPR;
     gather_tile_rows<kF, kTM>(a, x, indptr_j, indices_j, row0, nrows, [&](int t, float4 v) {
@@ -141,10 +157,11 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
 }  // namespace
 
 // Returns 0 when launched, 1 when the shape is not handled here, -1 on error.
+// z: rows already aggregated by a preceding launch (two-kernel form), or nullptr (fused form).
 int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,
                    const int32_t* indptr_i, const int32_t* indices_i, const int32_t* indptr_j,
                    const int32_t* indices_j, int num_rels, int feat, int nnz_i,
-                   cudaStream_t stream) {
+                   const float* z, cudaStream_t stream) {
   if (feat != kF) return 1;
   static thread_local int configured_device = -1;
   int dev = 0;
@@ -157,7 +174,7 @@ int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,
   // upper bound on the number of tiles: every relation can add one partly filled tile
   const long long blocks = static_cast<long long>(nnz_i) / kTM + num_rels;
   rgms_tc_kernel<<<static_cast<unsigned>(blocks), kRgmsThreads, kSmemBytes, stream>>>(
-      a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels);
+      a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, z);
   SPTIR_LAUNCH_OK("rgms_tc_kernel");
   return 0;
 }

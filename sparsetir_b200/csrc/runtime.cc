@@ -1,7 +1,10 @@
 // Error string, stream table and device selection.
 #include <atomic>
 #include <cstring>
+#include <map>
+#include <mutex>
 #include <string>
+#include <utility>
 
 #include "common.h"
 
@@ -33,6 +36,37 @@ int use_device(int device_id) {
 cudaStream_t stream_for(int device_id) {
   if (device_id < 0 || device_id >= kMaxDevices) return nullptr;
   return static_cast<cudaStream_t>(g_streams[device_id].load(std::memory_order_acquire));
+}
+
+namespace {
+struct Scratch {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+};
+std::mutex g_ws_mutex;
+std::map<std::pair<int, cudaStream_t>, Scratch> g_ws;
+}  // namespace
+
+void* workspace(int device_id, cudaStream_t stream, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_ws_mutex);
+  Scratch& s = g_ws[{device_id, stream}];
+  if (s.bytes >= bytes && s.ptr != nullptr) return s.ptr;
+  if (s.ptr != nullptr) {
+    cudaFree(s.ptr);  // synchronises: nothing in flight can still use the old buffer
+    s.ptr = nullptr;
+    s.bytes = 0;
+  }
+  const size_t want = (bytes + (size_t{1} << 20) - 1) & ~((size_t{1} << 20) - 1);
+  void* p = nullptr;
+  const cudaError_t err = cudaMalloc(&p, want);
+  if (err != cudaSuccess) {
+    cudaGetLastError();  // clear the sticky-free error state of the failed allocation
+    fail("workspace of %zu bytes: %s", want, cudaGetErrorString(err));
+    return nullptr;
+  }
+  s.ptr = p;
+  s.bytes = want;
+  return p;
 }
 
 }  // namespace sptir

@@ -9,10 +9,12 @@
 // columns = two tcgen05.mma.kind::f16 of K = 16.  The feature-contiguous B rows are an MN-major
 // operand, the row-major A block a K-major operand; neither needs a transpose in memory.
 //
-// Pipeline: 4 shared-memory stages; all 128 threads copy the next block's operands with
-// cp.async straight into the un-swizzled core-matrix layout the tensor core reads
-// (tc05.cuh), one elected thread issues the MMAs, tcgen05.commit arrives on the stage's
-// mbarrier when the tensor core has finished reading it.  Epilogue: TMEM -> registers
+// Pipeline: 6 shared-memory stages, operands of 4 blocks in flight; all 128 threads copy a
+// block's operands with cp.async straight into the un-swizzled core-matrix layout the tensor
+// core reads (tc05.cuh), one elected thread issues the MMAs, tcgen05.commit arrives on the
+// stage's mbarrier when the tensor core has finished reading it.  A stage is refilled two
+// blocks after it was multiplied, so the wait for "tensor core done with it" is normally over
+// before it starts and the loop never stalls on MMA latency.  Epilogue: TMEM -> registers
 // (lane = feature, 32 columns = 32 block rows) -> 32 coalesced row stores per warp.
 // Every mbarrier wait is bounded; a timeout is counted in a device-side status word and the block
 // gives up cleanly (TMEM freed), so a protocol error cannot hang the GPU.
@@ -32,11 +34,13 @@ namespace {
 constexpr int kThreads = 128;
 constexpr int kBlk = 32;
 constexpr int kTileF = 128;
-constexpr int kStages = 4;
+constexpr int kStages = 6;
+constexpr int kAhead = kStages - 2;  // blocks in flight ahead of the one being multiplied
 constexpr int kBBytes = kBlk * kTileF * 2;  // B tile of one block: 32 x 128 fp16 = 8 KB
 constexpr int kABytes = kBlk * kBlk * 2;    // A block: 2 KB
 constexpr int kStageBytes = kBBytes + kABytes;
 constexpr uint32_t kTmemCols = 32;
+constexpr int kColCache = 256;
 
 // B tile stage layout (MN-major operand): core matrix (kc = bj/8, fc = f/8) at (kc*16+fc)*128,
 // inside it K-step bj%8 at 16-byte stride, 8 features contiguous.
@@ -54,6 +58,8 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
   __shared__ __align__(8) uint64_t bar_free[kStages];  // stage may be overwritten
   __shared__ __align__(8) uint64_t bar_done;           // all MMAs of the row have finished
   __shared__ uint32_t s_tmem;
+  __shared__ int32_t s_cols[kColCache];  // block columns of the row: keeps a dependent global
+                                         // load out of every pipeline step
   const int i = blockIdx.x;
   const int f0 = blockIdx.y * kTileF;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -72,6 +78,7 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
     tc05::fence_mbar_init();
   }
   if (warp == 0) tc05::tmem_alloc(&s_tmem, kTmemCols);
+  for (int t = tid; t < min(nblk, kColCache); t += kThreads) s_cols[t] = __ldg(indices + p0 + t);
   tc05::fence_before_sync();
   __syncthreads();
   tc05::fence_after_sync();
@@ -83,7 +90,7 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
   auto load_stage = [&](int it) {
     unsigned char* st = smem + (it % kStages) * kStageBytes;
     const int p = p0 + it;
-    const size_t brow0 = static_cast<size_t>(__ldg(indices + p)) * kBlk;
+    const size_t brow0 = static_cast<size_t>(it < kColCache ? s_cols[it] : __ldg(indices + p)) * kBlk;
 #pragma unroll
     for (int kc = 0; kc < 4; ++kc) {
       const __half* src = b + (brow0 + kc * 8 + b_bjlo) * feat + f0 + b_fc * 8;
@@ -96,14 +103,14 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
   constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtF16, kTileF, kBlk, /*a_mn=*/1, /*b_mn=*/0);
   bool ok = true;
 
-  // prologue: blocks 0 .. kStages-2 in flight
+  // prologue: blocks 0 .. kAhead-1 in flight
 #pragma unroll
-  for (int it = 0; it < kStages - 1; ++it) {
+  for (int it = 0; it < kAhead; ++it) {
     if (it < nblk) load_stage(it);
     cp_async_commit();
   }
   for (int it = 0; it < nblk; ++it) {
-    cp_async_wait<kStages - 2>();  // block `it` has landed (for this thread's copies)
+    cp_async_wait<kAhead - 1>();  // block `it` has landed (for this thread's copies)
     tc05::fence_async_smem();
     __syncthreads();               // ... and for everybody's
     if (warp == 0 && lane == 0) {
@@ -119,12 +126,12 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
       tc05::mma_commit(&bar_free[it % kStages]);
       if (it == nblk - 1) tc05::mma_commit(&bar_done);
     }
-    // refill the stage that block it-1 used with block it+kStages-1
-    const int nxt = it + kStages - 1;
+    // refill the stage that block it-2 used with block it+kAhead (same stage modulo kStages)
+    const int nxt = it + kAhead;
     if (nxt < nblk) {
-      if (it >= 1) {
-        // the MMAs of block it-1 are the ((it-1)/kStages)-th use of that stage
-        if (!tc05::mbar_wait(&bar_free[(it - 1) % kStages], ((it - 1) / kStages) & 1)) ok = false;
+      if (it >= 2) {
+        // the MMAs of block it-2 are the ((it-2)/kStages)-th use of that stage
+        if (!tc05::mbar_wait(&bar_free[(it - 2) % kStages], ((it - 2) / kStages) & 1)) ok = false;
       }
       if (__syncthreads_or(!ok)) { ok = false; break; }
       load_stage(nxt);

@@ -33,10 +33,21 @@ constexpr int kLPR = kF / 4;                   // 16 lanes cover a feature row
 constexpr int kZBytes = kTM * kF * 4;          // 32 KB per Z part
 constexpr int kWBytes = kF * kF * 4;           // 16 KB per W part
 constexpr size_t kSmemBytes = 2 * kZBytes + 2 * kWBytes;
-// K-major operands, no swizzle: core matrix (kc = fi/4, g = row/8) at (kc*groups + g)*128,
-// row%8 at 16-byte stride inside it, 4 floats of K contiguous.
-constexpr uint32_t kZ_SBO = 128, kZ_LBO = (kTM / 8) * 128;  // 16 row groups
-constexpr uint32_t kW_SBO = 128, kW_LBO = (kF / 8) * 128;   // 8 row groups
+// K-major operands, no swizzle: core matrix (g = row/8, kc = fi/4) at (g*16 + kc)*128, row%8
+// at 16-byte stride inside it, 4 floats of K contiguous.  With the 16 K-chunks of a row group
+// adjacent, a warp that copies 8 rows x 4 chunks reads 64 contiguous bytes per row from global
+// memory and writes 512 contiguous bytes of shared memory: coalesced and bank-conflict free.
+constexpr uint32_t kZ_LBO = 128, kZ_SBO = kLPR * 128;  // next K chunk / next 8 rows
+constexpr uint32_t kW_LBO = 128, kW_SBO = kLPR * 128;
+__device__ __forceinline__ int core_off(int row, int kc) {
+  return ((row >> 3) * kLPR + kc) * 128 + (row & 7) * 16;
+}
+// chunk index -> (row, kc) such that the 32 lanes of a warp cover 8 rows x 4 K-chunks
+__device__ __forceinline__ void chunk_of(int ch, int* row, int* kc) {
+  const int lane = ch & 31, blk = ch >> 5;       // blk: (row group, quarter of the K chunks)
+  *row = (blk >> 2) * 8 + (lane & 7);
+  *kc = (blk & 3) * 4 + (lane >> 3);
+}
 
 __device__ __forceinline__ float tf32_hi(float x) {
   return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);  // what the tensor core keeps
@@ -70,11 +81,12 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
   // W_r[fo, fi] -> core matrices, split hi/lo.  One 16-byte chunk = (fo, kc = fi/4).
   const float4* wr = reinterpret_cast<const float4*>(w + static_cast<size_t>(rel) * kF * kF);
   for (int ch = tid; ch < kF * kF / 4; ch += kRgmsThreads) {
-    const int fo = ch / (kF / 4), kc = ch % (kF / 4);
-    const float4 v = __ldg(wr + ch);
+    int fo, kc;
+    chunk_of(ch, &fo, &kc);
+    const float4 v = __ldg(wr + fo * kLPR + kc);
     const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
     const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
-    const int off = (kc * (kF / 8) + (fo >> 3)) * 128 + (fo & 7) * 16;
+    const int off = core_off(fo, kc);
     *reinterpret_cast<float4*>(w_hi + off) = h;
     *reinterpret_cast<float4*>(w_lo + off) = l;
   }
@@ -85,11 +97,12 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
   if (z != nullptr) {
     const float4* zt = reinterpret_cast<const float4*>(z + static_cast<size_t>(row0) * kF);
     for (int ch = tid; ch < kTM * kLPR; ch += kRgmsThreads) {
-      const int t = ch / kLPR, kc = ch % kLPR;
-      const float4 v = t < nrows ? __ldg(zt + ch) : make_float4(0.f, 0.f, 0.f, 0.f);
+      int t, kc;
+      chunk_of(ch, &t, &kc);
+      const float4 v = t < nrows ? __ldg(zt + t * kLPR + kc) : make_float4(0.f, 0.f, 0.f, 0.f);
       const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
       const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
-      const int off = (kc * (kTM / 8) + (t >> 3)) * 128 + (t & 7) * 16;
+      const int off = core_off(t, kc);
       *reinterpret_cast<float4*>(z_hi + off) = h;
       *reinterpret_cast<float4*>(z_lo + off) = l;
     }
@@ -101,7 +114,7 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
     gather_tile_rows<kF, kTM>(a, x, indptr_j, indices_j, row0, nrows, [&](int t, float4 v) {
       const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
       const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
-      const int off = (lane * (kTM / 8) + (t >> 3)) * 128 + (t & 7) * 16;
+      const int off = core_off(t, lane);
       *reinterpret_cast<float4*>(z_hi + off) = h;
       *reinterpret_cast<float4*>(z_lo + off) = l;
     });

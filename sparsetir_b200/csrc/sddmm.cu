@@ -72,7 +72,51 @@ sddmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __
 #pragma unroll
   for (int v = 0; v < VPL; ++v) arow[v] = Vec<VEC>::zero();
 
+  int warp_end = __ldg(indptr + warp_row + 1);  // first position past the warp's current row
   for (int base = static_cast<int>(e_begin); base < e_end; base += 32) {
+    if (base + 32 <= min(warp_end, e_end)) {
+      // Fast path: all 32 positions belong to the warp's current row (the common case when rows
+      // are longer than a batch) — no row lookup, no per-position row bookkeeping.
+      const int col = __ldg(indices + base + wlane);
+      if (cur_row != warp_row) {
+        cur_row = warp_row;
+        const V* src = av + static_cast<size_t>(cur_row) * row_vecs;
+#pragma unroll
+        for (int v = 0; v < VPL; ++v) arow[v] = valid[v] ? __ldg(src + off[v]) : Vec<VEC>::zero();
+      }
+      float part[LPR];
+#pragma unroll
+      for (int k0 = 0; k0 < LPR; k0 += U) {
+        V x[U][VPL];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const V* src = bv + static_cast<size_t>(__shfl_sync(mask, col, k0 + u, LPR)) * row_vecs;
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) x[u][v] = valid[v] ? __ldg(src + off[v]) : Vec<VEC>::zero();
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          float s = 0.f;
+#pragma unroll
+          for (int v = 0; v < VPL; ++v) s = Vec<VEC>::dot(arow[v], x[u][v], s);
+          part[k0 + u] = s;
+        }
+      }
+#pragma unroll
+      for (int offl = LPR / 2, n = LPR; offl >= 1; offl >>= 1, n >>= 1) {
+        const bool upper = (lane & offl) != 0;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+          float send = upper ? part[i] : part[i + n / 2];
+          float keep = upper ? part[i + n / 2] : part[i];
+          part[i] = keep + __shfl_xor_sync(mask, send, offl, LPR);
+        }
+      }
+      float r = part[0];
+      if (scale != nullptr) r *= __ldg(scale + base + wlane);
+      c[base + wlane] = r;
+      continue;
+    }
     const int e = base + wlane;
     const bool live = e < e_end;
     int col = 0, row = warp_row;
@@ -90,6 +134,7 @@ sddmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __
     }
     // the next batch starts from the row of this batch's last live position
     warp_row = __shfl_sync(0xffffffffu, row, min(31, e_end - 1 - base));
+    warp_end = __ldg(indptr + warp_row + 1);
 
     const int cnt = min(LPR, e_end - (base + sub * LPR));  // live positions of this sub-warp (may be <= 0)
     float part[LPR];

@@ -207,6 +207,20 @@ SPARSETIR_API int sparsetir_rgms_raw(const float* a, const float* w, const float
                                      int n, int num_rels, int feat, int nnz_i, int nnz_j,
                                      int device_id, void* stream);
 
+/* RGMS that never allocates device memory.  No counterpart in the reference: it exists for
+ * hosts that may not call the CUDA allocator when they need the operator (loops that forbid
+ * allocation after start-up; processes whose device memory belongs to another pool).
+ * Same arguments and result as sparsetir_rgms_raw, but the intermediate of the two-launch form
+ * lives in a fixed 32 MiB array inside the library instead of an allocated scratch buffer:
+ *   - feat must be 64 and nnz_i at most 131072; anything else is refused with an error;
+ *   - all calls on one device share that array: calls that overlap on the GPU race, order them;
+ *   - the first call on a device fetches the array's address; make it before any stream capture. */
+SPARSETIR_API int sparsetir_rgms_noalloc(const float* a, const float* w, const float* x, float* y,
+                                         const int32_t* indptr_i, const int32_t* indices_i,
+                                         const int32_t* indptr_j, const int32_t* indices_j, int m,
+                                         int n, int num_rels, int feat, int nnz_i, int nnz_j,
+                                         int device_id, void* stream);
+
 /* ---- host-side format conversion (CPU int32 arrays) ----------------------------------- */
 
 /* Column partitioning + ELL bucketing of a CSR matrix, bit-exact with ColumnPartHyb

@@ -90,6 +90,7 @@ PLAIN_SYMBOLS = {
     "sparsetir_sddmm_edge_to_row_raw": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "sparsetir_bsrmm_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_raw": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),
+    "sparsetir_rgms_noalloc": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),
     "sparsetir_column_part_hyb": (_vp, [_i, _i, _i32p, _i32p, _i, _i32p, _i, _i]),
     "sparsetir_hyb_num_rows": (_i64, [_vp, _i, _i]),
     "sparsetir_hyb_copy_bucket": (_i, [_vp, _i, _i, _i32p, _i32p, _i32p, _i32p, _f32p, _f32p]),

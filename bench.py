@@ -229,10 +229,36 @@ def ours_arm(args, rank, world, local_rank):
     stop.record()
     barrier()
     ms_total = start.elapsed_time(stop)
+
+    # The same K steps replayed from a CUDA graph (the calls neither allocate nor synchronise,
+    # so a step can be captured): takes the per-launch host work out of the measurement.
+    graph_ms = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step()
+        torch.cuda.current_stream().wait_stream(side)
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            step()
+        for _ in range(3):
+            cg.replay()
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(args.steps):
+            cg.replay()
+        g1.record()
+        barrier()
+        graph_ms = g0.elapsed_time(g1) / args.steps
+    except Exception as exc:  # capture is an extra; the eager number stands on its own
+        log(f"bench.py: graph replay skipped: {exc!r}")
     if args.kernels_only:  # short run for profilers: no clock sampling tail, e2e, CPU or ops legs
         if rank == 0:
             sampler.stop()
             print(json.dumps({"kernels_only": True, "ms_per_step": ms_total / args.steps,
+                              "graph_replay_ms_per_step": graph_ms,
                               "per_feat_ms": {str(f): statistics.mean(a.elapsed_time(b) for a, b in events[f])
                                               for f in FEATS}}), flush=True)
         return
@@ -379,6 +405,7 @@ def ours_arm(args, rank, world, local_rank):
                 "includes": "H2D of X, kernels, D2H of Y" + (", NCCL broadcast of X and all-gather of Y" if world > 1 else "")},
         "gpu_launches": launches_per_call * len(FEATS) * args.steps,
         "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "per_feat": per_f,
+        "graph_replay_ms_per_step": graph_ms,
         "alg_gbs": sum(spmm_bytes(m_loc, g.n, nnz_loc, f) for f in FEATS) / (ms_step * 1e-3) / 1e9,
     }
     if args.ops and world == 1:

@@ -15,6 +15,95 @@ namespace {
 
 constexpr int kThreads = 256;
 
+// ---------------------------------------------------------------------------------------------
+// Lean kernel: fast path for 16-byte aligned operands and whole feature tiles.
+// A sub-warp of LPR lanes owns `rpi` consecutive rows (rpi < LPR).  Short rows are the hard
+// case for CSR: row pointer -> ids -> dense rows is a chain of three dependent memory round
+// trips, and a row of two or three entries gives nothing to overlap them with.  So the chain is
+// paid once per ITEM, not per row: the rpi+1 row pointers are read with one coalesced load and
+// kept in registers (lane j holds indptr[r0+j], fetched by shuffle at row ends), the item's
+// entries are one contiguous slot stream whose ids/values are read a batch of LPR ahead, and the
+// dense rows are gathered 8 at a time.  One writer per output row, CSR summation order, rows
+// without entries written as zeros.
+template <int LPR>
+__global__ void __launch_bounds__(kThreads, 4)
+csrmm_lean_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                  const int32_t* __restrict__ indptr, const int32_t* __restrict__ indices, int m,
+                  int feat, int rpi) {
+  constexpr int SUBS = kThreads / LPR;
+  constexpr int U = 8;
+  const int lane = threadIdx.x % LPR;
+  const unsigned mask = group_mask<LPR>();
+  const long long item = static_cast<long long>(blockIdx.x) * SUBS + threadIdx.x / LPR;
+  const long long r0l = item * rpi;
+  if (r0l >= m) return;
+  const int r0 = static_cast<int>(r0l);
+  const int nr = min(rpi, m - r0);
+  const int ptr = __ldg(indptr + r0 + min(lane, nr));  // lane j: start of row r0+j (j <= nr)
+  const int p0 = __shfl_sync(mask, ptr, 0, LPR);
+  const int nslots = __shfl_sync(mask, ptr, nr, LPR) - p0;
+  const unsigned row_bytes = static_cast<unsigned>(feat) * 4u;
+  const int off = blockIdx.y * LPR + lane;
+  const char* bl = reinterpret_cast<const char*>(reinterpret_cast<const float4*>(b) + off);
+  char* cl = reinterpret_cast<char*>(reinterpret_cast<float4*>(c) + off) +
+             static_cast<unsigned long long>(static_cast<unsigned>(r0)) * row_bytes;
+  const int32_t* cols = indices + p0;
+  const float* wts = a + p0;
+
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  int j = 0;                                        // row of the item being accumulated
+  int row_end = __shfl_sync(mask, ptr, 1, LPR) - p0;  // its end, as a slot number
+  int s = 0;                                        // slots consumed so far
+  auto finish_rows = [&]() {  // store every row whose last entry has been consumed
+    while (j < nr && s >= row_end) {
+      __stcs(reinterpret_cast<float4*>(cl), acc);  // written once: keep B rows in L2
+      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      cl += row_bytes;
+      ++j;
+      row_end = __shfl_sync(mask, ptr, min(j + 1, nr), LPR) - p0;
+    }
+  };
+  finish_rows();  // rows without entries at the front
+
+  int cid = 0, cidn = 0;
+  float av = 0.f, avn = 0.f;
+  if (lane < nslots) {
+    cid = __ldg(cols + lane);
+    av = __ldg(wts + lane);
+  }
+  for (int s0 = 0; s0 < nslots; s0 += LPR) {
+    cidn = 0;
+    avn = 0.f;
+    if (s0 + LPR + lane < nslots) {  // ids and values of the next batch
+      cidn = __ldg(cols + s0 + LPR + lane);
+      avn = __ldg(wts + s0 + LPR + lane);
+    }
+    const int cnt = min(LPR, nslots - s0);
+#pragma unroll
+    for (int k0 = 0; k0 < LPR; k0 += U) {
+      if (k0 < cnt) {
+        float4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {  // slots past the end ask for column 0: never consumed
+          const unsigned col = static_cast<unsigned>(__shfl_sync(mask, cid, k0 + u, LPR));
+          x[u] = __ldg(reinterpret_cast<const float4*>(bl + static_cast<unsigned long long>(col) * row_bytes));
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const float ak = __shfl_sync(mask, av, k0 + u, LPR);
+          if (k0 + u < cnt) {
+            Vec<4>::fma(acc, ak, x[u]);
+            ++s;
+            if (s >= row_end) finish_rows();
+          }
+        }
+      }
+    }
+    cid = cidn;
+    av = avn;
+  }
+}
+
 template <int LPR, int VPL, int VEC>
 __global__ void __launch_bounds__(kThreads)
 csrmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
@@ -98,6 +187,33 @@ extern "C" int sparsetir_csrmm_raw(const float* a, const float* b, float* c, con
   if (use_device(device_id) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
+  if (vec4 && static_cast<long long>(feat) * 4 < (1ll << 32) &&
+      static_cast<long long>(m) * feat * 4 < (1ll << 32) * 1024) {
+    // lanes per row: one per 16-byte vector, narrowed until the n x tile slice of B that a pass
+    // over the rows gathers from fits the resident part of L2 (see hyb_spmm.cu)
+    const int nv = feat / 4;
+    int lanes = nv <= 8 ? 8 : (nv <= 16 ? 16 : 32);
+    const size_t l2_budget = 48u << 20;
+    while (lanes > 8 && static_cast<size_t>(n) * lanes * 16 > l2_budget) lanes /= 2;
+    if (feat % (4 * lanes) == 0) {
+      const int subs = kThreads / lanes;
+      // about four id batches per item, but never so few items that SMs sit idle
+      const double avg = m > 0 ? static_cast<double>(nnz) / m : 0.0;
+      int rpi = static_cast<int>(4.0 * lanes / (avg > 1.0 ? avg : 1.0));
+      rpi = rpi < 1 ? 1 : (rpi > lanes - 1 ? lanes - 1 : rpi);
+      const long long want_items = 4ll * kNumSMs * 4 * subs;
+      while (rpi > 1 && (m + rpi - 1) / rpi < want_items) rpi /= 2;
+      dim3 grid(ceil_div(ceil_div(m, rpi), subs), feat / (4 * lanes));
+      if (lanes == 8)
+        csrmm_lean_kernel<8><<<grid, kThreads, 0, st>>>(a, b, c, indptr, indices, m, feat, rpi);
+      else if (lanes == 16)
+        csrmm_lean_kernel<16><<<grid, kThreads, 0, st>>>(a, b, c, indptr, indices, m, feat, rpi);
+      else
+        csrmm_lean_kernel<32><<<grid, kThreads, 0, st>>>(a, b, c, indptr, indices, m, feat, rpi);
+      SPTIR_LAUNCH_OK("csrmm_lean_kernel");
+      return 0;
+    }
+  }
   if (vec4) {
     const int nv = feat / 4;
     if (nv <= 8) return launch<8, 1, 4>(a, b, c, indptr, indices, m, feat, st);

@@ -53,12 +53,17 @@ __device__ __forceinline__ float tf32_hi(float x) {
   return __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);  // what the tensor core keeps
 }
 
+// Persistent form: a block walks `tiles_per_cta` consecutive tiles.  Tiles are numbered relation
+// by relation, so consecutive tiles mostly share the relation: W_r is staged once per change of
+// relation, the first tile is found with the block-wide scan and the following ones by stepping
+// through indptr_i, TMEM and the mbarrier are set up once, and (two-launch form) the next tile's
+// Z rows are already on their way into registers while the tensor core works on this one.
 __global__ void __launch_bounds__(kRgmsThreads)
 rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
                const float* __restrict__ x, float* __restrict__ y,
                const int32_t* __restrict__ indptr_i, const int32_t* __restrict__ indices_i,
                const int32_t* __restrict__ indptr_j, const int32_t* __restrict__ indices_j,
-               int num_rels, const float* __restrict__ z) {
+               int num_rels, const float* __restrict__ z, int tiles_per_cta) {
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(8) uint64_t bar_done;
   __shared__ uint32_t s_tmem;
@@ -66,10 +71,10 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
   unsigned char* z_lo = smem + kZBytes;
   unsigned char* w_hi = smem + 2 * kZBytes;
   unsigned char* w_lo = w_hi + kWBytes;
+  constexpr int kZPerThread = kTM * kLPR / kRgmsThreads;  // 16-byte chunks of a Z tile per thread
 
   int rel, row0, row1;
-  if (!locate_tile(indptr_i, num_rels, kTM, blockIdx.x, &rel, &row0, &row1)) return;
-  const int nrows = row1 - row0;
+  if (!locate_tile(indptr_i, num_rels, kTM, blockIdx.x * tiles_per_cta, &rel, &row0, &row1)) return;
   const int tid = threadIdx.x, warp = tid >> 5, lane32 = tid & 31;
 
   if (tid == 0) {
@@ -77,91 +82,132 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
     tc05::fence_mbar_init();
   }
   if (warp == 0) tc05::tmem_alloc(&s_tmem, kF);
-
-  // W_r[fo, fi] -> core matrices, split hi/lo.  One 16-byte chunk = (fo, kc = fi/4).
-  const float4* wr = reinterpret_cast<const float4*>(w + static_cast<size_t>(rel) * kF * kF);
-  for (int ch = tid; ch < kF * kF / 4; ch += kRgmsThreads) {
-    int fo, kc;
-    chunk_of(ch, &fo, &kc);
-    const float4 v = __ldg(wr + fo * kLPR + kc);
-    const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
-    const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
-    const int off = core_off(fo, kc);
-    *reinterpret_cast<float4*>(w_hi + off) = h;
-    *reinterpret_cast<float4*>(w_lo + off) = l;
-  }
-
-  // phase 1, two-kernel form: the aggregated rows were written to `z` by a CSR SpMM launch that
-  // ran before this kernel; the tile's rows are contiguous there, so they are read with fully
-  // coalesced 16-byte loads (chunk = (row t, kc)) and split on the way to shared memory
-  if (z != nullptr) {
-    const float4* zt = reinterpret_cast<const float4*>(z + static_cast<size_t>(row0) * kF);
-    for (int ch = tid; ch < kTM * kLPR; ch += kRgmsThreads) {
-      int t, kc;
-      chunk_of(ch, &t, &kc);
-      const float4 v = t < nrows ? __ldg(zt + t * kLPR + kc) : make_float4(0.f, 0.f, 0.f, 0.f);
-      const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
-      const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
-      const int off = core_off(t, kc);
-      *reinterpret_cast<float4*>(z_hi + off) = h;
-      *reinterpret_cast<float4*>(z_lo + off) = l;
-    }
-  } else
-  // phase 1, fused form: gather-aggregate here; lane = kc (its 4 features are one core-matrix
-  // row chunk)
-  {
-    const int lane = tid % kLPR;
-    gather_tile_rows<kF, kTM>(a, x, indptr_j, indices_j, row0, nrows, [&](int t, float4 v) {
-      const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
-      const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
-      const int off = core_off(t, lane);
-      *reinterpret_cast<float4*>(z_hi + off) = h;
-      *reinterpret_cast<float4*>(z_lo + off) = l;
-    });
-  }
-  tc05::fence_async_smem();   // shared-memory writes above -> visible to the tensor core
   tc05::fence_before_sync();
   __syncthreads();
   tc05::fence_after_sync();
   const uint32_t tmem = s_tmem;
 
-  // phase 2: one thread issues 8 K-steps x 3 products
-  if (tid == 0) {
-    constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtTF32, kTM, kF, /*a_mn=*/0, /*b_mn=*/0);
-    const uint32_t zh = tc05::smem_u32(z_hi), zl = tc05::smem_u32(z_lo);
-    const uint32_t wh = tc05::smem_u32(w_hi), wl = tc05::smem_u32(w_lo);
+  // this thread's chunks of a Z tile, fetched ahead of use (two-launch form)
+  float4 zreg[kZPerThread];
+  auto fetch_z = [&](int r0, int nr) {
+    const float4* zt = reinterpret_cast<const float4*>(z + static_cast<size_t>(r0) * kF);
 #pragma unroll
-    for (int ks = 0; ks < kF / 8; ++ks) {  // K = 8 floats = two core matrices per step
-      const uint64_t dzh = tc05::smem_desc(zh + ks * 2 * kZ_LBO, kZ_LBO, kZ_SBO);
-      const uint64_t dzl = tc05::smem_desc(zl + ks * 2 * kZ_LBO, kZ_LBO, kZ_SBO);
-      const uint64_t dwh = tc05::smem_desc(wh + ks * 2 * kW_LBO, kW_LBO, kW_SBO);
-      const uint64_t dwl = tc05::smem_desc(wl + ks * 2 * kW_LBO, kW_LBO, kW_SBO);
-      tc05::mma_tf32(tmem, dzl, dwh, idesc, ks > 0 ? 1u : 0u);  // small terms first
-      tc05::mma_tf32(tmem, dzh, dwl, idesc, 1u);
-      tc05::mma_tf32(tmem, dzh, dwh, idesc, 1u);
+    for (int k = 0; k < kZPerThread; ++k) {
+      int t, kc;
+      chunk_of(tid + k * kRgmsThreads, &t, &kc);
+      zreg[k] = t < nr ? __ldg(zt + t * kLPR + kc) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
-    tc05::mma_commit(&bar_done);
-  }
-  bool ok = tc05::mbar_wait(&bar_done, 0);
-  ok = !__syncthreads_or(!ok);
-  tc05::fence_after_sync();
+  };
+  if (z != nullptr) fetch_z(row0, row1 - row0);
 
-  // phase 3: warps w and w+4 share TMEM lanes 32*(w%4)..+31 and take 32 columns each
-  if (ok) {
-    const int t = (warp & 3) * 32 + lane32;
-    const int col0 = (warp >> 2) * 32;
-    uint32_t r[32];
-    tc05::tmem_ld32(tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + col0, r);
-    if (t < nrows) {
-      float4* dst = reinterpret_cast<float4*>(y + static_cast<size_t>(__ldg(indices_i + row0 + t)) * kF + col0);
-#pragma unroll
-      for (int k = 0; k < 8; ++k)
-        atomicAdd(dst + k, make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]),
-                                       __uint_as_float(r[4 * k + 2]), __uint_as_float(r[4 * k + 3])));
+  int staged_rel = -1;
+  uint32_t parity = 0;
+  bool ok = true;
+  for (int it = 0; it < tiles_per_cta; ++it) {
+    const int nrows = row1 - row0;
+    // W_r[fo, fi] -> core matrices, split hi/lo, when the relation changed
+    if (rel != staged_rel) {
+      staged_rel = rel;
+      const float4* wr = reinterpret_cast<const float4*>(w + static_cast<size_t>(rel) * kF * kF);
+      for (int ch = tid; ch < kF * kF / 4; ch += kRgmsThreads) {
+        int fo, kc;
+        chunk_of(ch, &fo, &kc);
+        const float4 v = __ldg(wr + fo * kLPR + kc);
+        const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+        const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+        const int off = core_off(fo, kc);
+        *reinterpret_cast<float4*>(w_hi + off) = h;
+        *reinterpret_cast<float4*>(w_lo + off) = l;
+      }
     }
-  } else if (tid == 0) {
-    atomicAdd(&g_rgms_tc_timeouts, 1u);
+    // phase 1: the tile's aggregated rows -> shared memory, split hi/lo
+    if (z != nullptr) {
+#pragma unroll
+      for (int k = 0; k < kZPerThread; ++k) {
+        int t, kc;
+        chunk_of(tid + k * kRgmsThreads, &t, &kc);
+        const float4 v = zreg[k];
+        const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+        const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+        const int off = core_off(t, kc);
+        *reinterpret_cast<float4*>(z_hi + off) = h;
+        *reinterpret_cast<float4*>(z_lo + off) = l;
+      }
+    } else {  // fused form: gather-aggregate here; lane = kc
+      const int lane = tid % kLPR;
+      gather_tile_rows<kF, kTM>(a, x, indptr_j, indices_j, row0, nrows, [&](int t, float4 v) {
+        const float4 h = make_float4(tf32_hi(v.x), tf32_hi(v.y), tf32_hi(v.z), tf32_hi(v.w));
+        const float4 l = make_float4(v.x - h.x, v.y - h.y, v.z - h.z, v.w - h.w);
+        const int off = core_off(t, lane);
+        *reinterpret_cast<float4*>(z_hi + off) = h;
+        *reinterpret_cast<float4*>(z_lo + off) = l;
+      });
+    }
+    tc05::fence_async_smem();  // shared-memory writes above -> visible to the tensor core
+    tc05::fence_before_sync();
+    __syncthreads();
+    tc05::fence_after_sync();
+    // phase 2: one thread issues 8 K-steps x 3 products
+    if (tid == 0) {
+      constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtTF32, kTM, kF, /*a_mn=*/0, /*b_mn=*/0);
+      const uint32_t zh = tc05::smem_u32(z_hi), zl = tc05::smem_u32(z_lo);
+      const uint32_t wh = tc05::smem_u32(w_hi), wl = tc05::smem_u32(w_lo);
+#pragma unroll
+      for (int ks = 0; ks < kF / 8; ++ks) {  // K = 8 floats = two core matrices per step
+        const uint64_t dzh = tc05::smem_desc(zh + ks * 2 * kZ_LBO, kZ_LBO, kZ_SBO);
+        const uint64_t dzl = tc05::smem_desc(zl + ks * 2 * kZ_LBO, kZ_LBO, kZ_SBO);
+        const uint64_t dwh = tc05::smem_desc(wh + ks * 2 * kW_LBO, kW_LBO, kW_SBO);
+        const uint64_t dwl = tc05::smem_desc(wl + ks * 2 * kW_LBO, kW_LBO, kW_SBO);
+        tc05::mma_tf32(tmem, dzl, dwh, idesc, ks > 0 ? 1u : 0u);  // small terms first
+        tc05::mma_tf32(tmem, dzh, dwl, idesc, 1u);
+        tc05::mma_tf32(tmem, dzh, dwh, idesc, 1u);
+      }
+      tc05::mma_commit(&bar_done);
+    }
+
+    // while the tensor core works: find the next tile, start fetching its rows, and read the
+    // destination row id this thread will scatter to
+    int nrel = rel, nrow0 = row1;
+    int rel_end = __ldg(indptr_i + rel + 1);
+    while (nrel < num_rels && nrow0 >= rel_end) {
+      ++nrel;
+      if (nrel < num_rels) rel_end = __ldg(indptr_i + nrel + 1);
+    }
+    const bool has_next = (it + 1 < tiles_per_cta) && nrel < num_rels;
+    const int nrow1 = min(rel_end, nrow0 + kTM);
+    if (z != nullptr && has_next) fetch_z(nrow0, nrow1 - nrow0);
+    const int t = (warp & 3) * 32 + lane32;  // tile row whose accumulators this thread reads
+    const int dst_row = t < nrows ? __ldg(indices_i + row0 + t) : 0;
+
+    if (!tc05::mbar_wait(&bar_done, parity)) ok = false;
+    parity ^= 1u;
+    ok = !__syncthreads_or(!ok);
+    tc05::fence_after_sync();
+    if (!ok) break;
+
+    // phase 3: warps w and w+4 share TMEM lanes 32*(w%4)..+31 and take 32 columns each
+    {
+      const int col0 = (warp >> 2) * 32;
+      uint32_t r[32];
+      tc05::tmem_ld32(tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + col0, r);
+      if (t < nrows) {
+        float4* dst = reinterpret_cast<float4*>(y + static_cast<size_t>(dst_row) * kF + col0);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          atomicAdd(dst + k, make_float4(__uint_as_float(r[4 * k]), __uint_as_float(r[4 * k + 1]),
+                                         __uint_as_float(r[4 * k + 2]), __uint_as_float(r[4 * k + 3])));
+      }
+    }
+    // every thread has read its accumulators before the next tile's first MMA overwrites them
+    tc05::fence_before_sync();
+    __syncthreads();
+    tc05::fence_after_sync();
+    if (!has_next) break;
+    rel = nrel;
+    row0 = nrow0;
+    row1 = nrow1;
   }
+  if (!ok && tid == 0) atomicAdd(&g_rgms_tc_timeouts, 1u);
   tc05::fence_before_sync();
   __syncthreads();
   if (warp == 0) tc05::tmem_dealloc(tmem, kF);
@@ -185,9 +231,12 @@ int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,
     configured_device = dev;
   }
   // upper bound on the number of tiles: every relation can add one partly filled tile
-  const long long blocks = static_cast<long long>(nnz_i) / kTM + num_rels;
-  rgms_tc_kernel<<<static_cast<unsigned>(blocks), kRgmsThreads, kSmemBytes, stream>>>(
-      a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, z);
+  const long long tiles = static_cast<long long>(nnz_i) / kTM + num_rels;
+  // two resident blocks per SM (shared memory), each walking a contiguous run of tiles
+  const long long grid = tiles < 2ll * kNumSMs ? tiles : 2ll * kNumSMs;
+  const int tiles_per_cta = static_cast<int>((tiles + grid - 1) / grid);
+  rgms_tc_kernel<<<static_cast<unsigned>(grid), kRgmsThreads, kSmemBytes, stream>>>(
+      a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, z, tiles_per_cta);
   SPTIR_LAUNCH_OK("rgms_tc_kernel");
   return 0;
 }

@@ -25,13 +25,15 @@ constexpr int kThreads = 256;
 // entries are one contiguous slot stream whose ids/values are read a batch of LPR ahead, and the
 // dense rows are gathered 8 at a time.  One writer per output row, CSR summation order, rows
 // without entries written as zeros.
-template <int LPR>
+template <int LPR, int W>  // W floats per lane: 4 (16-byte vectors) or 8 (32-byte vectors)
 __global__ void __launch_bounds__(kThreads, 4)
 csrmm_lean_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
                   const int32_t* __restrict__ indptr, const int32_t* __restrict__ indices, int m,
                   int feat, int rpi) {
+  using LV = LaneVec<W>;
+  using V = typename LV::type;
   constexpr int SUBS = kThreads / LPR;
-  constexpr int U = 8;
+  constexpr int U = (32 / W) < LPR ? (32 / W) : LPR;  // gathered rows in flight: 32 registers
   const int lane = threadIdx.x % LPR;
   const unsigned mask = group_mask<LPR>();
   const long long item = static_cast<long long>(blockIdx.x) * SUBS + threadIdx.x / LPR;
@@ -43,21 +45,21 @@ csrmm_lean_kernel(const float* __restrict__ a, const float* __restrict__ b, floa
   const int p0 = __shfl_sync(mask, ptr, 0, LPR);
   const int nslots = __shfl_sync(mask, ptr, nr, LPR) - p0;
   const unsigned row_bytes = static_cast<unsigned>(feat) * 4u;
-  const int off = blockIdx.y * LPR + lane;
-  const char* bl = reinterpret_cast<const char*>(reinterpret_cast<const float4*>(b) + off);
-  char* cl = reinterpret_cast<char*>(reinterpret_cast<float4*>(c) + off) +
+  const unsigned off = (blockIdx.y * LPR + lane) * (W * 4u);
+  const char* bl = reinterpret_cast<const char*>(b) + off;
+  char* cl = reinterpret_cast<char*>(c) + off +
              static_cast<unsigned long long>(static_cast<unsigned>(r0)) * row_bytes;
   const int32_t* cols = indices + p0;
   const float* wts = a + p0;
 
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  V acc = LV::zero();
   int j = 0;                                        // row of the item being accumulated
   int row_end = __shfl_sync(mask, ptr, 1, LPR) - p0;  // its end, as a slot number
   int s = 0;                                        // slots consumed so far
   auto finish_rows = [&]() {  // store every row whose last entry has been consumed
     while (j < nr && s >= row_end) {
-      __stcs(reinterpret_cast<float4*>(cl), acc);  // written once: keep B rows in L2
-      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      LV::stcs(cl, acc);  // written once: keep B rows in L2
+      acc = LV::zero();
       cl += row_bytes;
       ++j;
       row_end = __shfl_sync(mask, ptr, min(j + 1, nr), LPR) - p0;
@@ -82,17 +84,17 @@ csrmm_lean_kernel(const float* __restrict__ a, const float* __restrict__ b, floa
 #pragma unroll
     for (int k0 = 0; k0 < LPR; k0 += U) {
       if (k0 < cnt) {
-        float4 x[U];
+        V x[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {  // slots past the end ask for column 0: never consumed
           const unsigned col = static_cast<unsigned>(__shfl_sync(mask, cid, k0 + u, LPR));
-          x[u] = __ldg(reinterpret_cast<const float4*>(bl + static_cast<unsigned long long>(col) * row_bytes));
+          x[u] = LV::ldg(bl + static_cast<unsigned long long>(col) * row_bytes);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
           const float ak = __shfl_sync(mask, av, k0 + u, LPR);
           if (k0 + u < cnt) {
-            Vec<4>::fma(acc, ak, x[u]);
+            LV::fma(acc, ak, x[u]);
             ++s;
             if (s >= row_end) finish_rows();
           }
@@ -189,13 +191,17 @@ extern "C" int sparsetir_csrmm_raw(const float* a, const float* b, float* c, con
   const bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
   if (vec4 && static_cast<long long>(feat) * 4 < (1ll << 32) &&
       static_cast<long long>(m) * feat * 4 < (1ll << 32) * 1024) {
-    // lanes per row: one per 16-byte vector, narrowed until the n x tile slice of B that a pass
-    // over the rows gathers from fits the resident part of L2 (see hyb_spmm.cu)
-    const int nv = feat / 4;
-    int lanes = nv <= 8 ? 8 : (nv <= 16 ? 16 : 32);
+    // lanes per row: one per 32-byte vector when the operands allow it, else one per 16-byte
+    // vector; narrowed until the n x tile slice of B that a pass over the rows gathers from fits
+    // the resident part of L2 (see hyb_spmm.cu)
+    const int w = (feat % 32 == 0 && aligned32(b) && aligned32(c)) ? max_lane_floats() : 4;
+    const int nv = feat / w;
+    int lanes = nv <= 4 ? 4 : (nv <= 8 ? 8 : (nv <= 16 ? 16 : 32));
+    if (w == 4 && lanes < 8) lanes = 8;
     const size_t l2_budget = 48u << 20;
-    while (lanes > 8 && static_cast<size_t>(n) * lanes * 16 > l2_budget) lanes /= 2;
-    if (feat % (4 * lanes) == 0) {
+    const int min_lanes = w == 8 ? 4 : 8;
+    while (lanes > min_lanes && static_cast<size_t>(n) * lanes * w * 4 > l2_budget) lanes /= 2;
+    if (feat % (w * lanes) == 0) {
       const int subs = kThreads / lanes;
       // about four id batches per item, but never so few items that SMs sit idle
       const double avg = m > 0 ? static_cast<double>(nnz) / m : 0.0;
@@ -203,13 +209,20 @@ extern "C" int sparsetir_csrmm_raw(const float* a, const float* b, float* c, con
       rpi = rpi < 1 ? 1 : (rpi > lanes - 1 ? lanes - 1 : rpi);
       const long long want_items = 4ll * kNumSMs * 4 * subs;
       while (rpi > 1 && (m + rpi - 1) / rpi < want_items) rpi /= 2;
-      dim3 grid(ceil_div(ceil_div(m, rpi), subs), feat / (4 * lanes));
-      if (lanes == 8)
-        csrmm_lean_kernel<8><<<grid, kThreads, 0, st>>>(a, b, c, indptr, indices, m, feat, rpi);
-      else if (lanes == 16)
-        csrmm_lean_kernel<16><<<grid, kThreads, 0, st>>>(a, b, c, indptr, indices, m, feat, rpi);
-      else
-        csrmm_lean_kernel<32><<<grid, kThreads, 0, st>>>(a, b, c, indptr, indices, m, feat, rpi);
+      dim3 grid(ceil_div(ceil_div(m, rpi), subs), feat / (w * lanes));
+#define SPTIR_CSR_LEAN(L, WW) \
+  csrmm_lean_kernel<L, WW><<<grid, kThreads, 0, st>>>(a, b, c, indptr, indices, m, feat, rpi)
+      if (w == 8) {
+        if (lanes == 4) SPTIR_CSR_LEAN(4, 8);
+        else if (lanes == 8) SPTIR_CSR_LEAN(8, 8);
+        else if (lanes == 16) SPTIR_CSR_LEAN(16, 8);
+        else SPTIR_CSR_LEAN(32, 8);
+      } else {
+        if (lanes == 8) SPTIR_CSR_LEAN(8, 4);
+        else if (lanes == 16) SPTIR_CSR_LEAN(16, 4);
+        else SPTIR_CSR_LEAN(32, 4);
+      }
+#undef SPTIR_CSR_LEAN
       SPTIR_LAUNCH_OK("csrmm_lean_kernel");
       return 0;
     }

@@ -39,6 +39,8 @@ constexpr int kMaxB = SPARSETIR_HYB_MAX_BUCKETS;
 // Stored slots covered by one work item (one sub-warp of `lpr` lanes): four id batches, so that
 // the per-item set-up is amortised and the id prefetch of spmm_core.cuh has something to hide.
 constexpr int item_slots(int lpr) { return 4 * lpr; }
+// lean kernel: lpr lanes of w floats each; 4 batches of ids with 16-byte lanes, 8 with 32-byte lanes
+constexpr int lean_item_slots(int lpr, int w) { return lpr * w; }
 
 struct HybTable {
   const float* w[kMaxB];
@@ -158,19 +160,21 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
 // shuffle + four FMAs; row ends sit at compile-time positions of the unrolled batch (narrow
 // rows) or are tested once per 8 slots (wide rows); row ids travel in registers with the
 // "accumulate atomically" flag in the sign bit, so a row end costs one shuffle and a store.
-template <int LPR, int WM>  // WM = 1, 2, 4: the ELL width itself; WM = 8: a multiple of 8
+// W = floats per lane: 4 (16-byte vectors) or 8 (32-byte vectors, two-wide FMAs)
+template <int LPR, int WM, int W>  // WM = 1, 2, 4: the ELL width itself; WM = 8: a multiple of 8
 __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
                                           const float* __restrict__ wts,
                                           const int32_t* __restrict__ rows, int nrows, int r0,
                                           int nr, int nslots, int per_row,
-                                          const float4* __restrict__ bl, unsigned row_bytes,
-                                          float4* __restrict__ cl, bool always_atomic, int lane,
+                                          const char* __restrict__ bl, unsigned row_bytes,
+                                          char* __restrict__ cl, bool always_atomic, int lane,
                                           unsigned mask) {
-  constexpr int U = 8;
+  using LV = LaneVec<W>;
+  using V = typename LV::type;
+  constexpr int U = (32 / W) < LPR ? (32 / W) : LPR;  // gathered rows in flight: 32 registers
   // address of this lane's vector in dense row `col`: one 32x32->64 multiply-add
-  auto vec_of = [&](const float4* base, int col) -> const float4* {
-    return reinterpret_cast<const float4*>(reinterpret_cast<const char*>(base) +
-                                           static_cast<unsigned long long>(static_cast<unsigned>(col)) * row_bytes);
+  auto vec_of = [&](const char* base, int col) -> const char* {
+    return base + static_cast<unsigned long long>(static_cast<unsigned>(col)) * row_bytes;
   };
   static_assert(LPR % U == 0, "a batch is a whole number of chunks");
   constexpr int RPB = WM < 8 ? LPR / WM : 0;  // ELL rows that end inside one batch (narrow rows)
@@ -183,14 +187,14 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
                        (g + 1 < nrows && __ldg(rows + g + 1) == rid);
     return rid | ((always_atomic || split) ? 0x80000000 : 0);
   };
-  auto row_end = [&](float4& acc, int rf) {
-    float4* dst = const_cast<float4*>(vec_of(cl, rf & 0x7fffffff));
-    if (rf < 0) atomicAdd(dst, acc);
-    else __stcs(dst, acc);  // written once: do not displace B rows in L2
-    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  auto row_end = [&](V& acc, int rf) {
+    char* dst = const_cast<char*>(vec_of(cl, rf & 0x7fffffff));
+    if (rf < 0) LV::atomic_add(dst, acc);
+    else LV::stcs(dst, acc);  // written once: do not displace B rows in L2
+    acc = LV::zero();
   };
 
-  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  V acc = LV::zero();
   int c = 0, rf = 0;
   float a = 0.f;
   if (lane < nslots) {
@@ -200,7 +204,7 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
   if (WM < 8) {
     if (lane < RPB) rf = row_flag(r0 + lane);   // rows ending in batch 0
   } else {
-    if (lane < nr) rf = row_flag(r0 + lane);    // all rows of the item (nr <= LPR / 2)
+    if (lane < nr) rf = row_flag(r0 + lane);    // all rows of the item (nr <= LPR)
   }
   int left = per_row, jrow = 0;  // wide rows only
 
@@ -216,13 +220,13 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
     if (cnt >= LPR) {
 #pragma unroll
       for (int k0 = 0; k0 < LPR; k0 += U) {
-        float4 x[U];
+        V x[U];
 #pragma unroll
         for (int u = 0; u < U; ++u)
-          x[u] = __ldg(vec_of(bl, __shfl_sync(mask, c, k0 + u, LPR)));
+          x[u] = LV::ldg(vec_of(bl, __shfl_sync(mask, c, k0 + u, LPR)));
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          Vec<4>::fma(acc, __shfl_sync(mask, a, k0 + u, LPR), x[u]);
+          LV::fma(acc, __shfl_sync(mask, a, k0 + u, LPR), x[u]);
           if (WM < 8 && (k0 + u + 1) % WM == 0)
             row_end(acc, __shfl_sync(mask, rf, (k0 + u) / WM, LPR));
         }
@@ -239,16 +243,16 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
 #pragma unroll
       for (int k0 = 0; k0 < LPR; k0 += U) {
         if (k0 < cnt) {
-          float4 x[U];
+          V x[U];
 #pragma unroll
           for (int u = 0; u < U; ++u)
-            x[u] = __ldg(vec_of(bl, __shfl_sync(mask, c, k0 + u, LPR)));  // dead slots: column 0
+            x[u] = LV::ldg(vec_of(bl, __shfl_sync(mask, c, k0 + u, LPR)));  // dead slots: column 0
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const float ak = __shfl_sync(mask, a, k0 + u, LPR);
             const int rfe = (WM < 8) ? __shfl_sync(mask, rf, (k0 + u) / WM, LPR) : 0;
             if (k0 + u < cnt) {
-              Vec<4>::fma(acc, ak, x[u]);
+              LV::fma(acc, ak, x[u]);
               if (WM < 8 && (k0 + u + 1) % WM == 0) row_end(acc, rfe);
             }
           }
@@ -269,12 +273,12 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
   }
 }
 
-template <int LPR>
+template <int LPR, int W>
 __global__ void __launch_bounds__(kThreads, 4)
 hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b,
                      float* __restrict__ c, int feat, int all_atomic) {
   constexpr int SUBS = kThreads / LPR;
-  constexpr int ITEM = item_slots(LPR);
+  constexpr int ITEM = lean_item_slots(LPR, W);
   const int lane = threadIdx.x % LPR;
   const int sub = threadIdx.x / LPR;
   const unsigned mask = group_mask<LPR>();
@@ -303,21 +307,21 @@ hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const float* __restric
   }
   const int r0 = static_cast<int>(r0l);
   const unsigned stride = static_cast<unsigned>(feat) * 4u;  // bytes per dense row
-  const int off = blockIdx.y * LPR + lane;
-  const float4* bl = reinterpret_cast<const float4*>(b) + off;
-  float4* cl = reinterpret_cast<float4*>(c) + off;
+  const unsigned off = (blockIdx.y * LPR + lane) * (W * 4u);  // this lane's piece of the tile
+  const char* bl = reinterpret_cast<const char*>(b) + off;
+  char* cl = reinterpret_cast<char*>(c) + off;
   const int32_t* cols = tb.cols[q] + first;
   const float* wts = tb.w[q] + first;
   const int32_t* rows = tb.rows[q];
   const bool always_atomic = all_atomic || cpr > 1;
   if (width == 1)
-    lean_item<LPR, 1>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
+    lean_item<LPR, 1, W>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
   else if (width == 2)
-    lean_item<LPR, 2>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
+    lean_item<LPR, 2, W>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
   else if (width == 4)
-    lean_item<LPR, 4>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
+    lean_item<LPR, 4, W>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
   else
-    lean_item<LPR, 8>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
+    lean_item<LPR, 8, W>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
 }
 
 // The main kernel for 16-byte aligned operands: B rows are staged through per-lane rings in
@@ -462,9 +466,10 @@ void plan_items(HybTable& tb, int item) {
 // tile is narrowed until that slice fits the part of L2 that stays resident for data every SM
 // reads (measured: about half of the 126 MB), because re-reading the index arrays once per tile
 // costs little next to re-fetching B rows from HBM.
-int lanes_per_row(int feat, bool vec4, int n) {
-  const int units = vec4 ? feat / 4 : feat;
-  int lanes = units <= 8 ? 8 : (units <= 16 ? 16 : 32);
+int lanes_per_row(int feat, bool vec4, int n, int lane_w) {
+  const int units = vec4 ? feat / lane_w : feat;
+  const int min_lanes = lane_w == 8 ? 4 : 8;
+  int lanes = units <= min_lanes ? min_lanes : (units <= 8 ? 8 : (units <= 16 ? 16 : 32));
   if (vec4) {
     // SPARSETIR_L2_BUDGET_MB overrides the default for tuning on other parts
     static const size_t l2_budget = [] {
@@ -472,7 +477,7 @@ int lanes_per_row(int feat, bool vec4, int n) {
       const long mb = e ? std::atol(e) : 0;
       return static_cast<size_t>(mb > 0 ? mb : 48) << 20;
     }();
-    while (lanes > 8 && static_cast<size_t>(n) * lanes * 16 > l2_budget) lanes /= 2;
+    while (lanes > min_lanes && static_cast<size_t>(n) * lanes * lane_w * 4 > l2_budget) lanes /= 2;
   }
   return lanes;
 }
@@ -492,13 +497,13 @@ long long plan_blocks(HybTable& tb, int subs) {
   return blocks;
 }
 
-template <int LPR>
+template <int LPR, int W>
 int launch_lean(HybTable& tb, const float* b, float* c, int feat, int all_atomic,
                 cudaStream_t stream) {
   const long long blocks = plan_blocks(tb, kThreads / LPR);
   if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
-  dim3 grid(static_cast<unsigned>(blocks), feat / (4 * LPR));
-  hyb_spmm_lean_kernel<LPR><<<grid, kThreads, 0, stream>>>(tb, b, c, feat, all_atomic);
+  dim3 grid(static_cast<unsigned>(blocks), feat / (W * LPR));
+  hyb_spmm_lean_kernel<LPR, W><<<grid, kThreads, 0, stream>>>(tb, b, c, feat, all_atomic);
   SPTIR_LAUNCH_OK("hyb_spmm_lean_kernel");
   return 0;
 }
@@ -572,8 +577,21 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
     tb.nrows[k] = bk.nrows; tb.width[k] = bk.width;
   }
   const bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
-  const int lanes = lanes_per_row(feat, vec4, n);
-  plan_items(tb, item_slots(lanes));
+  // the lean kernel takes whole feature tiles and ELL widths of 1, 2, 4 or a multiple of 8; with
+  // 32-byte aligned operands and a multiple of 32 features its lanes own 8 floats, else 4
+  bool lean = vec4 && static_cast<long long>(feat) * 4 < (1ll << 32);
+  for (int q = 0; q < tb.nb; ++q) {
+    const int w = tb.width[q];
+    lean = lean && (w == 1 || w == 2 || w == 4 || w % 8 == 0);
+  }
+  int lane_w = (lean && feat % 32 == 0 && aligned32(b) && aligned32(c)) ? max_lane_floats() : 4;
+  int lanes = lanes_per_row(feat, vec4, n, lane_w);
+  if (lane_w == 8 && feat % (lane_w * lanes) != 0) {  // no whole tiles of 8-float lanes
+    lane_w = 4;
+    lanes = lanes_per_row(feat, vec4, n, lane_w);
+  }
+  lean = lean && feat % (lane_w * lanes) == 0;
+  plan_items(tb, lean ? lean_item_slots(lanes, lane_w) : item_slots(lanes));
 
   if (flags & SPARSETIR_HYB_ZERO_C) {
     SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(m) * feat * sizeof(float), st));
@@ -595,15 +613,16 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
   if (tb.nb == 0) return 0;
 
   if (vec4) {
-    bool lean = feat % (4 * lanes) == 0 && static_cast<long long>(feat) * 4 < (1ll << 32);
-    for (int q = 0; q < tb.nb; ++q) {
-      const int w = tb.width[q];
-      lean = lean && (w == 1 || w == 2 || w == 4 || w % 8 == 0);
+    if (lean && lane_w == 8) {
+      if (lanes == 4) return launch_lean<4, 8>(tb, b, c, feat, all_atomic, st);
+      if (lanes == 8) return launch_lean<8, 8>(tb, b, c, feat, all_atomic, st);
+      if (lanes == 16) return launch_lean<16, 8>(tb, b, c, feat, all_atomic, st);
+      return launch_lean<32, 8>(tb, b, c, feat, all_atomic, st);
     }
     if (lean) {
-      if (lanes == 8) return launch_lean<8>(tb, b, c, feat, all_atomic, st);
-      if (lanes == 16) return launch_lean<16>(tb, b, c, feat, all_atomic, st);
-      return launch_lean<32>(tb, b, c, feat, all_atomic, st);
+      if (lanes == 8) return launch_lean<8, 4>(tb, b, c, feat, all_atomic, st);
+      if (lanes == 16) return launch_lean<16, 4>(tb, b, c, feat, all_atomic, st);
+      return launch_lean<32, 4>(tb, b, c, feat, all_atomic, st);
     }
     if (lanes == 8) return launch_async<8>(tb, b, c, feat, all_atomic, st);
     if (lanes == 16) return launch_async<16>(tb, b, c, feat, all_atomic, st);

@@ -18,6 +18,9 @@
 //    butterfly: LPR-1 shuffles leave lane l with the finished dot product of position l,
 //    instead of log2(LPR) shuffles per position; the warp stores 32 consecutive results with
 //    one coalesced store.
+#include <cstdint>
+#include <cstdlib>
+
 #include "common.h"
 #include "vec.cuh"
 
@@ -187,6 +190,134 @@ sddmm_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Lean variant for feature counts that are multiples of 32 with 32-byte aligned operands.
+//
+// One launch covers a tile of 8*LPR consecutive features [foff, foff + 8*LPR) of every stored
+// position; the host walks the tiles with one launch each, the first storing C and the others
+// adding to it, and picks the tile so that the slice of B a launch gathers from stays in L2.
+// A lane owns 8 consecutive features: one 256-bit load per gathered row, the dot product as
+// packed two-wide fp32 FMAs.  A warp owns `chunk` consecutive positions, finds the row of its
+// first position with a 32-ary search done by the whole warp (4 dependent reads instead of 18
+// at 2^18 rows), and loads the column ids of the next batch before it gathers for this one.
+// first index idx in [0, m+1] with idx == m+1 or indptr[idx] > p, found by the whole warp;
+// row(p) is that index minus one (the search of sparse_tir_lowered_buffer_scripts.py:530-549)
+__device__ __forceinline__ int warp_row_search(const int32_t* __restrict__ indptr, int m, int p,
+                                               int wlane) {
+  int lo = 0, hi = m + 1;
+  while (hi - lo >= 32) {
+    const int step = (hi - lo + 31) / 32;
+    const long long probe = static_cast<long long>(lo) + static_cast<long long>(wlane + 1) * step;
+    const bool gt = probe >= hi || __ldg(indptr + probe) > p;
+    const int first = __ffs(__ballot_sync(0xffffffffu, gt)) - 1;  // lane 31 probes >= hi: always set
+    const int q = lo + (first + 1) * step;
+    if (first > 0) lo = q - step + 1;
+    hi = min(hi, q);
+  }
+  const int idx = lo + wlane;
+  const bool gt = idx >= hi || __ldg(indptr + idx) > p;  // lane hi - lo (< 32) has idx == hi
+  return lo + __ffs(__ballot_sync(0xffffffffu, gt)) - 1;
+}
+
+template <int LPR>
+__global__ void __launch_bounds__(kThreads, LPR <= 8 ? 4 : 2)
+sddmm_lean_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                  const int32_t* __restrict__ indptr, const int32_t* __restrict__ indices,
+                  const float* __restrict__ scale, int m, int nnz, int ld, int foff, int accumulate,
+                  int chunk) {
+  constexpr int U = LPR < 4 ? LPR : 4;  // gathered rows in flight per lane (8 registers each)
+  const int wlane = threadIdx.x & 31;
+  const int lane = wlane % LPR;
+  const unsigned mask = group_mask<LPR>();
+  const long long warp = static_cast<long long>(blockIdx.x) * (kThreads / 32) + threadIdx.x / 32;
+  const long long e_begin = warp * chunk;
+  if (e_begin >= nnz) return;
+  const int e_end = static_cast<int>(min(static_cast<long long>(nnz), e_begin + chunk));
+  const float* a_lane = a + foff + lane * 8;
+  const float* b_lane = b + foff + lane * 8;
+
+  int warp_row = max(0, min(m - 1, warp_row_search(indptr, m, static_cast<int>(e_begin), wlane) - 1));
+  int warp_end = __ldg(indptr + warp_row + 1);  // first position past the warp's current row
+  int cur_row = -1;
+  Pack4 arow = pack4_zero();
+
+  int col_next = (static_cast<int>(e_begin) + wlane < e_end) ? __ldg(indices + e_begin + wlane) : 0;
+  for (int base = static_cast<int>(e_begin); base < e_end; base += 32) {
+    const int e = base + wlane;
+    const bool live = e < e_end;
+    const int col = col_next;
+    if (e + 32 < e_end) col_next = __ldg(indices + e + 32);
+    float mul = 1.f, old = 0.f;
+    if (live) {
+      if (scale != nullptr) mul = __ldg(scale + e);
+      if (accumulate) old = c[e];
+    }
+    float part[LPR];
+    if (base + 32 <= min(warp_end, e_end)) {
+      // every position of the batch lies in the warp's current row
+      if (cur_row != warp_row) {
+        cur_row = warp_row;
+        arow = ldg256(a_lane + static_cast<size_t>(cur_row) * ld);
+      }
+#pragma unroll
+      for (int k0 = 0; k0 < LPR; k0 += U) {
+        Pack4 x[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+          x[u] = ldg256(b_lane + static_cast<size_t>(__shfl_sync(mask, col, k0 + u, LPR)) * ld);
+#pragma unroll
+        for (int u = 0; u < U; ++u) part[k0 + u] = dot8(arow, x[u]);
+      }
+    } else {
+      int row = warp_row;
+      if (live) {
+        int steps = 0;
+        // row < m - 1 keeps every read inside indptr even if nnz disagrees with indptr[m]
+        while (row < m - 1 && __ldg(indptr + row + 1) <= e) {
+          ++row;
+          if (++steps == 8) {  // long run of empty rows: finish with a search
+            row = min(m - 1, edge_row_search(indptr, row, m, e));
+            break;
+          }
+        }
+      }
+      // the next batch starts from the row of this batch's last live position
+      warp_row = __shfl_sync(0xffffffffu, row, min(31, e_end - 1 - base));
+      warp_end = __ldg(indptr + warp_row + 1);
+#pragma unroll
+      for (int k0 = 0; k0 < LPR; k0 += U) {
+        Pack4 x[U];
+        int rk[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {  // dead positions carry column 0 and the warp's row
+          rk[u] = __shfl_sync(mask, row, k0 + u, LPR);
+          x[u] = ldg256(b_lane + static_cast<size_t>(__shfl_sync(mask, col, k0 + u, LPR)) * ld);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (rk[u] != cur_row) {  // uniform inside the sub-warp
+            cur_row = rk[u];
+            arow = ldg256(a_lane + static_cast<size_t>(cur_row) * ld);
+          }
+          part[k0 + u] = dot8(arow, x[u]);
+        }
+      }
+    }
+    // transposing butterfly: afterwards part[0] of lane l is the dot product of position l
+#pragma unroll
+    for (int offl = LPR / 2, n = LPR; offl >= 1; offl >>= 1, n >>= 1) {
+      const bool upper = (lane & offl) != 0;
+#pragma unroll
+      for (int i = 0; i < n / 2; ++i) {
+        const float send = upper ? part[i] : part[i + n / 2];
+        const float keep = upper ? part[i + n / 2] : part[i];
+        part[i] = keep + __shfl_xor_sync(mask, send, offl, LPR);
+      }
+    }
+    if (live) c[e] = fmaf(part[0], mul, old);
+  }
+}
+
 // Fallback for feature sizes beyond the register-resident variants: a full warp per position,
 // looping over the feature dimension.
 __global__ void __launch_bounds__(kThreads)
@@ -229,6 +360,55 @@ int launch(const float* a, const float* b, float* c, const int32_t* indptr, cons
   return 0;
 }
 
+template <int LPR>
+int launch_lean_tile(const float* a, const float* b, float* c, const int32_t* indptr,
+                     const int32_t* indices, const float* scale, int m, int feat, int nnz, int foff,
+                     cudaStream_t stream) {
+  // long chunks amortise the row search; short ones keep small inputs spread over the SMs
+  const int chunk = nnz >= (1 << 22) ? 1024 : 256;
+  const int warps = ceil_div(nnz, chunk);
+  const int blocks = ceil_div(warps, kThreads / 32);
+  sddmm_lean_kernel<LPR><<<blocks, kThreads, 0, stream>>>(a, b, c, indptr, indices, scale, m, nnz,
+                                                           feat, foff, foff != 0, chunk);
+  SPTIR_LAUNCH_OK("sddmm_lean_kernel");
+  return 0;
+}
+
+// What stays resident in L2 of data that every SM reads (about half of the 126 MB);
+// SPARSETIR_L2_BUDGET_MB overrides it for tuning on other parts.
+size_t l2_budget_bytes() {
+  static const size_t budget = [] {
+    const char* e = std::getenv("SPARSETIR_L2_BUDGET_MB");
+    const long mb = e ? std::atol(e) : 0;
+    return static_cast<size_t>(mb > 0 ? mb : 48) << 20;
+  }();
+  return budget;
+}
+
+// feat is a multiple of 32: the widest tile (32..256 features) that divides feat and whose
+// slice of B (n rows) fits the L2 budget; one launch per tile, in stream order.
+int launch_lean(const float* a, const float* b, float* c, const int32_t* indptr,
+                const int32_t* indices, const float* scale, int m, int n, int feat, int nnz,
+                cudaStream_t stream) {
+  int tile = 32;
+  for (int t = 256; t > 32; t /= 2)
+    if (feat % t == 0 && static_cast<size_t>(n) * t * 4 <= l2_budget_bytes()) {
+      tile = t;
+      break;
+    }
+  for (int foff = 0; foff < feat; foff += tile) {
+    int rc;
+    switch (tile) {
+      case 256: rc = launch_lean_tile<32>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, stream); break;
+      case 128: rc = launch_lean_tile<16>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, stream); break;
+      case 64: rc = launch_lean_tile<8>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, stream); break;
+      default: rc = launch_lean_tile<4>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, stream); break;
+    }
+    if (rc != 0) return rc;
+  }
+  return 0;
+}
+
 }  // namespace
 }  // namespace sptir
 
@@ -236,8 +416,7 @@ extern "C" int sparsetir_sddmm_raw(const float* a, const float* b, float* c, con
                                    const int32_t* indices, const float* scale, int m, int n,
                                    int feat, int nnz, int device_id, void* stream) {
   using namespace sptir;
-  (void)n;
-  if (m < 0 || feat < 0 || nnz < 0) return fail("sparsetir_sddmm: negative size");
+  if (m < 0 || n < 0 || feat < 0 || nnz < 0) return fail("sparsetir_sddmm: negative size");
   if (nnz == 0) return 0;
   if (m < 1) return fail("sparsetir_sddmm: %d stored entries but no rows", nnz);
   if (!c || !indptr || !indices || (feat > 0 && (!a || !b)))
@@ -248,6 +427,8 @@ extern "C" int sparsetir_sddmm_raw(const float* a, const float* b, float* c, con
     SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(nnz) * sizeof(float), st));
     return 0;
   }
+  if (feat % 32 == 0 && aligned32(a) && aligned32(b))
+    return launch_lean(a, b, c, indptr, indices, scale, m, n, feat, nnz, st);
   const bool vec4 = (feat % 4 == 0) && aligned16(a) && aligned16(b);
   if (vec4) {
     const int nv = feat / 4;

@@ -1,6 +1,7 @@
 """Parity of the CUDA kernels with the CPU oracle, called through the packed C ABI exactly like
 the reference calls a built operator.  Tolerances are the ones stated for this path: bit-exact
 integers; fp32 rtol 1e-4 / atol 1e-5; fp16 inputs with fp32 accumulation rtol 1e-2."""
+import ctypes
 import os
 
 import numpy as np
@@ -247,7 +248,7 @@ def run_sddmm(c: dg.CSR, a, b, device, scale=None, scalars=False):
     return out
 
 
-@pytest.mark.parametrize("feat", [1, 4, 8, 20, 32, 64, 128, 200, 256, 512, 516, 1024])
+@pytest.mark.parametrize("feat", [1, 4, 8, 20, 32, 64, 96, 128, 160, 200, 256, 320, 512, 516, 1024])
 def test_sddmm_matches_oracle(cuda_device, feat):
     c = dg.csr_lognormal(n=900, mu=3.0, sigma=1.0, max_deg=500, seed=feat)
     a = dg.dense_operand(1, c.m, feat)
@@ -278,6 +279,39 @@ def test_sddmm_empty_rows_and_tails(cuda_device):
         a = dg.dense_operand(3, c.m, feat)
         b = dg.dense_operand(4, c.n, feat)
         close(run_sddmm(c, a, b, cuda_device), orc.sddmm(a, b, c.indptr, c.indices, c.m, c.n, feat))
+
+
+def test_sddmm_long_chunks_and_feature_tiles(cuda_device):
+    # more than 2^22 stored positions (the kernel then gives a warp 1024 of them) and feature
+    # counts that take several launches, with and without the per-position scale
+    c = dg.csr_lognormal(n=20000, mu=5.3, sigma=0.6, max_deg=4000, seed=11)
+    assert c.nnz > (1 << 22)
+    scale = np.random.default_rng(5).random(c.nnz, dtype=np.float32)
+    for feat, sc in ((32, None), (96, scale)):
+        a = dg.dense_operand(5, c.m, feat)
+        b = dg.dense_operand(6, c.n, feat)
+        want = orc.sddmm(a, b, c.indptr, c.indices, c.m, c.n, feat, scale=sc)
+        close(run_sddmm(c, a, b, cuda_device, scale=sc), want, atol=ATOL * max(1, feat // 32))
+
+
+def test_sddmm_operands_not_32_byte_aligned(cuda_device):
+    # operands that start 16 bytes into an allocation take the 16-byte-vector kernel
+    c = dg.csr_lognormal(n=700, mu=3.0, sigma=1.0, max_deg=300, seed=3)
+    feat = 64
+    a = dg.dense_operand(7, c.m, feat)
+    b = dg.dense_operand(8, c.n, feat)
+    abuf = torch.zeros(a.size + 4, device=cuda_device)
+    bbuf = torch.zeros(b.size + 4, device=cuda_device)
+    abuf[4:] = dev(a.reshape(-1), cuda_device)
+    bbuf[4:] = dev(b.reshape(-1), cuda_device)
+    out = torch.full((c.nnz,), -7.0, device=cuda_device)
+    ip, ix = dev(c.indptr, cuda_device), dev(c.indices, cuda_device)
+    rc = L.load().sparsetir_sddmm_raw(abuf.data_ptr() + 16, bbuf.data_ptr() + 16, out.data_ptr(),
+                                      ip.data_ptr(), ix.data_ptr(), None, c.m, c.n, feat, c.nnz,
+                                      0, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0, L.last_error()
+    torch.cuda.synchronize()
+    close(out, orc.sddmm(a, b, c.indptr, c.indices, c.m, c.n, feat), atol=ATOL * 2)
 
 
 def test_edge_to_row_bit_exact(cuda_device):
@@ -399,3 +433,43 @@ def test_tensor_core_waits_never_ran_out(cuda_device):
     n = ctypes.c_uint(123)
     assert L.load().sparsetir_tc_timeouts(0, ctypes.byref(n)) == 0, L.last_error()
     assert n.value == 0
+
+
+# ------------------------------------------------------------------ 32-byte-lane SpMM variants
+_WIDE_LANE_CHILD = r"""
+import sys
+import numpy as np, torch
+sys.path.insert(0, {root!r}); sys.path.insert(0, {tests!r})
+from oracle import oracle as orc
+from sparsetir_b200 import datagen as dg, format as fmt, ops
+d = torch.device("cuda", 0)
+dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(d)
+g = dg.csr_powerlaw(n=3000, max_deg=1500, seed=4)
+for feat in (32, 64, 128, 512):
+    x = dg.dense_operand(9, g.n, feat)
+    want = np.zeros((g.m, feat), np.float32)
+    orc.csrmm(g.data, x, want, g.indptr, g.indices, g.m, g.n, feat)
+    y = torch.full((g.m * feat,), 5.0, device=d)
+    ops.csrmm(dev(g.data), dev(x.reshape(-1)), y, dev(g.indptr), dev(g.indices))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(y.cpu().numpy().reshape(g.m, feat), want, rtol=1e-4, atol=1e-5)
+    bk = [1, 2, 4, 8, 16]
+    rows, cols, mask, vals, pos = fmt.column_part_hyb(g.m, g.n, g.indptr, g.indices, 1, bk, data=g.data)
+    devb = [(dev(vals[0][k]), dev(rows[0][k]), dev(cols[0][k])) for k in range(len(bk))]
+    y2 = torch.zeros(g.m * feat, device=d)
+    ops.hyb_spmm(*ops.hyb_args(dev(x), y2, devb, feat))
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(y2.cpu().numpy().reshape(g.m, feat), want, rtol=1e-4, atol=1e-5)
+print("wide lanes ok")
+"""
+
+
+def test_spmm_32_byte_lane_variants_in_child_process(cuda_device):
+    # SPARSETIR_LANE_FLOATS is read once per process, so the variants run in a child
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, SPARSETIR_LANE_FLOATS="8")
+    code = _WIDE_LANE_CHILD.format(root=root, tests=os.path.join(root, "tests"))
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "wide lanes ok" in r.stdout, r.stdout + r.stderr

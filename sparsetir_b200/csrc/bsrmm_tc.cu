@@ -9,13 +9,18 @@
 // columns = two tcgen05.mma.kind::f16 of K = 16.  The feature-contiguous B rows are an MN-major
 // operand, the row-major A block a K-major operand; neither needs a transpose in memory.
 //
-// Pipeline: 6 shared-memory stages, operands of 4 blocks in flight; all 128 threads copy a
-// block's operands with cp.async straight into the un-swizzled core-matrix layout the tensor
-// core reads (tc05.cuh), one elected thread issues the MMAs, tcgen05.commit arrives on the
-// stage's mbarrier when the tensor core has finished reading it.  A stage is refilled two
-// blocks after it was multiplied, so the wait for "tensor core done with it" is normally over
-// before it starts and the loop never stalls on MMA latency.  Epilogue: TMEM -> registers
-// (lane = feature, 32 columns = 32 block rows) -> 32 coalesced row stores per warp.
+// Pipeline: operands travel global -> registers -> shared memory.  (Asynchronous 16-byte
+// copies straight into shared memory were measured at about 16 bytes per clock per SM on this
+// part, which capped the kernel at ~5 TB/s of L2 reads; plain 16-byte loads are not so limited.)
+// Every thread owns five 16-byte pieces of a block's operands and keeps TWO blocks in registers:
+// the loads of block it+2 are issued before the pieces of block it are multiplied, so the wait
+// for a load is hidden behind two iterations and behind the other thread blocks of the SM
+// (3 stages = 30 KB, all 512 blocks of a 128 x 128-block matrix at 512 features are resident at
+// once).  The pieces are stored in the un-swizzled core-matrix layout the tensor core reads
+// (tc05.cuh), one elected thread issues the MMAs, tcgen05.commit arrives on the stage's mbarrier
+// when the tensor core has finished reading it, and a thread waits on that mbarrier before it
+// overwrites the stage three blocks later.  Epilogue: TMEM -> registers (lane = feature,
+// 32 columns = 32 block rows) -> 32 coalesced row stores per warp.
 // Every mbarrier wait is bounded; a timeout is counted in a device-side status word and the block
 // gives up cleanly (TMEM freed), so a protocol error cannot hang the GPU.
 #include <cuda_fp16.h>
@@ -34,8 +39,7 @@ namespace {
 constexpr int kThreads = 128;
 constexpr int kBlk = 32;
 constexpr int kTileF = 128;
-constexpr int kStages = 6;
-constexpr int kAhead = kStages - 2;  // blocks in flight ahead of the one being multiplied
+constexpr int kStages = 3;
 constexpr int kBBytes = kBlk * kTileF * 2;  // B tile of one block: 32 x 128 fp16 = 8 KB
 constexpr int kABytes = kBlk * kBlk * 2;    // A block: 2 KB
 constexpr int kStageBytes = kBBytes + kABytes;
@@ -84,38 +88,57 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
   tc05::fence_after_sync();
   const uint32_t tmem = s_tmem;
 
-  // this thread's share of a stage: 4 chunks of the B tile, 1 chunk of the A block (16 bytes each)
-  const int b_fc = tid >> 3, b_bjlo = tid & 7;  // B: feature chunk 0..15, block column bj%8
+  // this thread's share of a block: 4 pieces of the B tile, 1 piece of the A block (16 bytes each)
+  // B tile: 32 rows (block columns bj) x 16 chunks of 8 features.  Loads want whole 128-byte lines
+  // (8 consecutive chunks of a row); conflict-free 16-byte stores into the core-matrix layout want
+  // the 32 lanes of a warp to cover all 8 values of bj%8 (the 16-byte slot inside a 128-byte core
+  // matrix).  A load instruction k covers rows 4k..4k+3 (+16 for warps 2, 3) x 8 chunks, and
+  // store instruction j of a lane writes the piece it loaded with instruction j ^ (lane & 1): even
+  // and odd chunks of one store come from rows 4 apart, which makes the 8 slots appear 4 times each.
+  const int b_fc = (warp & 1) * 8 + (lane & 7);         // feature chunk 0..15
+  const int b_row0 = (warp >> 1) * 16 + (lane >> 3);    // row of load instruction 0; +4 per instruction
+  const bool b_odd = (lane & 1) != 0;
   const int a_bi = tid >> 2, a_kc = tid & 3;    // A: block row, 8-column chunk
-  auto load_stage = [&](int it) {
-    unsigned char* st = smem + (it % kStages) * kStageBytes;
+  struct Pieces {
+    uint4 b[4];
+    uint4 a;
+  };
+  auto load_block = [&](int it, Pieces& x) {
     const int p = p0 + it;
     const size_t brow0 = static_cast<size_t>(it < kColCache ? s_cols[it] : __ldg(indices + p)) * kBlk;
 #pragma unroll
-    for (int kc = 0; kc < 4; ++kc) {
-      const __half* src = b + (brow0 + kc * 8 + b_bjlo) * feat + f0 + b_fc * 8;
-      cp_async16(st + (kc * 16 + b_fc) * 128 + b_bjlo * 16, src);
+    for (int kc = 0; kc < 4; ++kc)
+      x.b[kc] = __ldg(reinterpret_cast<const uint4*>(b + (brow0 + b_row0 + kc * 4) * feat + f0 + b_fc * 8));
+    x.a = __ldg(reinterpret_cast<const uint4*>(a + static_cast<size_t>(p) * (kBlk * kBlk) + a_bi * kBlk + a_kc * 8));
+  };
+  auto store_block = [&](int stage, const Pieces& x) {
+    unsigned char* st = smem + stage * kStageBytes;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint4 v = b_odd ? x.b[j ^ 1] : x.b[j];
+      const int row = b_row0 + (b_odd ? (j ^ 1) : j) * 4;  // block column bj of the piece
+      *reinterpret_cast<uint4*>(st + ((row >> 3) * 16 + b_fc) * 128 + (row & 7) * 16) = v;
     }
-    const __half* asrc = a + static_cast<size_t>(p) * (kBlk * kBlk) + a_bi * kBlk + a_kc * 8;
-    cp_async16(st + kBBytes + (a_kc * 4 + (a_bi >> 3)) * 128 + (a_bi & 7) * 16, asrc);
+    *reinterpret_cast<uint4*>(st + kBBytes + (a_kc * 4 + (a_bi >> 3)) * 128 + (a_bi & 7) * 16) = x.a;
   };
 
   constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtF16, kTileF, kBlk, /*a_mn=*/1, /*b_mn=*/0);
   bool ok = true;
 
-  // prologue: blocks 0 .. kAhead-1 in flight
-#pragma unroll
-  for (int it = 0; it < kAhead; ++it) {
-    if (it < nblk) load_stage(it);
-    cp_async_commit();
-  }
-  for (int it = 0; it < nblk; ++it) {
-    cp_async_wait<kAhead - 1>();  // block `it` has landed (for this thread's copies)
+  // one pipeline step: block `it` (already in registers) -> shared memory -> tensor core, and
+  // the loads of block it+2 into the same registers; false when a bounded wait ran out
+  auto step = [&](int it, Pieces& x) -> bool {
+    const int stage = it % kStages;
+    if (it >= kStages) {  // the MMAs of block it-kStages are the previous use of this stage
+      if (!tc05::mbar_wait(&bar_free[stage], ((it - kStages) / kStages) & 1)) ok = false;
+    }
+    if (ok) store_block(stage, x);
+    if (it + 2 < nblk) load_block(it + 2, x);
     tc05::fence_async_smem();
-    __syncthreads();               // ... and for everybody's
+    if (__syncthreads_or(!ok)) return false;
     if (warp == 0 && lane == 0) {
       tc05::fence_after_sync();
-      const uint32_t sb = tc05::smem_u32(smem + (it % kStages) * kStageBytes);
+      const uint32_t sb = tc05::smem_u32(smem + stage * kStageBytes);
       const uint32_t sa = sb + kBBytes;
 #pragma unroll
       for (int ks = 0; ks < 2; ++ks) {  // K = 32 block columns = 2 x 16
@@ -123,22 +146,19 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
         const uint64_t db = tc05::smem_desc(sa + ks * 2 * kA_LBO, kA_LBO, kA_SBO);
         tc05::mma_f16(tmem, da, db, idesc, (it > 0 || ks > 0) ? 1u : 0u);
       }
-      tc05::mma_commit(&bar_free[it % kStages]);
+      tc05::mma_commit(&bar_free[stage]);
       if (it == nblk - 1) tc05::mma_commit(&bar_done);
     }
-    // refill the stage that block it-2 used with block it+kAhead (same stage modulo kStages)
-    const int nxt = it + kAhead;
-    if (nxt < nblk) {
-      if (it >= 2) {
-        // the MMAs of block it-2 are the ((it-2)/kStages)-th use of that stage
-        if (!tc05::mbar_wait(&bar_free[(it - 2) % kStages], ((it - 2) / kStages) & 1)) ok = false;
-      }
-      if (__syncthreads_or(!ok)) { ok = false; break; }
-      load_stage(nxt);
-    }
-    cp_async_commit();
+    return true;
+  };
+
+  Pieces x0, x1;
+  load_block(0, x0);
+  if (nblk > 1) load_block(1, x1);
+  for (int it = 0; it < nblk; it += 2) {
+    if (!step(it, x0)) { ok = false; break; }
+    if (it + 1 < nblk && !step(it + 1, x1)) { ok = false; break; }
   }
-  cp_async_wait<0>();
 
   if (ok && !tc05::mbar_wait(&bar_done, 0)) ok = false;
   ok = !__syncthreads_or(!ok);

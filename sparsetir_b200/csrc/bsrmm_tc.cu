@@ -12,9 +12,9 @@
 // Pipeline: operands travel global -> registers -> shared memory.  (Asynchronous 16-byte
 // copies straight into shared memory were measured at about 16 bytes per clock per SM on this
 // part, which capped the kernel at ~5 TB/s of L2 reads; plain 16-byte loads are not so limited.)
-// Every thread owns five 16-byte pieces of a block's operands and keeps TWO blocks in registers:
-// the loads of block it+2 are issued before the pieces of block it are multiplied, so the wait
-// for a load is hidden behind two iterations and behind the other thread blocks of the SM
+// Every thread owns five 16-byte pieces of a block's operands and keeps THREE blocks in registers:
+// the loads of block it+3 are issued before the pieces of block it are multiplied, so the wait
+// for a load is hidden behind three iterations and behind the other thread blocks of the SM
 // (3 stages = 30 KB, all 512 blocks of a 128 x 128-block matrix at 512 features are resident at
 // once).  The pieces are stored in the un-swizzled core-matrix layout the tensor core reads
 // (tc05.cuh), one elected thread issues the MMAs, tcgen05.commit arrives on the stage's mbarrier
@@ -40,6 +40,7 @@ constexpr int kThreads = 128;
 constexpr int kBlk = 32;
 constexpr int kTileF = 128;
 constexpr int kStages = 3;
+constexpr int kSets = 3;  // blocks a thread holds in registers (loaded, not yet stored to shared memory)
 constexpr int kBBytes = kBlk * kTileF * 2;  // B tile of one block: 32 x 128 fp16 = 8 KB
 constexpr int kABytes = kBlk * kBlk * 2;    // A block: 2 KB
 constexpr int kStageBytes = kBBytes + kABytes;
@@ -126,14 +127,14 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
   bool ok = true;
 
   // one pipeline step: block `it` (already in registers) -> shared memory -> tensor core, and
-  // the loads of block it+2 into the same registers; false when a bounded wait ran out
+  // the loads of block it+kSets into the same registers; false when a bounded wait ran out
   auto step = [&](int it, Pieces& x) -> bool {
     const int stage = it % kStages;
     if (it >= kStages) {  // the MMAs of block it-kStages are the previous use of this stage
       if (!tc05::mbar_wait(&bar_free[stage], ((it - kStages) / kStages) & 1)) ok = false;
     }
     if (ok) store_block(stage, x);
-    if (it + 2 < nblk) load_block(it + 2, x);
+    if (it + kSets < nblk) load_block(it + kSets, x);
     tc05::fence_async_smem();
     if (__syncthreads_or(!ok)) return false;
     if (warp == 0 && lane == 0) {
@@ -152,12 +153,15 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
     return true;
   };
 
-  Pieces x0, x1;
-  load_block(0, x0);
-  if (nblk > 1) load_block(1, x1);
-  for (int it = 0; it < nblk; it += 2) {
-    if (!step(it, x0)) { ok = false; break; }
-    if (it + 1 < nblk && !step(it + 1, x1)) { ok = false; break; }
+  Pieces x[kSets];
+#pragma unroll
+  for (int k = 0; k < kSets; ++k)
+    if (k < nblk) load_block(k, x[k]);
+  for (int it = 0; it < nblk && ok; it += kSets) {
+#pragma unroll
+    for (int k = 0; k < kSets; ++k) {
+      if (ok && it + k < nblk && !step(it + k, x[k])) ok = false;  // uniform: step ends in a barrier vote
+    }
   }
 
   if (ok && !tc05::mbar_wait(&bar_done, 0)) ok = false;

@@ -25,8 +25,12 @@
 // gives up cleanly (TMEM freed), so a protocol error cannot hang the GPU.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "common.h"
 #include "tc05.cuh"
+#include "tmap.h"
 #include "vec.cuh"
 
 namespace sptir {
@@ -180,6 +184,153 @@ bsrmm_tc_kernel(const __half* __restrict__ a, const __half* __restrict__ b, floa
   if (warp == 0) tc05::tmem_dealloc(tmem, kTmemCols);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// TMA-fed variant (the default): the same tiles and the same MMAs, but the operands are brought
+// in by the tensor memory accelerator.  Warp 0 is the producer: per stored block it waits for the
+// stage to be free, arms the stage's "full" mbarrier with the byte count and issues three tile
+// loads (two 64-feature x 32-row boxes of B with the 128-byte swizzle, one 32 x 32 box of A with
+// the 64-byte swizzle).  Warp 1 issues the MMAs when "full" completes and lets tcgen05.commit
+// arrive on the stage's "empty" mbarrier.  No thread touches the operands, there is no block-wide
+// barrier inside the loop, and the loads in flight are bounded by the stages (4 x 10 KB), not by
+// registers.  All four warps run the epilogue.
+constexpr int kTStages = 4;
+constexpr int kTmaSmem = kTStages * kStageBytes + 1024;  // + slack to align the tiles to 1024 bytes
+
+__global__ void __launch_bounds__(kThreads)
+bsrmm_tma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                 float* __restrict__ c, const int32_t* __restrict__ indptr,
+                 const int32_t* __restrict__ indices, int feat) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kTStages];   // operands of the stage have landed
+  __shared__ __align__(8) uint64_t bar_empty[kTStages];  // the tensor core has read the stage
+  __shared__ __align__(8) uint64_t bar_done;             // all MMAs of the row have finished
+  __shared__ uint32_t s_tmem;
+  const int i = blockIdx.x;
+  const int f0 = blockIdx.y * kTileF;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int p0 = __ldg(indptr + i), nblk = __ldg(indptr + i + 1) - p0;
+
+  float* crow = c + (static_cast<size_t>(i) * kBlk) * feat + f0 + warp * 32 + lane;
+  if (nblk <= 0) {  // empty block-row: zeros, no tensor-core work
+#pragma unroll 4
+    for (int bi = 0; bi < kBlk; ++bi) crow[static_cast<size_t>(bi) * feat] = 0.f;
+    return;
+  }
+  // swizzle atoms repeat every 1024 bytes of shared-memory address
+  unsigned char* tiles = smem_raw + ((1024u - (tc05::smem_u32(smem_raw) & 1023u)) & 1023u);
+
+  if (tid == 0) {
+    for (int s = 0; s < kTStages; ++s) {
+      tc05::mbar_init(&bar_full[s], 1);
+      tc05::mbar_init(&bar_empty[s], 1);
+    }
+    tc05::mbar_init(&bar_done, 1);
+    tc05::fence_mbar_init();
+    tc05::prefetch_tensormap(&tm_a);
+    tc05::prefetch_tensormap(&tm_b);
+  }
+  if (warp == 0) tc05::tmem_alloc(&s_tmem, kTmemCols);
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tmem = s_tmem;
+  constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtF16, kTileF, kBlk, /*a_mn=*/1, /*b_mn=*/0);
+  bool ok = true;
+  int armed = 0;  // producer: blocks whose loads have been issued
+
+  if (warp == 0) {
+    int cols = 0;
+    for (int it = 0; it < nblk; ++it) {
+      const int stage = it % kTStages, use = it / kTStages;
+      if ((it & 31) == 0) cols = (it + lane < nblk) ? __ldg(indices + p0 + it + lane) : 0;
+      const int col = __shfl_sync(0xffffffffu, cols, it & 31);
+      if (use > 0) {
+        if (lane == 0) ok = tc05::mbar_wait(&bar_empty[stage], (use - 1) & 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+      }
+      if (lane == 0) {
+        unsigned char* st = tiles + stage * kStageBytes;
+        tc05::mbar_arrive_expect_tx(&bar_full[stage], kStageBytes);
+        tc05::tma_load_2d(st, &tm_b, f0, col * kBlk, &bar_full[stage]);
+        tc05::tma_load_2d(st + kBBytes / 2, &tm_b, f0 + 64, col * kBlk, &bar_full[stage]);
+        tc05::tma_load_2d(st + kBBytes, &tm_a, 0, (p0 + it) * kBlk, &bar_full[stage]);
+      }
+      armed = it + 1;
+    }
+  } else if (warp == 1) {
+    for (int it = 0; it < nblk; ++it) {
+      const int stage = it % kTStages, use = it / kTStages;
+      if (lane == 0) ok = tc05::mbar_wait(&bar_full[stage], use & 1);
+      ok = __shfl_sync(0xffffffffu, ok, 0);
+      if (!ok) break;
+      if (lane == 0) {
+        tc05::fence_after_sync();
+        const uint32_t sb = tc05::smem_u32(tiles + stage * kStageBytes);
+        const uint32_t sa = sb + kBBytes;
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {  // K = 32 block columns = 2 x 16
+          // B tile, MN-major: 16 K rows of 128 bytes per step; the two 64-feature atoms are 4 KB apart
+          const uint64_t da = tc05::smem_desc_swizzled(sb + ks * 16 * 128, kBBytes / 2, 1024, tc05::kSwizzle128B);
+          // A block, K-major: rows of 64 bytes, 16 columns (32 bytes) per step inside the row
+          const uint64_t db = tc05::smem_desc_swizzled(sa + ks * 32, 0, 512, tc05::kSwizzle64B);
+          tc05::mma_f16(tmem, da, db, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+        }
+        tc05::mma_commit(&bar_empty[stage]);
+        if (it == nblk - 1) tc05::mma_commit(&bar_done);
+      }
+      __syncwarp();
+    }
+  }
+
+  if (ok && !tc05::mbar_wait(&bar_done, 0)) ok = false;
+  ok = !__syncthreads_or(!ok);
+  tc05::fence_after_sync();
+  if (ok) {
+    uint32_t r[32];
+    tc05::tmem_ld32(tmem + (static_cast<uint32_t>(warp * 32) << 16), r);
+#pragma unroll
+    for (int bi = 0; bi < kBlk; ++bi) __stcs(crow + static_cast<size_t>(bi) * feat, __uint_as_float(r[bi]));
+  } else {
+    // gave up: let the copies already issued land (bounded) before the block's memory is released
+    if (tid == 0) {
+      atomicAdd(&g_tc_timeouts, 1u);
+      for (int it = max(0, armed - kTStages); it < armed; ++it)
+        tc05::mbar_wait(&bar_full[it % kTStages], (it / kTStages) & 1);
+    }
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc05::tmem_dealloc(tmem, kTmemCols);
+}
+
+// 0 when launched, 1 when this path cannot take the call (caller falls back), -1 on error
+int bsrmm_tma_launch(const __half* a, const __half* b, float* c, const int32_t* indptr,
+                     const int32_t* indices, int nb, int mb, int nnzb, int feat, cudaStream_t stream) {
+  if (nnzb <= 0 || mb <= 0) return 1;
+  CUtensorMap tm_a, tm_b;
+  if (make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, kBlk, static_cast<uint64_t>(nnzb) * kBlk,
+                   kBlk * 2, kBlk, kBlk, CU_TENSOR_MAP_SWIZZLE_64B) != 0)
+    return 1;
+  if (make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, b, static_cast<uint64_t>(feat),
+                   static_cast<uint64_t>(mb) * kBlk, static_cast<uint64_t>(feat) * 2, 64, kBlk,
+                   CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return 1;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  SPTIR_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(bsrmm_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kTmaSmem));
+    configured_device = dev;
+  }
+  dim3 grid(nb, feat / kTileF);
+  bsrmm_tma_kernel<<<grid, kThreads, kTmaSmem, stream>>>(tm_a, tm_b, c, indptr, indices, feat);
+  SPTIR_LAUNCH_OK("bsrmm_tma_kernel");
+  return 0;
+}
+
 }  // namespace
 
 // Returns 0 when launched, 1 when the shape is not handled here, -1 on error.
@@ -190,6 +341,15 @@ int bsrmm_tc_launch(const __half* a, const __half* b, float* c, const int32_t* i
   if (blk != kBlk || feat % kTileF != 0) return 1;
   if (!aligned16(a) || !aligned16(b) || !aligned16(c)) return 1;
   if (feat / kTileF > 65535) return 1;
+  // SPARSETIR_BSR_PATH=regs keeps the operands on the load/store path (comparison switch)
+  static const bool use_tma = [] {
+    const char* e = std::getenv("SPARSETIR_BSR_PATH");
+    return !(e && std::strcmp(e, "regs") == 0);
+  }();
+  if (use_tma) {
+    const int rc = bsrmm_tma_launch(a, b, c, indptr, indices, nb, mb, nnzb, feat, stream);
+    if (rc <= 0) return rc;
+  }
   const size_t smem = static_cast<size_t>(kStages) * kStageBytes;
   static thread_local int configured_device = -1;
   int dev = 0;

@@ -37,6 +37,25 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
   return d;         // base offset 0, layout type 0 (no swizzle)
 }
 
+// Swizzled operand layouts (what a TMA tile load with the same swizzle mode writes): rows of
+// 128 / 64 / 32 bytes whose 16-byte chunks are XORed with the row number inside an 8-row atom.
+//   K-major : a row is one M/N index; SBO = byte stride between 8-row groups; LBO unused; a K step
+//             inside the swizzled row is taken by advancing the start address.
+//   MN-major: a row is one K index holding 64 / 32 / 16 ... contiguous M/N elements; SBO = byte
+//             stride between groups of 8 K rows, LBO = byte stride between row-wide M/N atoms.
+// Atoms must start on a multiple of 8 rows (1024 / 512 / 256 bytes).
+enum : uint64_t { kSwizzleNone = 0, kSwizzle128B = 2, kSwizzle64B = 4, kSwizzle32B = 6 };
+__device__ __forceinline__ uint64_t smem_desc_swizzled(uint32_t addr, uint32_t lbo_bytes,
+                                                       uint32_t sbo_bytes, uint64_t swizzle) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr >> 4) & 0x3FFFu);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;  // descriptor version of this architecture
+  d |= swizzle << 61;
+  return d;
+}
+
 enum : uint32_t { kFmtF16 = 0, kFmtBF16 = 1, kFmtTF32 = 2 };
 
 // 32-bit instruction descriptor: fp32 accumulate, dense, no negation.
@@ -73,6 +92,26 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     if (done) return true;
   }
   return false;
+}
+
+// Producer side of a TMA pipeline: one arrival plus the number of bytes the copies will deliver.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+// 2-D tiled TMA load into this block's shared memory; completes on `bar` with the tile's bytes.
+// x (innermost coordinate) times the element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tensor_map, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(tensor_map), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tensormap(const void* tensor_map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tensor_map) : "memory");
 }
 
 // TMEM allocation: executed by one whole warp; the base address lands in shared memory.

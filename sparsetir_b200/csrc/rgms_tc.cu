@@ -19,7 +19,11 @@
 #include "common.h"
 #include "rgms_common.cuh"
 #include "spmm_core.cuh"
+#include <cstdlib>
+#include <cstring>
+
 #include "tc05.cuh"
+#include "tmap.h"
 
 namespace sptir {
 
@@ -213,6 +217,296 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
   if (warp == 0) tc05::tmem_dealloc(tmem, kF);
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// TMA-fed, warp-specialised form for the two-launch path (rows already aggregated in z).
+// One persistent block per SM walks consecutive tiles; its 12 warps are four roles that hand
+// tiles to each other through mbarriers, so loading, splitting, multiplying and scattering of
+// different tiles overlap:
+//   warp 0      producer: two TMA tile loads (128 rows x 128 bytes, 128-byte swizzle) bring the
+//               tile's z rows into one of two stages;
+//   warps 8-11  converters: the tensor core reads only the upper 19 bits of an fp32 operand, so
+//               the raw tile serves as the "high" part as it is; the converters compute the
+//               remainder z - tf32(z) element by element into a second buffer at the same
+//               (swizzled) offsets, and stage W_r (raw and remainder) when the relation changes;
+//   warp 1      issues the 8 K-steps x 3 products (3xTF32 as above) into one of two TMEM
+//               accumulators, tcgen05.commit frees the stage and publishes the accumulator;
+//   warps 4-7   epilogue: TMEM -> registers -> one padded row of shared memory per thread -> one
+//               bulk reduce-add (cp.reduce.async.bulk, 256 bytes) of that row into Y[I[t], :].
+// Every mbarrier wait is bounded.
+constexpr int kPThreads = 384;
+constexpr int kZStages = 2;
+constexpr int kZBox = kTM * 128;     // one swizzled box: 128 rows x 32 floats
+constexpr int kZTile = 2 * kZBox;    // 32 KB
+constexpr int kWBox = kF * 128;      // 64 rows x 32 floats
+constexpr int kWPart = 2 * kWBox;    // 16 KB
+constexpr int kOutStride = kF * 4 + 16;  // padded row: 16-byte stores of 32 rows spread over all banks
+constexpr int kOffZRaw = 0;
+constexpr int kOffZLo = kOffZRaw + kZStages * kZTile;
+constexpr int kOffWHi = kOffZLo + kZStages * kZTile;
+constexpr int kOffWLo = kOffWHi + kWPart;
+constexpr int kOffOut = kOffWLo + kWPart;
+constexpr int kPSmemBytes = kOffOut + kTM * kOutStride + 1024;  // + slack to align to 1024 bytes
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc05::smem_u32(bar)) : "memory");
+}
+// offset of 16-byte chunk `kc` (0..15) of row `row` in a tile stored as two 128-byte-swizzled boxes
+__device__ __forceinline__ int swz_off(int row, int kc, int box_bytes) {
+  return (kc >> 3) * box_bytes + (row >> 3) * 1024 + (row & 7) * 128 + (((kc & 7) ^ (row & 7)) << 4);
+}
+
+// Which relation and row range tile `tile_id` covers; called by the 32 lanes of one warp.
+__device__ inline bool locate_tile_warp(const int32_t* __restrict__ indptr_i, int num_rels,
+                                        int tile_id, int lane, int* rel, int* row0, int* row1) {
+  int base = 0;
+  for (int r0 = 0; r0 < num_rels; r0 += 32) {
+    const int r = r0 + lane;
+    int s = 0, e = 0, nt = 0;
+    if (r < num_rels) {
+      s = __ldg(indptr_i + r);
+      e = __ldg(indptr_i + r + 1);
+      nt = (e - s + kTM - 1) / kTM;
+    }
+    int incl = nt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const int excl = base + incl - nt;
+    const bool mine = tile_id >= excl && tile_id < excl + nt;
+    const unsigned hit = __ballot_sync(0xffffffffu, mine);
+    if (hit != 0) {
+      const int src = __ffs(hit) - 1;
+      *rel = __shfl_sync(0xffffffffu, r, src);
+      *row0 = __shfl_sync(0xffffffffu, s + (tile_id - excl) * kTM, src);
+      *row1 = __shfl_sync(0xffffffffu, min(e, s + (tile_id - excl + 1) * kTM), src);
+      return true;
+    }
+    base += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  return false;
+}
+
+struct TileWalk {
+  int rel, row0, row1;
+  // steps to the tile after this one; false when there is none
+  __device__ __forceinline__ bool next(const int32_t* __restrict__ indptr_i, int num_rels) {
+    int nrel = rel;
+    const int nrow0 = row1;
+    int rel_end = __ldg(indptr_i + rel + 1);
+    while (nrel < num_rels && nrow0 >= rel_end) {
+      ++nrel;
+      if (nrel < num_rels) rel_end = __ldg(indptr_i + nrel + 1);
+    }
+    if (nrel >= num_rels) return false;
+    rel = nrel;
+    row0 = nrow0;
+    row1 = min(rel_end, nrow0 + kTM);
+    return true;
+  }
+};
+
+__global__ void __launch_bounds__(kPThreads, 1)
+rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restrict__ w,
+                float* __restrict__ y, const int32_t* __restrict__ indptr_i,
+                const int32_t* __restrict__ indices_i, int num_rels, int tiles_per_cta) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kZStages];   // z rows of the stage have landed
+  __shared__ __align__(8) uint64_t bar_conv[kZStages];   // remainders written (128 arrivals)
+  __shared__ __align__(8) uint64_t bar_empty[kZStages];  // tensor core has read the stage
+  __shared__ __align__(8) uint64_t bar_acc_full[2];      // accumulator holds a finished tile
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];     // epilogue has read it (128 arrivals)
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_tile[4];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  unsigned char* base = smem_raw + ((1024u - (tc05::smem_u32(smem_raw) & 1023u)) & 1023u);
+
+  if (warp == 0) {
+    int rel, row0, row1;
+    const bool found = locate_tile_warp(indptr_i, num_rels, blockIdx.x * tiles_per_cta, lane, &rel, &row0, &row1);
+    if (lane == 0) {
+      s_tile[0] = found ? 1 : 0; s_tile[1] = rel; s_tile[2] = row0; s_tile[3] = row1;
+      for (int s = 0; s < kZStages; ++s) {
+        tc05::mbar_init(&bar_full[s], 1);
+        tc05::mbar_init(&bar_conv[s], 128);
+        tc05::mbar_init(&bar_empty[s], 1);
+      }
+      for (int b = 0; b < 2; ++b) {
+        tc05::mbar_init(&bar_acc_full[b], 1);
+        tc05::mbar_init(&bar_acc_empty[b], 128);
+      }
+      tc05::fence_mbar_init();
+      tc05::prefetch_tensormap(&tm_z);
+    }
+    __syncwarp();
+    tc05::tmem_alloc(&s_tmem, 2 * kF);
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  if (s_tile[0] == 0) {  // no tile for this block (uniform)
+    if (warp == 0) tc05::tmem_dealloc(s_tmem, 2 * kF);
+    return;
+  }
+  const uint32_t tmem = s_tmem;
+  TileWalk tw{s_tile[1], s_tile[2], s_tile[3]};
+  bool ok = true;
+  int armed = 0;
+
+  if (warp == 0) {
+    // ---- producer
+    if (lane == 0) {
+      for (int k = 0; k < tiles_per_cta; ++k) {
+        const int s = k % kZStages, use = k / kZStages;
+        if (use > 0 && !tc05::mbar_wait(&bar_empty[s], (use - 1) & 1)) { ok = false; break; }
+        unsigned char* dst = base + kOffZRaw + s * kZTile;
+        tc05::mbar_arrive_expect_tx(&bar_full[s], kZTile);
+        tc05::tma_load_2d(dst, &tm_z, 0, tw.row0, &bar_full[s]);
+        tc05::tma_load_2d(dst + kZBox, &tm_z, 32, tw.row0, &bar_full[s]);
+        armed = k + 1;
+        if (k + 1 == tiles_per_cta || !tw.next(indptr_i, num_rels)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtTF32, kTM, kF, /*a_mn=*/0, /*b_mn=*/0);
+      const uint32_t wh = tc05::smem_u32(base + kOffWHi), wl = tc05::smem_u32(base + kOffWLo);
+      for (int k = 0; k < tiles_per_cta; ++k) {
+        const int s = k % kZStages, use = k / kZStages, buf = k & 1, buse = k >> 1;
+        if (!tc05::mbar_wait(&bar_conv[s], use & 1)) { ok = false; break; }
+        if (buse > 0 && !tc05::mbar_wait(&bar_acc_empty[buf], (buse - 1) & 1)) { ok = false; break; }
+        tc05::fence_after_sync();
+        const uint32_t zh = tc05::smem_u32(base + kOffZRaw + s * kZTile);
+        const uint32_t zl = tc05::smem_u32(base + kOffZLo + s * kZTile);
+        const uint32_t acc = tmem + buf * kF;
+#pragma unroll
+        for (int ks = 0; ks < kF / 8; ++ks) {  // K = 8 floats = 32 bytes inside the swizzled row
+          const uint32_t zo = (ks >> 2) * kZBox + (ks & 3) * 32, wo = (ks >> 2) * kWBox + (ks & 3) * 32;
+          const uint64_t dzh = tc05::smem_desc_swizzled(zh + zo, 0, 1024, tc05::kSwizzle128B);
+          const uint64_t dzl = tc05::smem_desc_swizzled(zl + zo, 0, 1024, tc05::kSwizzle128B);
+          const uint64_t dwh = tc05::smem_desc_swizzled(wh + wo, 0, 1024, tc05::kSwizzle128B);
+          const uint64_t dwl = tc05::smem_desc_swizzled(wl + wo, 0, 1024, tc05::kSwizzle128B);
+          tc05::mma_tf32(acc, dzl, dwh, idesc, ks > 0 ? 1u : 0u);  // small terms first
+          tc05::mma_tf32(acc, dzh, dwl, idesc, 1u);
+          tc05::mma_tf32(acc, dzh, dwh, idesc, 1u);
+        }
+        tc05::mma_commit(&bar_empty[s]);
+        tc05::mma_commit(&bar_acc_full[buf]);
+        if (k + 1 == tiles_per_cta || !tw.next(indptr_i, num_rels)) break;
+      }
+    }
+  } else if (warp >= 8) {
+    // ---- converters
+    const int ct = tid - 256;
+    int staged_rel = -1;
+    for (int k = 0; k < tiles_per_cta; ++k) {
+      const int s = k % kZStages, use = k / kZStages;
+      if (tw.rel != staged_rel) {
+        // the MMAs of the previous tile are the last readers of the staged W
+        if (k > 0 && !tc05::mbar_wait(&bar_empty[(k - 1) % kZStages], ((k - 1) / kZStages) & 1)) { ok = false; break; }
+        staged_rel = tw.rel;
+        const float4* wr = reinterpret_cast<const float4*>(w + static_cast<size_t>(tw.rel) * kF * kF);
+        for (int ch = ct; ch < kF * kF / 4; ch += 128) {
+          const int fo = ch >> 4, kc = ch & 15;
+          const float4 v = __ldg(wr + ch);
+          const float4 l = make_float4(v.x - tf32_hi(v.x), v.y - tf32_hi(v.y), v.z - tf32_hi(v.z), v.w - tf32_hi(v.w));
+          const int off = swz_off(fo, kc, kWBox);
+          *reinterpret_cast<float4*>(base + kOffWHi + off) = v;
+          *reinterpret_cast<float4*>(base + kOffWLo + off) = l;
+        }
+      }
+      if (!tc05::mbar_wait(&bar_full[s], use & 1)) { ok = false; break; }
+      const unsigned char* zr = base + kOffZRaw + s * kZTile;
+      unsigned char* zl = base + kOffZLo + s * kZTile;
+#pragma unroll 4
+      for (int j = 0; j < kZTile / 16 / 128; ++j) {
+        const int off = (j * 128 + ct) * 16;
+        const float4 v = *reinterpret_cast<const float4*>(zr + off);
+        *reinterpret_cast<float4*>(zl + off) =
+            make_float4(v.x - tf32_hi(v.x), v.y - tf32_hi(v.y), v.z - tf32_hi(v.z), v.w - tf32_hi(v.w));
+      }
+      tc05::fence_async_smem();
+      mbar_arrive(&bar_conv[s]);
+      if (k + 1 == tiles_per_cta || !tw.next(indptr_i, num_rels)) break;
+    }
+  } else if (warp >= 4) {
+    // ---- epilogue: thread = tile row = TMEM lane
+    const int t = tid - 128;
+    unsigned char* my_row = base + kOffOut + t * kOutStride;
+    for (int k = 0; k < tiles_per_cta; ++k) {
+      const int buf = k & 1, buse = k >> 1;
+      const int nrows = tw.row1 - tw.row0;
+      const int dst_row = t < nrows ? __ldg(indices_i + tw.row0 + t) : 0;
+      if (!tc05::mbar_wait(&bar_acc_full[buf], buse & 1)) { ok = false; break; }
+      tc05::fence_after_sync();
+      uint32_t r0[32], r1[32];
+      const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + buf * kF;
+      tc05::tmem_ld32(taddr, r0);
+      tc05::tmem_ld32(taddr + 32, r1);
+      tc05::fence_before_sync();
+      mbar_arrive(&bar_acc_empty[buf]);
+      // the bulk reduce of the previous tile has read this thread's row
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        *reinterpret_cast<uint4*>(my_row + q * 16) = make_uint4(r0[4 * q], r0[4 * q + 1], r0[4 * q + 2], r0[4 * q + 3]);
+        *reinterpret_cast<uint4*>(my_row + 128 + q * 16) = make_uint4(r1[4 * q], r1[4 * q + 1], r1[4 * q + 2], r1[4 * q + 3]);
+      }
+      tc05::fence_async_smem();
+      if (t < nrows) {
+        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(
+                         y + static_cast<size_t>(dst_row) * kF),
+                     "r"(tc05::smem_u32(my_row)), "r"(kF * 4)
+                     : "memory");
+      }
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+      if (k + 1 == tiles_per_cta || !tw.next(indptr_i, num_rels)) break;
+    }
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // reduces done before the block ends
+  }
+
+  const bool all_ok = !__syncthreads_or(!ok);
+  if (!all_ok && tid == 0) {
+    atomicAdd(&g_rgms_tc_timeouts, 1u);
+    // gave up: let the tile loads already issued land (bounded) before the block's memory is released
+    for (int k = max(0, armed - kZStages); k < armed; ++k)
+      tc05::mbar_wait(&bar_full[k % kZStages], (k / kZStages) & 1);
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc05::tmem_dealloc(tmem, 2 * kF);
+}
+
+// 0 when launched, 1 when this path cannot take the call (caller falls back), -1 on error
+int rgms_tma_launch(const float* w, float* y, const int32_t* indptr_i, const int32_t* indices_i,
+                    int num_rels, int nnz_i, const float* z, cudaStream_t stream) {
+  if (nnz_i <= 0 || num_rels <= 0) return 1;
+  if ((reinterpret_cast<uintptr_t>(z) & 15u) || (reinterpret_cast<uintptr_t>(y) & 15u) ||
+      (reinterpret_cast<uintptr_t>(w) & 15u))
+    return 1;
+  CUtensorMap tm_z;
+  if (make_tmap_2d(&tm_z, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, z, kF, static_cast<uint64_t>(nnz_i), kF * 4, 32,
+                   kTM, CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return 1;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  SPTIR_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(rgms_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmemBytes));
+    configured_device = dev;
+  }
+  const long long tiles = static_cast<long long>(nnz_i) / kTM + num_rels;  // upper bound
+  const long long grid = tiles < kNumSMs ? tiles : kNumSMs;
+  const int tiles_per_cta = static_cast<int>((tiles + grid - 1) / grid);
+  rgms_tma_kernel<<<static_cast<unsigned>(grid), kPThreads, kPSmemBytes, stream>>>(
+      tm_z, w, y, indptr_i, indices_i, num_rels, tiles_per_cta);
+  SPTIR_LAUNCH_OK("rgms_tma_kernel");
+  return 0;
+}
+
 }  // namespace
 
 // Returns 0 when launched, 1 when the shape is not handled here, -1 on error.
@@ -222,6 +516,15 @@ int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,
                    const int32_t* indices_j, int num_rels, int feat, int nnz_i,
                    const float* z, cudaStream_t stream) {
   if (feat != kF) return 1;
+  // SPARSETIR_RGMS_PATH=regs keeps the tile on the load/store path (comparison switch)
+  static const bool use_tma = [] {
+    const char* e = std::getenv("SPARSETIR_RGMS_PATH");
+    return !(e && std::strcmp(e, "regs") == 0);
+  }();
+  if (z != nullptr && use_tma) {
+    const int rc = rgms_tma_launch(w, y, indptr_i, indices_i, num_rels, nnz_i, z, stream);
+    if (rc <= 0) return rc;
+  }
   static thread_local int configured_device = -1;
   int dev = 0;
   SPTIR_CUDA_OK(cudaGetDevice(&dev));

@@ -373,7 +373,11 @@ def ours_arm(args, rank, world, local_rank):
     alg_bytes = spmm_bytes(m_loc, g.n, nnz_loc, f_dom)
     achieved = alg_bytes / (per_f_ms[f_dom] * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / peaks["hbm_gbs"], "traffic": None, "peak_source": peaks["source"],
+                "frac": achieved / peaks["hbm_gbs"],
+                # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the committed ncu
+                # capture of the same workload (profiles/hyb_spmm_lean_kernel_F512.md), one GPU
+                "traffic": 690.9e6 if (world == 1 and FEATS[-1] == 512) else None,
+                "peak_source": peaks["source"],
                 "kernel": "hyb_spmm_lean_kernel<32> (+ hyb_rearm_kernel), F=512 call",
                 "algorithmic_bytes": alg_bytes, "launch_ms": per_f_ms[f_dom]}
     per_f = {}

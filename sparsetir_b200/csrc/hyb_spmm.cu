@@ -189,8 +189,14 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
   };
   auto row_end = [&](V& acc, int rf) {
     char* dst = const_cast<char*>(vec_of(cl, rf & 0x7fffffff));
-    if (rf < 0) LV::atomic_add(dst, acc);
-    else LV::stcs(dst, acc);  // written once: do not displace B rows in L2
+    if (rf < 0) {
+      // rows accumulated atomically were cleared by the re-arm launch, which may still be running
+      // when this kernel was started as its programmatic dependent (returns at once otherwise)
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      LV::atomic_add(dst, acc);
+    } else {
+      LV::stcs(dst, acc);  // written once: do not displace B rows in L2
+    }
     acc = LV::zero();
   };
 
@@ -430,6 +436,9 @@ hyb_spmm_async_kernel(const __grid_constant__ HybTable tb, const float* __restri
 // are rare, and each is then cleared by the whole warp.
 __global__ void __launch_bounds__(kThreads)
 hyb_rearm_kernel(const __grid_constant__ HybTable tb, float* __restrict__ c, int feat) {
+  // the SpMM launch that follows may start now (programmatic dependent launch): it synchronises
+  // with this grid's completion only before its first atomic accumulation
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int q = find_bucket(tb, blockIdx.x);
   const int nrows = tb.nrows[q];
   const int32_t* __restrict__ rows = tb.rows[q];
@@ -499,10 +508,25 @@ long long plan_blocks(HybTable& tb, int subs) {
 
 template <int LPR, int W>
 int launch_lean(HybTable& tb, const float* b, float* c, int feat, int all_atomic,
-                cudaStream_t stream) {
+                cudaStream_t stream, bool after_rearm) {
   const long long blocks = plan_blocks(tb, kThreads / LPR);
   if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
   dim3 grid(static_cast<unsigned>(blocks), feat / (W * LPR));
+  if (after_rearm) {
+    // start while the re-arm launch of this call is still running; see hyb_rearm_kernel
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    SPTIR_CUDA_OK(cudaLaunchKernelEx(&cfg, hyb_spmm_lean_kernel<LPR, W>, tb, b, c, feat, all_atomic));
+    return 0;
+  }
   hyb_spmm_lean_kernel<LPR, W><<<grid, kThreads, 0, stream>>>(tb, b, c, feat, all_atomic);
   SPTIR_LAUNCH_OK("hyb_spmm_lean_kernel");
   return 0;
@@ -593,6 +617,7 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
   lean = lean && feat % (lane_w * lanes) == 0;
   plan_items(tb, lean ? lean_item_slots(lanes, lane_w) : item_slots(lanes));
 
+  bool after_rearm = false;  // this call's re-arm kernel directly precedes the SpMM launch
   if (flags & SPARSETIR_HYB_ZERO_C) {
     SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(m) * feat * sizeof(float), st));
   } else if (flags & SPARSETIR_HYB_REARM) {
@@ -608,21 +633,22 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
       if (blocks > INT32_MAX) return fail("sparsetir_hyb_spmm: too many thread blocks");
       hyb_rearm_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(tb, c, feat);
       SPTIR_LAUNCH_OK("hyb_rearm_kernel");
+      after_rearm = true;
     }
   }
   if (tb.nb == 0) return 0;
 
   if (vec4) {
     if (lean && lane_w == 8) {
-      if (lanes == 4) return launch_lean<4, 8>(tb, b, c, feat, all_atomic, st);
-      if (lanes == 8) return launch_lean<8, 8>(tb, b, c, feat, all_atomic, st);
-      if (lanes == 16) return launch_lean<16, 8>(tb, b, c, feat, all_atomic, st);
-      return launch_lean<32, 8>(tb, b, c, feat, all_atomic, st);
+      if (lanes == 4) return launch_lean<4, 8>(tb, b, c, feat, all_atomic, st, after_rearm);
+      if (lanes == 8) return launch_lean<8, 8>(tb, b, c, feat, all_atomic, st, after_rearm);
+      if (lanes == 16) return launch_lean<16, 8>(tb, b, c, feat, all_atomic, st, after_rearm);
+      return launch_lean<32, 8>(tb, b, c, feat, all_atomic, st, after_rearm);
     }
     if (lean) {
-      if (lanes == 8) return launch_lean<8, 4>(tb, b, c, feat, all_atomic, st);
-      if (lanes == 16) return launch_lean<16, 4>(tb, b, c, feat, all_atomic, st);
-      return launch_lean<32, 4>(tb, b, c, feat, all_atomic, st);
+      if (lanes == 8) return launch_lean<8, 4>(tb, b, c, feat, all_atomic, st, after_rearm);
+      if (lanes == 16) return launch_lean<16, 4>(tb, b, c, feat, all_atomic, st, after_rearm);
+      return launch_lean<32, 4>(tb, b, c, feat, all_atomic, st, after_rearm);
     }
     if (lanes == 8) return launch_async<8>(tb, b, c, feat, all_atomic, st);
     if (lanes == 16) return launch_async<16>(tb, b, c, feat, all_atomic, st);

@@ -220,7 +220,7 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
 
 // ---------------------------------------------------------------------------------------------
 // TMA-fed, warp-specialised form for the two-launch path (rows already aggregated in z).
-// One persistent block per SM walks consecutive tiles; its 12 warps are four roles that hand
+// One persistent block per SM walks consecutive tiles; its 16 warps are four roles that hand
 // tiles to each other through mbarriers, so loading, splitting, multiplying and scattering of
 // different tiles overlap:
 //   warp 0      producer: two TMA tile loads (128 rows x 128 bytes, 128-byte swizzle) bring the
@@ -231,22 +231,25 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
 //               (swizzled) offsets, and stage W_r (raw and remainder) when the relation changes;
 //   warp 1      issues the 8 K-steps x 3 products (3xTF32 as above) into one of two TMEM
 //               accumulators, tcgen05.commit frees the stage and publishes the accumulator;
-//   warps 4-7   epilogue: TMEM -> registers -> one padded row of shared memory per thread -> one
-//               bulk reduce-add (cp.reduce.async.bulk, 256 bytes) of that row into Y[I[t], :].
+//   warps 4-7, 12-15  epilogue (even / odd tiles): TMEM -> registers -> one padded half row of
+//               shared memory per thread -> read back 8 lanes per row -> 16-byte vector atomics
+//               into Y[I[t], :], four whole 128-byte lines per warp instruction.  (One bulk reduce-add per row, cp.reduce.async.bulk, was
+//               measured first: the block issues a bulk operation only every ~20 clocks, which
+//               made the epilogue the slowest role at 3,200 clocks per tile.)
 // Every mbarrier wait is bounded.
-constexpr int kPThreads = 384;
+constexpr int kPThreads = 512;
 constexpr int kZStages = 2;
 constexpr int kZBox = kTM * 128;     // one swizzled box: 128 rows x 32 floats
 constexpr int kZTile = 2 * kZBox;    // 32 KB
 constexpr int kWBox = kF * 128;      // 64 rows x 32 floats
 constexpr int kWPart = 2 * kWBox;    // 16 KB
-constexpr int kOutStride = kF * 4 + 16;  // padded row: 16-byte stores of 32 rows spread over all banks
+constexpr int kOutStride = 128 + 16;  // padded half row: 16-byte stores of 32 rows spread over all banks
 constexpr int kOffZRaw = 0;
 constexpr int kOffZLo = kOffZRaw + kZStages * kZTile;
 constexpr int kOffWHi = kOffZLo + kZStages * kZTile;
 constexpr int kOffWLo = kOffWHi + kWPart;
 constexpr int kOffOut = kOffWLo + kWPart;
-constexpr int kPSmemBytes = kOffOut + kTM * kOutStride + 1024;  // + slack to align to 1024 bytes
+constexpr int kPSmemBytes = kOffOut + 2 * kTM * kOutStride + 1024;  // two epilogue groups; + slack to align to 1024 bytes
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc05::smem_u32(bar)) : "memory");
@@ -290,18 +293,15 @@ __device__ inline bool locate_tile_warp(const int32_t* __restrict__ indptr_i, in
 }
 
 struct TileWalk {
-  int rel, row0, row1;
-  // steps to the tile after this one; false when there is none
+  int rel, row0, row1, rel_end;  // rel_end: first row past the relation (cached indptr_i[rel + 1])
+  // steps to the tile after this one; false when there is none.  Inside a relation this costs no
+  // memory access; the row pointer is read again only when the relation changes.
   __device__ __forceinline__ bool next(const int32_t* __restrict__ indptr_i, int num_rels) {
-    int nrel = rel;
     const int nrow0 = row1;
-    int rel_end = __ldg(indptr_i + rel + 1);
-    while (nrel < num_rels && nrow0 >= rel_end) {
-      ++nrel;
-      if (nrel < num_rels) rel_end = __ldg(indptr_i + nrel + 1);
+    while (nrow0 >= rel_end) {
+      if (++rel >= num_rels) return false;
+      rel_end = __ldg(indptr_i + rel + 1);
     }
-    if (nrel >= num_rels) return false;
-    rel = nrel;
     row0 = nrow0;
     row1 = min(rel_end, nrow0 + kTM);
     return true;
@@ -311,7 +311,7 @@ struct TileWalk {
 __global__ void __launch_bounds__(kPThreads, 1)
 rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restrict__ w,
                 float* __restrict__ y, const int32_t* __restrict__ indptr_i,
-                const int32_t* __restrict__ indices_i, int num_rels, int tiles_per_cta) {
+                const int32_t* __restrict__ indices_i, int num_rels, int nnz_i, int tiles_per_cta) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kZStages];   // z rows of the stage have landed
   __shared__ __align__(8) uint64_t bar_conv[kZStages];   // remainders written (128 arrivals)
@@ -351,7 +351,7 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
     return;
   }
   const uint32_t tmem = s_tmem;
-  TileWalk tw{s_tile[1], s_tile[2], s_tile[3]};
+  TileWalk tw{s_tile[1], s_tile[2], s_tile[3], __ldg(indptr_i + s_tile[1] + 1)};
   bool ok = true;
   int armed = 0;
 
@@ -398,7 +398,7 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
         if (k + 1 == tiles_per_cta || !tw.next(indptr_i, num_rels)) break;
       }
     }
-  } else if (warp >= 8) {
+  } else if (warp >= 8 && warp < 12) {
     // ---- converters
     const int ct = tid - 256;
     int staged_rel = -1;
@@ -433,39 +433,57 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
       if (k + 1 == tiles_per_cta || !tw.next(indptr_i, num_rels)) break;
     }
   } else if (warp >= 4) {
-    // ---- epilogue: thread = tile row = TMEM lane
-    const int t = tid - 128;
-    unsigned char* my_row = base + kOffOut + t * kOutStride;
-    for (int k = 0; k < tiles_per_cta; ++k) {
-      const int buf = k & 1, buse = k >> 1;
-      const int nrows = tw.row1 - tw.row0;
-      const int dst_row = t < nrows ? __ldg(indices_i + tw.row0 + t) : 0;
-      if (!tc05::mbar_wait(&bar_acc_full[buf], buse & 1)) { ok = false; break; }
+    // ---- epilogue, two groups of four warps: group 0 (warps 4-7) takes the even tiles and
+    // accumulator 0, group 1 (warps 12-15) the odd tiles and accumulator 1, so that one group
+    // reads TMEM and transposes while the other is busy issuing its atomics.
+    // thread = tile row = TMEM lane
+    const int grp = warp >= 12 ? 1 : 0;
+    const int t = (warp & 3) * 32 + lane;
+    unsigned char* gbuf = base + kOffOut + grp * (kTM * kOutStride);
+    unsigned char* my_row = gbuf + t * kOutStride;
+    const unsigned char* wbase = gbuf + (warp & 3) * 32 * kOutStride;
+    bool have = true;
+    if (grp == 1) have = tiles_per_cta > 1 && tw.next(indptr_i, num_rels);
+    int nrows = tw.row1 - tw.row0;
+    int dst_row = __ldg(indices_i + min(tw.row0 + t, nnz_i - 1));
+    for (int k = grp; have && k < tiles_per_cta; k += 2) {
+      const int buse = k >> 1;
+      // destination rows of this group's next tile (two tiles on): requested now, needed later
+      bool has_next = (k + 2 < tiles_per_cta) && tw.next(indptr_i, num_rels);
+      has_next = has_next && tw.next(indptr_i, num_rels);
+      const int dst_next = __ldg(indices_i + min(tw.row0 + t, nnz_i - 1));
+      if (!tc05::mbar_wait(&bar_acc_full[grp], buse & 1)) { ok = false; break; }
       tc05::fence_after_sync();
-      uint32_t r0[32], r1[32];
-      const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + buf * kF;
-      tc05::tmem_ld32(taddr, r0);
-      tc05::tmem_ld32(taddr + 32, r1);
-      tc05::fence_before_sync();
-      mbar_arrive(&bar_acc_empty[buf]);
-      // the bulk reduce of the previous tile has read this thread's row
-      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + grp * kF;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        *reinterpret_cast<uint4*>(my_row + q * 16) = make_uint4(r0[4 * q], r0[4 * q + 1], r0[4 * q + 2], r0[4 * q + 3]);
-        *reinterpret_cast<uint4*>(my_row + 128 + q * 16) = make_uint4(r1[4 * q], r1[4 * q + 1], r1[4 * q + 2], r1[4 * q + 3]);
+      for (int half = 0; half < 2; ++half) {  // 32 columns at a time
+        uint32_t r[32];
+        tc05::tmem_ld32(taddr + half * 32, r);
+        if (half == 1) {  // both halves are in registers or on their way to Y: accumulator free
+          tc05::fence_before_sync();
+          mbar_arrive(&bar_acc_empty[grp]);
+        }
+        // transpose through shared memory: a thread holds one row, the reductions want a row
+        // spread over 8 lanes (four whole 128-byte lines per warp instruction)
+        __syncwarp();  // the warp's reads of the previous half are over
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(my_row + q * 16) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+        __syncwarp();
+#pragma unroll 4
+        for (int i = 0; i < 8; ++i) {
+          const int lr = 4 * i + (lane >> 3);  // row inside the warp's 32
+          const int drow = __shfl_sync(0xffffffffu, dst_row, lr);
+          if ((warp & 3) * 32 + lr < nrows) {
+            const float4 v = *reinterpret_cast<const float4*>(wbase + lr * kOutStride + (lane & 7) * 16);
+            atomicAdd(reinterpret_cast<float4*>(y + static_cast<size_t>(drow) * kF + half * 32) + (lane & 7), v);
+          }
+        }
       }
-      tc05::fence_async_smem();
-      if (t < nrows) {
-        asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(
-                         y + static_cast<size_t>(dst_row) * kF),
-                     "r"(tc05::smem_u32(my_row)), "r"(kF * 4)
-                     : "memory");
-      }
-      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-      if (k + 1 == tiles_per_cta || !tw.next(indptr_i, num_rels)) break;
+      if (!has_next) break;
+      nrows = tw.row1 - tw.row0;  // tw already describes this group's next tile
+      dst_row = dst_next;
     }
-    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // reduces done before the block ends
   }
 
   const bool all_ok = !__syncthreads_or(!ok);
@@ -502,7 +520,7 @@ int rgms_tma_launch(const float* w, float* y, const int32_t* indptr_i, const int
   const long long grid = tiles < kNumSMs ? tiles : kNumSMs;
   const int tiles_per_cta = static_cast<int>((tiles + grid - 1) / grid);
   rgms_tma_kernel<<<static_cast<unsigned>(grid), kPThreads, kPSmemBytes, stream>>>(
-      tm_z, w, y, indptr_i, indices_i, num_rels, tiles_per_cta);
+      tm_z, w, y, indptr_i, indices_i, num_rels, nnz_i, tiles_per_cta);
   SPTIR_LAUNCH_OK("rgms_tma_kernel");
   return 0;
 }

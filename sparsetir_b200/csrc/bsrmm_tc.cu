@@ -260,6 +260,11 @@ bsrmm_tma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       armed = it + 1;
     }
   } else if (warp == 1) {
+    // descriptors of stage 0, built once; the loop advances their address fields
+    // B tile, MN-major: 16 K rows of 128 bytes per step; the two 64-feature atoms are 4 KB apart
+    const uint64_t da0 = tc05::smem_desc_swizzled(tc05::smem_u32(tiles), kBBytes / 2, 1024, tc05::kSwizzle128B);
+    // A block, K-major: rows of 64 bytes, 16 columns (32 bytes) per step inside the row
+    const uint64_t db0 = tc05::smem_desc_swizzled(tc05::smem_u32(tiles) + kBBytes, 0, 512, tc05::kSwizzle64B);
     for (int it = 0; it < nblk; ++it) {
       const int stage = it % kTStages, use = it / kTStages;
       if (lane == 0) ok = tc05::mbar_wait(&bar_full[stage], use & 1);
@@ -267,16 +272,12 @@ bsrmm_tma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       if (!ok) break;
       if (lane == 0) {
         tc05::fence_after_sync();
-        const uint32_t sb = tc05::smem_u32(tiles + stage * kStageBytes);
-        const uint32_t sa = sb + kBBytes;
+        const uint64_t da_s = tc05::desc_advance(da0, stage * kStageBytes);
+        const uint64_t db_s = tc05::desc_advance(db0, stage * kStageBytes);
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {  // K = 32 block columns = 2 x 16
-          // B tile, MN-major: 16 K rows of 128 bytes per step; the two 64-feature atoms are 4 KB apart
-          const uint64_t da = tc05::smem_desc_swizzled(sb + ks * 16 * 128, kBBytes / 2, 1024, tc05::kSwizzle128B);
-          // A block, K-major: rows of 64 bytes, 16 columns (32 bytes) per step inside the row
-          const uint64_t db = tc05::smem_desc_swizzled(sa + ks * 32, 0, 512, tc05::kSwizzle64B);
-          tc05::mma_f16(tmem, da, db, idesc, (it > 0 || ks > 0) ? 1u : 0u);
-        }
+        for (int ks = 0; ks < 2; ++ks)  // K = 32 block columns = 2 x 16
+          tc05::mma_f16(tmem, tc05::desc_advance(da_s, ks * 16 * 128), tc05::desc_advance(db_s, ks * 32), idesc,
+                        (it > 0 || ks > 0) ? 1u : 0u);
         tc05::mma_commit(&bar_empty[stage]);
         if (it == nblk - 1) tc05::mma_commit(&bar_done);
       }

@@ -373,22 +373,26 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
     // ---- MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtTF32, kTM, kF, /*a_mn=*/0, /*b_mn=*/0);
-      const uint32_t wh = tc05::smem_u32(base + kOffWHi), wl = tc05::smem_u32(base + kOffWLo);
+      // descriptors are built once; the loop only advances their address fields (a lone thread
+      // issues one dependent instruction every few clocks, so rebuilding four descriptors per
+      // K-step made this warp the slowest role)
+      const uint64_t dwh0 = tc05::smem_desc_swizzled(tc05::smem_u32(base + kOffWHi), 0, 1024, tc05::kSwizzle128B);
+      const uint64_t dwl0 = tc05::smem_desc_swizzled(tc05::smem_u32(base + kOffWLo), 0, 1024, tc05::kSwizzle128B);
+      const uint64_t dzh0 = tc05::smem_desc_swizzled(tc05::smem_u32(base + kOffZRaw), 0, 1024, tc05::kSwizzle128B);
+      const uint64_t dzl0 = tc05::smem_desc_swizzled(tc05::smem_u32(base + kOffZLo), 0, 1024, tc05::kSwizzle128B);
       for (int k = 0; k < tiles_per_cta; ++k) {
         const int s = k % kZStages, use = k / kZStages, buf = k & 1, buse = k >> 1;
         if (!tc05::mbar_wait(&bar_conv[s], use & 1)) { ok = false; break; }
         if (buse > 0 && !tc05::mbar_wait(&bar_acc_empty[buf], (buse - 1) & 1)) { ok = false; break; }
         tc05::fence_after_sync();
-        const uint32_t zh = tc05::smem_u32(base + kOffZRaw + s * kZTile);
-        const uint32_t zl = tc05::smem_u32(base + kOffZLo + s * kZTile);
+        const uint64_t dzh_s = tc05::desc_advance(dzh0, s * kZTile);
+        const uint64_t dzl_s = tc05::desc_advance(dzl0, s * kZTile);
         const uint32_t acc = tmem + buf * kF;
 #pragma unroll
         for (int ks = 0; ks < kF / 8; ++ks) {  // K = 8 floats = 32 bytes inside the swizzled row
           const uint32_t zo = (ks >> 2) * kZBox + (ks & 3) * 32, wo = (ks >> 2) * kWBox + (ks & 3) * 32;
-          const uint64_t dzh = tc05::smem_desc_swizzled(zh + zo, 0, 1024, tc05::kSwizzle128B);
-          const uint64_t dzl = tc05::smem_desc_swizzled(zl + zo, 0, 1024, tc05::kSwizzle128B);
-          const uint64_t dwh = tc05::smem_desc_swizzled(wh + wo, 0, 1024, tc05::kSwizzle128B);
-          const uint64_t dwl = tc05::smem_desc_swizzled(wl + wo, 0, 1024, tc05::kSwizzle128B);
+          const uint64_t dzh = tc05::desc_advance(dzh_s, zo), dzl = tc05::desc_advance(dzl_s, zo);
+          const uint64_t dwh = tc05::desc_advance(dwh0, wo), dwl = tc05::desc_advance(dwl0, wo);
           tc05::mma_tf32(acc, dzl, dwh, idesc, ks > 0 ? 1u : 0u);  // small terms first
           tc05::mma_tf32(acc, dzh, dwl, idesc, 1u);
           tc05::mma_tf32(acc, dzh, dwh, idesc, 1u);

@@ -56,6 +56,14 @@ __device__ __forceinline__ uint64_t smem_desc_swizzled(uint32_t addr, uint32_t l
   return d;
 }
 
+// Descriptor of the same layout `bytes` further on in shared memory (bytes a multiple of 16; the
+// 14-bit address field must not overflow, which holds inside one block's shared memory): one
+// 32-bit add, for issue loops that would otherwise rebuild a descriptor per MMA.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t bytes) {
+  const uint32_t lo = static_cast<uint32_t>(desc) + (bytes >> 4);
+  return (desc & 0xFFFFFFFF00000000ull) | lo;
+}
+
 enum : uint32_t { kFmtF16 = 0, kFmtBF16 = 1, kFmtTF32 = 2 };
 
 // 32-bit instruction descriptor: fp32 accumulate, dense, no negation.

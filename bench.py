@@ -13,8 +13,9 @@ X / Y buffers (1.3 GB touched per step, ten times the L2, so no call finds its o
 operand resident in HBM.  ``e2e`` is the same work with X in pinned host memory copied in and Y
 copied back to pinned host memory inside the timed region.  With N > 1 the rows are cut into
 nnz-balanced contiguous shards, one per rank (strong scaling on the same graph); ``value`` times
-the shard kernels (max over ranks), ``e2e`` additionally broadcasts X from rank 0 and all-gathers
-the output rows over NCCL.
+the shard kernels (max over ranks); for ``e2e`` every rank copies its 1/N slice of X from its own
+pinned host memory, the slices are all-gathered over NCCL, and the shard's output rows go back to
+the rank's pinned host memory.
 
 ``--impl reference`` times the CPU restatement of the reference's lowered loop nest (the
 oracle's OpenMP csrmm — what the reference's ``llvm`` target would run, parallel over rows)
@@ -295,10 +296,17 @@ def ours_arm(args, rank, world, local_rank):
         ms_step, launch_mode = graph_ms, "cuda_graph_replay"
     value = total_flops / (ms_step * 1e-3) / 1e9
 
-    # ---- end to end: X from pinned host memory, Y back to pinned host memory
-    y_host = {f: torch.empty(g.m * f, dtype=torch.float32).pin_memory() for f in FEATS} if rank == 0 else None
-    y_full = {f: torch.empty(g.m * f, device=device) for f in FEATS} if world > 1 else None
-    shard_rows = [int(cuts[k + 1] - cuts[k]) for k in range(world)]
+    # ---- end to end: X from pinned host memory, Y back to pinned host memory.
+    # One GPU: the whole X in, the whole Y out.  N GPUs: every rank owns an equal slice of the
+    # rows of X in ITS pinned host memory and the rows of Y of its shard; per step it copies its
+    # slice in over its own PCIe link, the slices are all-gathered over NVLink (NCCL), the shard
+    # kernels run, and the shard's output rows go back to the rank's pinned host memory.  The
+    # bytes per step are the same as with one GPU; they are spread over N links.
+    xcuts = [(g.n * k) // world for k in range(world + 1)]
+    xr0, xr1 = xcuts[rank], xcuts[rank + 1]
+    x_host_loc = ({f: x_host[f].reshape(-1)[xr0 * f:xr1 * f].clone().pin_memory() for f in FEATS}
+                  if world > 1 else x_host)
+    y_host = {f: torch.empty(m_loc * f, dtype=torch.float32).pin_memory() for f in FEATS}
 
     # Three streams so that the PCIe link runs in both directions while kernels execute: the
     # copy-in of feature size k+1 and the copy-out of k-1 overlap the kernels of k.  Events order
@@ -313,31 +321,27 @@ def ours_arm(args, rank, world, local_rank):
         ev_out[f].record(main)
 
     def e2e_step():
-        if world == 1:
-            for f in FEATS:
-                s_in.wait_event(ev_done[f])       # previous step's kernels have read x_dev[f]
-                with torch.cuda.stream(s_in):
-                    x_dev[f].copy_(x_host[f], non_blocking=True)
-                    ev_in[f].record(s_in)
-            for f in FEATS:
-                main.wait_event(ev_in[f])
-                main.wait_event(ev_out[f])        # previous step's copy-out has read y_dev[f]
-                calls[f]()
-                ev_done[f].record(main)
-                s_out.wait_event(ev_done[f])
-                with torch.cuda.stream(s_out):
-                    y_host[f].copy_(y_dev[f], non_blocking=True)
-                    ev_out[f].record(s_out)
-            main.wait_event(ev_out[FEATS[-1]])    # the step ends when its last result is on the host
-            return
         for f in FEATS:
-            if rank == 0:
-                x_dev[f].copy_(x_host[f], non_blocking=True)
-            dist.broadcast(x_dev[f], src=0)
+            s_in.wait_event(ev_done[f])       # previous step's kernels have read x_dev[f]
+            with torch.cuda.stream(s_in):
+                if world == 1:
+                    x_dev[f].copy_(x_host[f], non_blocking=True)
+                else:
+                    piece = x_dev[f].view(-1)[xr0 * f:xr1 * f]
+                    piece.copy_(x_host_loc[f], non_blocking=True)
+                    sdist.all_gather_blocks(piece, [(xcuts[k + 1] - xcuts[k]) * f for k in range(world)],
+                                            out=x_dev[f].view(-1))
+                ev_in[f].record(s_in)
+        for f in FEATS:
+            main.wait_event(ev_in[f])
+            main.wait_event(ev_out[f])        # previous step's copy-out has read y_dev[f]
             calls[f]()
-            sdist.all_gather_rows(y_dev[f], shard_rows, f, out=y_full[f])
-            if rank == 0:
-                y_host[f].copy_(y_full[f], non_blocking=True)
+            ev_done[f].record(main)
+            s_out.wait_event(ev_done[f])
+            with torch.cuda.stream(s_out):
+                y_host[f].copy_(y_dev[f], non_blocking=True)
+                ev_out[f].record(s_out)
+        main.wait_event(ev_out[FEATS[-1]])    # the step ends when its last result is on the host
 
     for _ in range(2):
         e2e_step()
@@ -357,6 +361,16 @@ def ours_arm(args, rank, world, local_rank):
     h2d = sum(4 * g.n * f for f in FEATS)
     d2h = sum(4 * g.m * f for f in FEATS)
 
+    # ---- the largest graph of the benchmark set (SDDMM, 1.2e8 positions) sharded the same way:
+    # collective, so every rank runs it; rank 0 reports it
+    ops_sharded = None
+    if world > 1 and args.ops:
+        try:
+            from sparsetir_b200 import opbench
+            ops_sharded = {"sddmm": opbench.bench_sddmm_sharded(device, peaks, rank, world)}
+        except Exception as e:  # the headline line must still be printed
+            ops_sharded = {"error": repr(e)}
+
     if rank != 0:
         return
 
@@ -365,8 +379,8 @@ def ours_arm(args, rank, world, local_rank):
     f_chk = 64 if 64 in FEATS else FEATS[0]
     want = np.zeros((g.m, f_chk), np.float32)
     orc.csrmm(g.data, x_host[f_chk].numpy(), want, g.indptr, g.indices, g.m, g.n, f_chk, omp=True)
-    got = y_host[f_chk].numpy().reshape(g.m, f_chk)
-    np.testing.assert_allclose(got, want, rtol=1e-4, atol=1e-5)
+    got = y_host[f_chk].numpy().reshape(m_loc, f_chk)  # rank 0 holds the rows of its shard
+    np.testing.assert_allclose(got, want[int(cuts[0]):int(cuts[1])], rtol=1e-4, atol=1e-5)
 
     # ---- roofline of the dominant launch (F = 512)
     f_dom = FEATS[-1]
@@ -420,12 +434,17 @@ def ours_arm(args, rank, world, local_rank):
                    "host_decompose_ms_rank0": decompose_ms},
         "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e9, "unit": "GFLOP/s",
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                "includes": "H2D of X, kernels, D2H of Y" + (", NCCL broadcast of X and all-gather of Y" if world > 1 else "")},
+                "includes": "H2D of X, kernels, D2H of Y" + (
+                    "; every rank copies its 1/N slice of X from its own pinned host memory, NCCL "
+                    "all-gather of the slices, shard kernels, D2H of the shard's output rows to the "
+                    "rank's pinned host memory" if world > 1 else "")},
         "gpu_launches": launches_per_call * len(FEATS) * args.steps,
         "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "per_feat": per_f,
         "graph_replay_ms_per_step": graph_ms, "eager_ms_per_step": eager_ms_step,
         "alg_gbs": sum(spmm_bytes(m_loc, g.n, nnz_loc, f) for f in FEATS) / (ms_step * 1e-3) / 1e9,
     }
+    if ops_sharded is not None:
+        line["ops_sharded"] = ops_sharded
     if args.ops and world == 1:
         try:
             from sparsetir_b200 import opbench

@@ -165,6 +165,65 @@ def bench_sddmm(device, peaks, feats=(32, 64, 128, 256)) -> dict:
     return out
 
 
+def bench_sddmm_sharded(device, peaks, rank: int, world: int, feats=(32, 128)) -> dict:
+    """Config 3 cut into nnz-balanced row blocks, one per rank (every rank builds the same seeded
+    graph and keeps its block).  Per feature size: the shard kernels alone (max over ranks) and
+    with the all-gather of the per-position outputs.  Collective: every rank must call it."""
+    import torch.distributed as dist
+
+    from . import dist as sdist
+    from . import format as fmt
+
+    n = 232_965
+    indptr, indices, scale, nnz = sddmm_graph_on_device(device)
+    cuts = fmt.row_partition(indptr.cpu().numpy(), world)
+    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
+    ip_host = indptr.cpu().numpy()
+    sizes = [int(ip_host[cuts[k + 1]] - ip_host[cuts[k]]) for k in range(world)]
+    p0, p1 = int(ip_host[r0]), int(ip_host[r1])
+    ip_loc = (indptr[r0:r1 + 1] - indptr[r0]).contiguous()
+    ix_loc, sc_loc = indices[p0:p1], scale[p0:p1]
+    c_full = torch.empty(nnz, device=device)
+    c_loc = c_full[p0:p1]
+    gen = torch.Generator(device=device)
+    gen.manual_seed(1)
+    out = {"workload": "sddmm_lognormal_232965", "nnz": nnz, "rows_per_rank": [int(cuts[k + 1] - cuts[k]) for k in range(world)],
+           "nnz_per_rank": sizes, "per_feat": {}}
+
+    def max_over_ranks(ms: float) -> float:
+        t = torch.tensor([ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for f in feats:
+        a = torch.rand(n * f, device=device, generator=gen) * 2 - 1
+        b = torch.rand(n * f, device=device, generator=gen) * 2 - 1
+        fn = ops.sddmm.prepare(a[r0 * f:r1 * f], b, c_loc, ip_loc, ix_loc, sc_loc)
+        dist.barrier()
+        ms = max_over_ranks(_time(fn, number=3, repeat=3, warmup=2))
+
+        def with_gather():
+            fn()
+            sdist.all_gather_blocks(c_loc, sizes, out=c_full)
+
+        dist.barrier()
+        ms_g = max_over_ranks(_time(with_gather, number=2, repeat=3, warmup=1))
+        flops = 2.0 * nnz * f + nnz
+        out["per_feat"][str(f)] = {"ms": ms, "gflops": flops / (ms * 1e-3) / 1e9,
+                                   "gather_gbs": (4.0 * nnz * f) / (ms * 1e-3) / 1e9,
+                                   "ms_with_allgather": ms_g,
+                                   "gflops_with_allgather": flops / (ms_g * 1e-3) / 1e9}
+        if f == feats[0]:  # the gathered result is the right one: float64 spot check on rank 0
+            e = torch.randint(0, nnz, (4096,), device=device)
+            row = torch.searchsorted(indptr.long(), e, right=True) - 1
+            want = (a.view(n, f)[row].double() * b.view(n, f)[indices[e].long()].double()).sum(1) * scale[e].double()
+            err = (c_full[e].double() - want).abs().max().item()
+            out["spot_check_max_abs_err"] = err
+            assert err < 1e-4, err
+        del a, b
+    return out
+
+
 def bench_bsrmm(device, peaks, flush) -> dict:
     bs = dg.bsr_mask(seed=0)
     feat = 512

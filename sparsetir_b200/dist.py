@@ -101,3 +101,81 @@ def all_gather_rows(local: torch.Tensor, rows_per_rank: Sequence[int], feat: int
                     out: Optional[torch.Tensor] = None, group=None) -> torch.Tensor:
     """All-gather of row blocks ``[rows_k * feat]`` into the full ``[sum(rows) * feat]`` output."""
     return all_gather_blocks(local, [int(r) * feat for r in rows_per_rank], out=out, group=group)
+
+
+@dataclass
+class BsrShard:
+    """Block rows [row0, row1) of a BSR matrix with its own zero-based block indptr."""
+    rank: int
+    world: int
+    row0: int
+    row1: int
+    indptr: np.ndarray   # int32 [row1 - row0 + 1]
+    indices: np.ndarray  # int32 [stored blocks of the shard]
+    data: np.ndarray     # [stored blocks of the shard, blk, blk]
+    cuts: np.ndarray     # int64 [world + 1]
+
+
+def shard_bsr(indptr: np.ndarray, indices: np.ndarray, data: np.ndarray, world: int, rank: int) -> BsrShard:
+    """The rank's block rows under a partition balanced by stored blocks (the dense operand and
+    the block column space stay whole)."""
+    indptr = np.ascontiguousarray(indptr, dtype=np.int32)
+    cuts = fmt.row_partition(indptr, world)
+    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
+    p0, p1 = int(indptr[r0]), int(indptr[r1])
+    return BsrShard(rank, world, r0, r1, (indptr[r0:r1 + 1] - indptr[r0]).astype(np.int32),
+                    np.ascontiguousarray(indices[p0:p1], dtype=np.int32), np.ascontiguousarray(data[p0:p1]), cuts)
+
+
+@dataclass
+class RgmsShard:
+    """The part of an RGMS operand (CSF over relation / destination row / source) whose
+    destination rows lie in [row0, row1); destination ids are re-based to the shard."""
+    rank: int
+    world: int
+    row0: int
+    row1: int
+    indptr_i: np.ndarray   # int32 [num_rels + 1]
+    indices_i: np.ndarray  # int32 [nnz_i of the shard], destination row - row0
+    indptr_j: np.ndarray   # int32 [nnz_i of the shard + 1]
+    indices_j: np.ndarray  # int32 [edges of the shard]
+    data: np.ndarray       # float32 [edges of the shard]
+    cuts: np.ndarray       # int64 [world + 1] over destination rows
+
+    @property
+    def num_rows(self) -> int:
+        return self.row1 - self.row0
+
+
+def rgms_row_cuts(indices_i: np.ndarray, indptr_j: np.ndarray, num_rows: int, world: int) -> np.ndarray:
+    """Cut points over the destination rows with balanced numbers of edges: one writer per output
+    row, so no reduction across GPUs is needed."""
+    per_entry = np.diff(np.asarray(indptr_j, dtype=np.int64))
+    per_row = np.bincount(np.asarray(indices_i, dtype=np.int64), weights=per_entry, minlength=num_rows)
+    prefix = np.concatenate([[0], np.cumsum(per_row)]).astype(np.int32)
+    return fmt.row_partition(prefix, world)
+
+
+def shard_rgms(indptr_i: np.ndarray, indices_i: np.ndarray, indptr_j: np.ndarray, indices_j: np.ndarray,
+               data: np.ndarray, num_rows: int, world: int, rank: int) -> RgmsShard:
+    """The rank's destination-row block of an RGMS operand.  Inside a relation the destination
+    rows are ascending, so the block is one contiguous run of level-0 entries per relation; the
+    order of relations and of the entries of a row is kept, hence the same summation order."""
+    indptr_i = np.asarray(indptr_i, dtype=np.int64)
+    indices_i = np.asarray(indices_i, dtype=np.int64)
+    indptr_j = np.asarray(indptr_j, dtype=np.int64)
+    cuts = rgms_row_cuts(indices_i, indptr_j, num_rows, world)
+    lo, hi = int(cuts[rank]), int(cuts[rank + 1])
+    keep = (indices_i >= lo) & (indices_i < hi)
+    num_rels = len(indptr_i) - 1
+    rel_of = np.repeat(np.arange(num_rels), np.diff(indptr_i))
+    new_indptr_i = np.concatenate([[0], np.cumsum(np.bincount(rel_of[keep], minlength=num_rels))])
+    starts, ends = indptr_j[:-1][keep], indptr_j[1:][keep]
+    lens = ends - starts
+    new_indptr_j = np.concatenate([[0], np.cumsum(lens)])
+    # positions of the kept edges: for every kept level-0 entry the run [start, end)
+    edge_pos = np.repeat(starts - new_indptr_j[:-1], lens) + np.arange(int(new_indptr_j[-1]))
+    return RgmsShard(rank, world, lo, hi, new_indptr_i.astype(np.int32),
+                     (indices_i[keep] - lo).astype(np.int32), new_indptr_j.astype(np.int32),
+                     np.ascontiguousarray(np.asarray(indices_j)[edge_pos], dtype=np.int32),
+                     np.ascontiguousarray(np.asarray(data)[edge_pos], dtype=np.float32), cuts)

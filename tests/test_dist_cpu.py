@@ -92,3 +92,43 @@ def test_single_process_collectives_are_identity():
     t = torch.arange(12, dtype=torch.float32)
     assert torch.equal(sdist.all_gather_rows(t, [3], 4), t)
     assert sdist.broadcast_dense(t) is t
+
+
+def test_bsr_block_row_shards_reproduce_the_whole_product():
+    bs = dg.bsr_mask(size=512, blk=32, density=0.15, seed=3)
+    feat = 64
+    b = dg.dense_operand_normal(1, bs.nb * bs.blk, feat).astype(np.float16)
+    want = orc.bsrmm_f16(bs.data, b, bs.indptr, bs.indices, bs.mb, bs.nb, bs.blk, feat).reshape(-1, feat)
+    for world in (1, 2, 3, 8):
+        shards = [sdist.shard_bsr(bs.indptr, bs.indices, bs.data, world, r) for r in range(world)]
+        assert shards[0].row0 == 0 and shards[-1].row1 == bs.mb
+        assert sum(len(s.indices) for s in shards) == bs.nnzb
+        parts = [orc.bsrmm_f16(s.data, b, s.indptr, s.indices, s.row1 - s.row0, bs.nb, bs.blk, feat)
+                 for s in shards if s.row1 > s.row0]
+        got = np.concatenate(parts).reshape(-1, feat)
+        assert np.array_equal(got, want)  # same blocks, same order inside a block row: bit-exact
+
+
+def test_rgms_destination_row_shards_reproduce_the_whole_result():
+    c = dg.csf_relational(n=3000, num_rels=7, num_edges=40000, seed=2)
+    feat = 16
+    x = dg.dense_operand(4, c.n, feat)
+    w = dg.relation_weights(5, c.num_rels, feat)
+    want = np.zeros((c.m, feat), np.float32)
+    orc.rgms(c.data, w, x, want, c.indptr_i, c.indices_i, c.indptr_j, c.indices_j, c.m, c.n, c.num_rels, feat)
+    for world in (1, 2, 4):
+        got = np.zeros_like(want)
+        edges = []
+        for r in range(world):
+            s = sdist.shard_rgms(c.indptr_i, c.indices_i, c.indptr_j, c.indices_j, c.data, c.m, world, r)
+            assert s.indptr_i[-1] == len(s.indices_i) and s.indptr_j[-1] == len(s.indices_j)
+            assert np.all(s.indices_i >= 0) and np.all(s.indices_i < max(1, s.num_rows))
+            edges.append(len(s.indices_j))
+            y = np.zeros((s.num_rows, feat), np.float32)
+            if s.num_rows:
+                orc.rgms(s.data, w, x, y, s.indptr_i, s.indices_i, s.indptr_j, s.indices_j, s.num_rows, c.n,
+                         c.num_rels, feat)
+            got[s.row0:s.row1] = y
+        assert sum(edges) == c.nnz_j
+        assert max(edges) <= c.nnz_j / world + 64  # balanced up to the heaviest destination row
+        assert np.array_equal(got, want)  # relation and entry order kept: bit-exact

@@ -176,6 +176,15 @@ SPARSETIR_API int sparsetir_bsrmm(SPARSETIR_PACKED_ARGS);
  * examples/rgms/rgcn/bench_rgcn_non_composable.py:108). */
 SPARSETIR_API int sparsetir_rgms(SPARSETIR_PACKED_ARGS);
 
+/* RGMS over the decomposed ELL3D format, fp32: for every bucket b, group g, row slot ii,
+ * column slot j:  Y[rows_b[g,ii], fo] += A_b[g,ii,j] * sum_fi W[mid_b[g],fo,fi] * X[cols_b[g,ii,j],fi].
+ * args: (w f32[R*feat*feat], x f32[n*feat], y f32[m*feat],
+ *        {a f32[G_b*rows_b*cols_b], rows i32[G_b*rows_b], cols i32[G_b*rows_b*cols_b]} x K,
+ *        {mid i32[G_b]} x K, feat_size) — the argument list of the function built in
+ * examples/rgms/rgcn/bench_rgcn_composable.py:196-208 (buckets from CSFToELL3D, `mid` = relation
+ * of every group, :40-45), plus feat_size.  Accumulates into the caller's zero-filled y. */
+SPARSETIR_API int sparsetir_rgms_ell3d(SPARSETIR_PACKED_ARGS);
+
 /* ---- operators, plain-pointer form (device pointers; stream is a cudaStream_t) -------- */
 SPARSETIR_API int sparsetir_csrmm_raw(const float* a, const float* b, float* c,
                                       const int32_t* indptr, const int32_t* indices, int m, int n,
@@ -206,6 +215,24 @@ SPARSETIR_API int sparsetir_rgms_raw(const float* a, const float* w, const float
                                      const int32_t* indptr_j, const int32_t* indices_j, int m,
                                      int n, int num_rels, int feat, int nnz_i, int nnz_j,
                                      int device_id, void* stream);
+
+/* RGMS over ELL3D buckets (the decomposed form of examples/rgms/rgcn/bench_rgcn_composable.py:
+ * per bucket the arrays CSFToELL3D returns plus the relation id of every group, :40-45).
+ * a/cols are [num_groups*rows_per_group*cols_per_row], rows [num_groups*rows_per_group],
+ * mid [num_groups] ascending.  Accumulates into y. */
+typedef struct {
+  const float* a;
+  const int32_t* rows;
+  const int32_t* cols;
+  const int32_t* mid;
+  int32_t num_groups;
+  int32_t rows_per_group;
+  int32_t cols_per_row;
+} SparsetirEll3dBucket;
+SPARSETIR_API int sparsetir_rgms_ell3d_raw(const float* w, const float* x, float* y,
+                                           const SparsetirEll3dBucket* buckets, int num_buckets,
+                                           int m, int n, int num_rels, int feat, int device_id,
+                                           void* stream);
 
 /* RGMS that never allocates device memory.  No counterpart in the reference: it exists for
  * hosts that may not call the CUDA allocator when they need the operator (loops that forbid

@@ -196,3 +196,22 @@ def rgms(a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, m, n, num_rels, f
        _p(indices_i, _i32p), _p(indptr_j, _i32p), _p(indices_j, _i32p), int(m), int(n),
        int(num_rels), int(feat), int(len(indices_i)), int(len(indices_j)))
     return y
+
+
+def rgms_ell3d(w, x, y, buckets, feat) -> np.ndarray:
+    """Decomposed RGMS over ELL3D buckets; ``buckets`` is a list of ``(a, rows, cols, mid)`` with
+    ``a``/``cols`` shaped ``[groups, rows_b, cols_b]`` and ``rows`` ``[groups, rows_b]``.
+    Accumulates into (and returns) ``y``."""
+    w, x = _f32(w), _f32(x)
+    assert y.dtype == np.float32 and y.flags.c_contiguous
+    for a, rows, cols, mid in buckets:
+        a, rows, cols, mid = _f32(a), _i32(rows), _i32(cols), _i32(mid)
+        ng = int(mid.shape[0])
+        if ng == 0:
+            continue
+        rpg = rows.size // ng
+        cpr = cols.size // rows.size
+        lib().oracle_rgms_ell3d_bucket(_p(a, _f32p), _p(w, _f32p), _p(x, _f32p), _p(y, _f32p),
+                                       _p(rows, _i32p), _p(cols, _i32p), _p(mid, _i32p), ng, rpg, cpr,
+                                       int(feat))
+    return y

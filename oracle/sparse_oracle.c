@@ -542,3 +542,37 @@ ORACLE_API void oracle_rgms_omp(const float* a, const float* w, const float* x, 
   for (int fo = 0; fo < feat; ++fo)
     rgms_range(a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, feat, fo, fo + 1);
 }
+
+/* ------------------------------------------------------------ rgms on ELL3D */
+/*
+ * One bucket of the decomposed RGMS of examples/rgms/rgcn/bench_rgcn_composable.py:
+ * the rgcn_hetero_forward nest (tests/python/sparsetir/sparse_tir_scripts.py:468-499) rewritten
+ * to the axes (R, IO, II, J) of the ell3d buffer (examples/rgms/rgcn/utils.py:90-108) with R and
+ * IO fused into one loop over groups whose relation comes from the `mid` array
+ * (bench_rgcn_composable.py:40-45, :176-178):
+ *   for group g, row slot ii, output feature fo, column slot j, input feature fi:
+ *     Y[rows[g,ii], fo] += A[g,ii,j] * W[mid[g], fo, fi] * X[cols[g,ii,j], fi]
+ * Y is accumulated into (zero-filled by the caller, :209), loop order as scheduled there
+ * (io, ii, fo, j, fi).  Padding slots carry A = 0 and column 0.
+ */
+ORACLE_API void oracle_rgms_ell3d_bucket(const float* a, const float* w, const float* x, float* y,
+                                         const int32_t* rows, const int32_t* cols,
+                                         const int32_t* mid, int num_groups, int rows_per_group,
+                                         int cols_per_row, int feat) {
+  for (int g = 0; g < num_groups; ++g) {
+    const float* wr = w + (size_t)mid[g] * feat * feat;
+    for (int ii = 0; ii < rows_per_group; ++ii) {
+      size_t q = (size_t)g * rows_per_group + ii;
+      float* yr = y + (size_t)rows[q] * feat;
+      for (int fo = 0; fo < feat; ++fo) {
+        float acc = yr[fo];
+        for (int j = 0; j < cols_per_row; ++j) {
+          float av = a[q * cols_per_row + j];
+          const float* xr = x + (size_t)cols[q * cols_per_row + j] * feat;
+          for (int fi = 0; fi < feat; ++fi) acc += av * wr[(size_t)fo * feat + fi] * xr[fi];
+        }
+        yr[fo] = acc;
+      }
+    }
+  }
+}

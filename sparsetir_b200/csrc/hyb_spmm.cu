@@ -60,8 +60,14 @@ __device__ __forceinline__ int find_bucket(const HybTable& tb, int block) {
   return q;
 }
 
+// A bucket without a row-id array (`rows == nullptr`) writes ELL row r to output row r.
+__device__ __forceinline__ int row_id(const int32_t* __restrict__ rows, int r) {
+  return rows != nullptr ? __ldg(rows + r) : r;
+}
+
 __device__ __forceinline__ bool is_split_row(const int32_t* __restrict__ rows, int r, int nrows,
                                              int row) {
+  if (rows == nullptr) return false;
   return (r > 0 && __ldg(rows + r - 1) == row) || (r + 1 < nrows && __ldg(rows + r + 1) == row);
 }
 
@@ -107,7 +113,7 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
   const int32_t* __restrict__ rows = tb.rows[q];
   for (int j = lane; j < nr + 2; j += LPR) {
     const int idx = r0 - 1 + j;
-    s_rows[sub][j] = (idx >= 0 && idx < nrows) ? __ldg(rows + idx) : -1;
+    s_rows[sub][j] = (idx >= 0 && idx < nrows) ? row_id(rows, idx) : -1;
   }
   __syncwarp(mask);
   const FeatLane<LPR, VPL, VEC> fl(feat, blockIdx.y, lane);
@@ -182,9 +188,8 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
   // row id of ELL row g of the bucket, sign bit set when it must be accumulated atomically
   auto row_flag = [&](int g) -> int {
     if (g >= nrows) return 0;
-    const int rid = __ldg(rows + g);
-    const bool split = (g > 0 && __ldg(rows + g - 1) == rid) ||
-                       (g + 1 < nrows && __ldg(rows + g + 1) == rid);
+    const int rid = row_id(rows, g);
+    const bool split = is_split_row(rows, g, nrows, rid);
     return rid | ((always_atomic || split) ? 0x80000000 : 0);
   };
   auto row_end = [&](V& acc, int rf) {
@@ -393,7 +398,7 @@ hyb_spmm_async_kernel(const __grid_constant__ HybTable tb, const float* __restri
     }
     for (int j = lane; j < nr + 2; j += LPR) {
       const int idx = r0 - 1 + j;
-      s_rows[j] = (idx >= 0 && idx < nrows) ? __ldg(rows + idx) : -1;
+      s_rows[j] = (idx >= 0 && idx < nrows) ? row_id(rows, idx) : -1;
     }
   }
   __syncwarp(mask);
@@ -446,10 +451,10 @@ hyb_rearm_kernel(const __grid_constant__ HybTable tb, float* __restrict__ c, int
   int row = -1;
   bool clear = false;
   if (r < nrows) {
-    row = __ldg(rows + r);
+    row = row_id(rows, static_cast<int>(r));
     clear = tb.chunks_per_row[q] > 1 || is_split_row(rows, static_cast<int>(r), nrows, row);
     // of a run of equal ids only the first ELL row clears
-    if (clear && r > 0 && __ldg(rows + r - 1) == row) clear = false;
+    if (clear && r > 0 && rows != nullptr && __ldg(rows + r - 1) == row) clear = false;
   }
   unsigned todo = __ballot_sync(0xffffffffu, clear);
   const int lane = threadIdx.x & 31;
@@ -588,7 +593,8 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
     if (bk.nrows < 0 || bk.width < 0) return fail("sparsetir_hyb_spmm: negative bucket size");
     if (bk.nrows == 0) continue;
     if (bk.width == 0) return fail("sparsetir_hyb_spmm: bucket %d has rows but width 0", q);
-    if (!bk.w || !bk.rows || !bk.cols) return fail("sparsetir_hyb_spmm: null bucket array");
+    // rows may be null: ELL row r then belongs to output row r
+    if (!bk.w || !bk.cols) return fail("sparsetir_hyb_spmm: null bucket array");
     order.push_back(q);
   }
   std::stable_sort(order.begin(), order.end(),

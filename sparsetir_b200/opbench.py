@@ -273,12 +273,70 @@ def bench_rgms(device, peaks, flush) -> dict:
             "note": "gflops counts the reference's per-edge formulation; the kernel aggregates first"}
 
 
+def ell3d_values(cf, cols_bkt, masks) -> list:
+    """The CSF values scattered into the ELL3D slots.  Inside a bucket the stored slots follow
+    the CSF order of the rows that fall into the bucket (relation-major, rows ascending, entries
+    in order), so the values of those rows, in order, fill the slots whose mask is 1."""
+    deg = np.diff(cf.indptr_j)
+    cb = np.asarray(cols_bkt)
+    bucket_of_row = np.minimum(np.searchsorted(cb, deg, side="left"), len(cb) - 1)
+    entry_bucket = np.repeat(bucket_of_row, deg)
+    out = []
+    for b, m in enumerate(masks):
+        v = np.zeros(m.shape, np.float32)
+        v[m == 1] = cf.data[entry_bucket == b]
+        out.append(v)
+    return out
+
+
+def bench_rgms_ell3d(device, peaks, flush) -> dict:
+    """Config 5 in the decomposed ELL3D form (buckets of 1..32 columns, 32 slots per group)."""
+    from . import format as fmt
+    cf = dg.csf_relational(seed=0)
+    feat = 64
+    cols_bkt = [1, 2, 4, 8, 16, 32]
+    rows_bkt = [32 // c for c in cols_bkt]
+    ip, rows, cols, mask = fmt.csf_to_ell3d(cf.indptr_i, cf.indices_i, cf.indptr_j, cf.indices_j,
+                                            rows_bkt, cols_bkt)
+    vals = ell3d_values(cf, cols_bkt, mask)
+    dv = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)  # noqa: E731
+    buckets = []
+    for b in range(len(cols_bkt)):
+        mid = np.repeat(np.arange(cf.num_rels, dtype=np.int32), np.diff(ip[b]))
+        buckets.append((dv(vals[b]), dv(rows[b]), dv(cols[b]), dv(mid)))
+    x = dv(dg.dense_operand(1, cf.n, feat).reshape(-1))
+    w = dv(dg.relation_weights(2, cf.num_rels, feat).reshape(-1))
+    y = torch.zeros(cf.m * feat, device=device)
+    call = ops.rgms_ell3d.prepare(*ops.rgms_ell3d_args(w, x, y, buckets, feat))
+
+    def fn():
+        y.zero_()
+        call()
+
+    # same answer as the CSF form on the same graph
+    fn()
+    y_csf = torch.zeros_like(y)
+    ops.rgms(dv(cf.data), w, x, y_csf, dv(cf.indptr_i), dv(cf.indices_i), dv(cf.indptr_j), dv(cf.indices_j))
+    err = (y - y_csf).abs().max().item()
+    assert err < 1e-3, err
+    slots = int(sum(m.size for m in mask))
+    ell_rows = int(sum(r.size for r in rows))
+    flops_ref = 2.0 * cf.nnz_j * feat * feat + 2.0 * cf.nnz_j * feat
+    byts = 12 * cf.nnz_j + 4 * cf.num_rels * feat * feat + 8 * cf.n * feat
+    warm = _time(fn, number=20)
+    cold = _time_cold(fn, flush)
+    return {"workload": "rgms_ell3d_100k_46rel_1.5M_F64", "buckets": cols_bkt, "ell_rows": ell_rows,
+            "slots": slots, "padding": 1.0 - cf.nnz_j / slots, "max_abs_diff_vs_csf": err,
+            "warm": _entry(warm, flops_ref, byts, peaks), "cold_l2": _entry(cold, flops_ref, byts, peaks)}
+
+
 def run_all(device, peaks, log=print) -> Dict[str, dict]:
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
     out = {}
     for name, fn in (("csrmm", lambda: bench_csrmm(device, peaks, flush)),
                      ("bsrmm", lambda: bench_bsrmm(device, peaks, flush)),
                      ("rgms", lambda: bench_rgms(device, peaks, flush)),
+                     ("rgms_ell3d", lambda: bench_rgms_ell3d(device, peaks, flush)),
                      ("sddmm", lambda: bench_sddmm(device, peaks))):
         try:
             out[name] = fn()

@@ -171,6 +171,7 @@ sddmm = PackedFunc("sparsetir_sddmm")
 sddmm_edge_to_row = PackedFunc("sparsetir_sddmm_edge_to_row")
 bsrmm = PackedFunc("sparsetir_bsrmm")
 rgms = PackedFunc("sparsetir_rgms")
+rgms_ell3d = PackedFunc("sparsetir_rgms_ell3d")
 
 
 def hyb_args(x: torch.Tensor, y: torch.Tensor, buckets: Sequence[Sequence[torch.Tensor]],
@@ -184,4 +185,17 @@ def hyb_args(x: torch.Tensor, y: torch.Tensor, buckets: Sequence[Sequence[torch.
     args.append(int(feat_size))
     if flags:
         args.append(int(flags))
+    return args
+
+
+def rgms_ell3d_args(w: torch.Tensor, x: torch.Tensor, y: torch.Tensor,
+                    buckets: Sequence[Sequence[torch.Tensor]], feat_size: int) -> list:
+    """Argument list of ``rgms_ell3d`` in the reference's layout
+    (examples/rgms/rgcn/bench_rgcn_composable.py:196-208): ``[w, x, y]``, then ``a, rows, cols`` per
+    bucket, then ``mid`` per bucket, then ``feat_size``.  ``buckets`` holds ``(a, rows, cols, mid)``."""
+    args = [w.reshape(-1), x.reshape(-1), y.reshape(-1)]
+    for a, rows, cols, _ in buckets:
+        args += [a.reshape(-1), rows.reshape(-1), cols.reshape(-1)]
+    args += [mid.reshape(-1) for _, _, _, mid in buckets]
+    args.append(int(feat_size))
     return args

@@ -415,6 +415,56 @@ def test_rgms_accumulates_into_y(cuda_device):
     close(y, want + 1.0)
 
 
+# ------------------------------------------------------------------------------ rgms on ELL3D
+def ell3d_buckets(cf: dg.CSF, cols_bkt, group=32):
+    """Host buckets (a, rows, cols, mid) the way the reference example prepares them
+    (examples/rgms/rgcn/bench_rgcn_composable.py:123-138, :196-208): mask as the weights."""
+    rows_bkt = [max(1, group // c) for c in cols_bkt]
+    ip, rows, cols, mask = fmt.csf_to_ell3d(cf.indptr_i, cf.indices_i, cf.indptr_j, cf.indices_j,
+                                            rows_bkt, cols_bkt)
+    out = []
+    for b in range(len(cols_bkt)):
+        mid = np.repeat(np.arange(cf.num_rels, dtype=np.int32), np.diff(ip[b]))
+        out.append((mask[b].astype(np.float32), rows[b], cols[b], mid))
+    return out
+
+
+def run_rgms_ell3d(cf, x, w, buckets, device, feat):
+    y = torch.zeros(cf.m * feat, device=device)
+    devb = [tuple(dev(t, device) for t in bk) for bk in buckets]
+    ops.rgms_ell3d(*ops.rgms_ell3d_args(dev(w, device), dev(x, device), y, devb, feat))
+    torch.cuda.synchronize()
+    return y
+
+
+@pytest.mark.parametrize("feat", [16, 32, 64, 128])
+def test_rgms_ell3d_matches_oracle_and_the_csf_form(cuda_device, feat):
+    cf = dg.csf_relational(n=3000, num_rels=9, num_edges=50000, seed=feat)
+    x = dg.dense_operand(1, cf.n, feat)
+    w = dg.relation_weights(2, cf.num_rels, feat)
+    buckets = ell3d_buckets(cf, [1, 2, 4, 8])
+    want = orc.rgms_ell3d(w, x, np.zeros((cf.m, feat), np.float32), buckets, feat)
+    got = run_rgms_ell3d(cf, x, w, buckets, cuda_device, feat)
+    close(got, want, atol=ATOL * 4)
+    # the same matrix in the CSF form with unit values gives the same Y
+    ones = dg.CSF(cf.m, cf.n, cf.num_rels, cf.indptr_i, cf.indices_i, cf.indptr_j, cf.indices_j,
+                  np.ones(cf.nnz_j, np.float32))
+    close(got, oracle_rgms(ones, x, w), atol=ATOL * 4)
+
+
+def test_rgms_ell3d_wide_and_empty_buckets(cuda_device):
+    # rows longer than the widest bucket are split; a bucket of 64 columns is accumulated
+    # atomically; bucket 16 stays empty for this degree distribution of tiny relations
+    cf = dg.csf_relational(n=300, num_rels=3, num_edges=30000, seed=12)  # ~33 entries per (rel, row)
+    feat = 64
+    x = dg.dense_operand(3, cf.n, feat)
+    w = dg.relation_weights(4, cf.num_rels, feat)
+    for cols_bkt in ([64], [1, 16, 64], [4]):
+        buckets = ell3d_buckets(cf, cols_bkt, group=64)
+        want = orc.rgms_ell3d(w, x, np.zeros((cf.m, feat), np.float32), buckets, feat)
+        close(run_rgms_ell3d(cf, x, w, buckets, cuda_device, feat), want, atol=ATOL * 8)
+
+
 # ------------------------------------------------------------------------------ streams
 def test_calls_run_on_the_current_torch_stream(cuda_device):
     c = dg.csr_poisson(m=2000, n=2000, mean_deg=10, seed=30)

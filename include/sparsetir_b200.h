@@ -176,6 +176,14 @@ SPARSETIR_API int sparsetir_bsrmm(SPARSETIR_PACKED_ARGS);
  * examples/rgms/rgcn/bench_rgcn_non_composable.py:108). */
 SPARSETIR_API int sparsetir_rgms(SPARSETIR_PACKED_ARGS);
 
+/* Condensed tensor-core SpMM ("tcspmm"), fp16 operands, fp32 accumulation:
+ *   C[io*t + ii, f] = sum_{jo in [indptr[io], indptr[io+1])} sum_{ji < g} A[jo,ii,ji] * B[indices[jo*g+ji], f]
+ * args: (a f16[nnzb*t*g], b f16[nb*g*feat], c f16 or f32 [mb*t*feat], indptr i32[mb+1],
+ *        indices i32[nnzb*g], mb, nb, nnzb, feat_size, tile_size, group_size)
+ * with (indptr, indices, a) as ConDense returns them (group_indptr, tile_indices, mask).  Replaces
+ * the function built from `tcspmm` (examples/spmm/bench_tc_spmm.py:537-565, call :641-648). */
+SPARSETIR_API int sparsetir_tcspmm(SPARSETIR_PACKED_ARGS);
+
 /* RGMS over the decomposed ELL3D format, fp32: for every bucket b, group g, row slot ii,
  * column slot j:  Y[rows_b[g,ii], fo] += A_b[g,ii,j] * sum_fi W[mid_b[g],fo,fi] * X[cols_b[g,ii,j],fi].
  * args: (w f32[R*feat*feat], x f32[n*feat], y f32[m*feat],
@@ -215,6 +223,11 @@ SPARSETIR_API int sparsetir_rgms_raw(const float* a, const float* w, const float
                                      const int32_t* indptr_j, const int32_t* indices_j, int m,
                                      int n, int num_rels, int feat, int nnz_i, int nnz_j,
                                      int device_id, void* stream);
+
+SPARSETIR_API int sparsetir_tcspmm_raw(const void* a_f16, const void* b_f16, void* c, int c_is_f16,
+                                       const int32_t* indptr, const int32_t* indices, int mb, int nb,
+                                       int nnzb, int feat, int tile_size, int group_size,
+                                       int device_id, void* stream);
 
 /* RGMS over ELL3D buckets (the decomposed form of examples/rgms/rgcn/bench_rgcn_composable.py:
  * per bucket the arrays CSFToELL3D returns plus the relation id of every group, :40-45).

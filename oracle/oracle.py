@@ -215,3 +215,15 @@ def rgms_ell3d(w, x, y, buckets, feat) -> np.ndarray:
                                        _p(rows, _i32p), _p(cols, _i32p), _p(mid, _i32p), ng, rpg, cpr,
                                        int(feat))
     return y
+
+
+def tcspmm_f16(a, b, indptr, indices, mb, t, g, feat) -> np.ndarray:
+    """Condensed SpMM: fp16 ``a`` [groups, t, g] and ``b`` [rows, feat], fp32 sums [mb * t, feat]."""
+    a = np.ascontiguousarray(a, dtype=np.float16)
+    b = np.ascontiguousarray(b, dtype=np.float16)
+    indptr, indices = _i32(indptr), _i32(indices)
+    c = np.empty((mb * t, feat), np.float32)
+    u16p = ctypes.POINTER(ctypes.c_uint16)
+    lib().oracle_tcspmm_f16(a.ctypes.data_as(u16p), b.ctypes.data_as(u16p), _p(c, _f32p), _p(indptr, _i32p),
+                            _p(indices, _i32p), int(mb), int(t), int(g), int(feat))
+    return c

@@ -576,3 +576,33 @@ ORACLE_API void oracle_rgms_ell3d_bucket(const float* a, const float* w, const f
     }
   }
 }
+
+/* ----------------------------------------------------------------- tcspmm */
+/*
+ * Condensed ("TC-GNN") SpMM of examples/spmm/bench_tc_spmm.py:537-565 (tcspmm):
+ *   for row tile io, group jo in [indptr[io], indptr[io+1]), row ii < t, slot ji < g, feature f:
+ *     C[io, ii, f] += A[jo, ii, ji] * B[indices[jo, ji], f]        (init 0 per output element)
+ * A is the condensed mask/value array [groups, t, g], `indices` the g source rows of every
+ * group (ConDense, src/sparse/format.cc:353-429; unused slots hold row 0 with A = 0).
+ * fp16 operands; the products are accumulated in fp32 here (the reference's wmma fragments
+ * accumulate in fp16) and the fp32 sums are returned.
+ */
+ORACLE_API void oracle_tcspmm_f16(const uint16_t* a, const uint16_t* b, float* c,
+                                  const int32_t* indptr, const int32_t* indices, int mb, int t,
+                                  int g, int feat) {
+  const _Float16* ah = (const _Float16*)a;
+  const _Float16* bh = (const _Float16*)b;
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int io = 0; io < mb; ++io)
+    for (int ii = 0; ii < t; ++ii) {
+      float* cr = c + ((size_t)io * t + ii) * feat;
+      for (int f = 0; f < feat; ++f) cr[f] = 0.f;
+      for (int jo = indptr[io]; jo < indptr[io + 1]; ++jo)
+        for (int ji = 0; ji < g; ++ji) {
+          float av = (float)ah[((size_t)jo * t + ii) * g + ji];
+          if (av == 0.f) continue; /* adding 0 * x changes nothing for finite x */
+          const _Float16* br = bh + (size_t)indices[(size_t)jo * g + ji] * feat;
+          for (int f = 0; f < feat; ++f) cr[f] += av * (float)br[f];
+        }
+    }
+}

@@ -71,6 +71,7 @@ PACKED_SYMBOLS = (
     "sparsetir_bsrmm",
     "sparsetir_rgms",
     "sparsetir_rgms_ell3d",
+    "sparsetir_tcspmm",
 )
 
 # every other exported symbol: name -> (restype, argtypes)
@@ -91,6 +92,7 @@ PLAIN_SYMBOLS = {
     "sparsetir_sddmm_edge_to_row_raw": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "sparsetir_bsrmm_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_raw": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),
+    "sparsetir_tcspmm_raw": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_ell3d_raw": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_noalloc": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),
     "sparsetir_column_part_hyb": (_vp, [_i, _i, _i32p, _i32p, _i, _i32p, _i, _i]),

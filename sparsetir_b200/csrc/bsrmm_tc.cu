@@ -37,6 +37,7 @@ namespace sptir {
 
 __device__ unsigned int g_tc_timeouts = 0;  // bounded waits that ran out, since module load
 int rgms_tc_timeouts(unsigned int* count);  // the same counter of rgms_tc.cu
+int tcspmm_timeouts(unsigned int* count);   // ... and of tcspmm.cu
 
 namespace {
 
@@ -378,6 +379,8 @@ extern "C" int sparsetir_tc_timeouts(int device_id, unsigned int* count) {
   unsigned int bsr = 0, rgms = 0;
   SPTIR_CUDA_OK(cudaMemcpyFromSymbol(&bsr, g_tc_timeouts, sizeof(unsigned int)));
   if (rgms_tc_timeouts(&rgms) != 0) return -1;
-  *count = bsr + rgms;
+  unsigned int tcs = 0;
+  if (tcspmm_timeouts(&tcs) != 0) return -1;
+  *count = bsr + rgms + tcs;
   return 0;
 }

@@ -330,6 +330,31 @@ def bench_rgms_ell3d(device, peaks, flush) -> dict:
             "warm": _entry(warm, flops_ref, byts, peaks), "cold_l2": _entry(cold, flops_ref, byts, peaks)}
 
 
+def bench_tcspmm(device, peaks, flush, feats=(128, 512), t: int = 16, g: int = 16) -> dict:
+    """The power-law graph of the headline workload, condensed (ConDense, t x g = 16 x 16) and
+    multiplied in fp16 with fp32 accumulation and fp16 output, as the reference example does."""
+    from . import format as fmt
+    gr = dg.csr_powerlaw(seed=0)
+    gi, ti, mk = fmt.condense(gr.indptr, gr.indices, t, g)
+    mb, nb, nnzb = len(gi) - 1, -(-gr.n // g), len(ti)
+    dv = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)  # noqa: E731
+    a16, gi_d, ti_d = dv(mk.astype(np.float16).reshape(-1)), dv(gi), dv(ti.reshape(-1))
+    out = {"workload": "tcspmm_powerlaw_169343_t16_g16_f16", "nnz": gr.nnz, "groups": nnzb,
+           "condensed_density": float(mk.mean()), "per_feat": {}}
+    for f in feats:
+        xb = torch.zeros(nb * g * f, dtype=torch.float16, device=device)
+        xb[:gr.n * f] = dv(dg.dense_operand(100 + f, gr.n, f).astype(np.float16).reshape(-1))
+        c = torch.empty(mb * t * f, dtype=torch.float16, device=device)
+        fn = ops.tcspmm.prepare(a16, xb, c, gi_d, ti_d, mb, nb, nnzb, f, t, g)
+        warm = _time(fn, number=50)
+        cold = _time_cold(fn, flush)
+        flops = 2.0 * gr.nnz * f                                   # useful products only
+        byts = 2 * nnzb * t * g + 4 * nnzb * g + 4 * (mb + 1) + 2 * gr.n * f + 2 * gr.m * f
+        out["per_feat"][str(f)] = {"warm": _entry(warm, flops, byts, peaks), "cold_l2": _entry(cold, flops, byts, peaks),
+                                   "gflops_executed": 2.0 * nnzb * t * g * f / (warm * 1e-3) / 1e9}
+    return out
+
+
 def run_all(device, peaks, log=print) -> Dict[str, dict]:
     flush = torch.empty(2 * L2_BYTES, dtype=torch.uint8, device=device)
     out = {}
@@ -337,6 +362,7 @@ def run_all(device, peaks, log=print) -> Dict[str, dict]:
                      ("bsrmm", lambda: bench_bsrmm(device, peaks, flush)),
                      ("rgms", lambda: bench_rgms(device, peaks, flush)),
                      ("rgms_ell3d", lambda: bench_rgms_ell3d(device, peaks, flush)),
+                     ("tcspmm", lambda: bench_tcspmm(device, peaks, flush)),
                      ("sddmm", lambda: bench_sddmm(device, peaks))):
         try:
             out[name] = fn()

@@ -172,6 +172,7 @@ sddmm_edge_to_row = PackedFunc("sparsetir_sddmm_edge_to_row")
 bsrmm = PackedFunc("sparsetir_bsrmm")
 rgms = PackedFunc("sparsetir_rgms")
 rgms_ell3d = PackedFunc("sparsetir_rgms_ell3d")
+tcspmm = PackedFunc("sparsetir_tcspmm")
 
 
 def hyb_args(x: torch.Tensor, y: torch.Tensor, buckets: Sequence[Sequence[torch.Tensor]],

@@ -465,6 +465,50 @@ def test_rgms_ell3d_wide_and_empty_buckets(cuda_device):
         close(run_rgms_ell3d(cf, x, w, buckets, cuda_device, feat), want, atol=ATOL * 8)
 
 
+# ------------------------------------------------------------------------------ tcspmm
+def run_tcspmm(g: dg.CSR, x16, t, gs, device, out_dtype, weights=None):
+    """Condense the graph on the host (ConDense), then the condensed SpMM on the GPU."""
+    gi, ti, mk = fmt.condense(g.indptr, g.indices, t, gs)
+    a16 = mk.astype(np.float16) if weights is None else weights(mk)
+    mb, nb, feat = len(gi) - 1, -(-g.n // gs), x16.shape[1]
+    xb = np.zeros((nb * gs, feat), np.float16)
+    xb[:g.n] = x16
+    c = torch.full((mb * t * feat,), 3.0, device=device, dtype=out_dtype)
+    ops.tcspmm(dev(a16.reshape(-1), device), dev(xb.reshape(-1), device), c, dev(gi, device),
+               dev(ti.reshape(-1), device), mb, nb, len(ti), feat, t, gs)
+    torch.cuda.synchronize()
+    want = orc.tcspmm_f16(a16, xb, gi, ti.reshape(-1), mb, t, gs, feat)
+    return c.float().cpu().numpy().reshape(mb * t, feat), want
+
+
+@pytest.mark.parametrize("t,gs,feat", [(16, 16, 128), (8, 16, 128), (32, 16, 256), (16, 16, 512),
+                                       (16, 16, 96), (16, 8, 128), (4, 16, 64)])
+def test_tcspmm_matches_oracle(cuda_device, t, gs, feat):
+    g = dg.csr_powerlaw(n=3000, max_deg=1500, seed=t + feat)
+    x16 = dg.dense_operand(1, g.n, feat).astype(np.float16)
+    got, want = run_tcspmm(g, x16, t, gs, cuda_device, torch.float32)
+    np.testing.assert_allclose(got, want, rtol=1e-2, atol=1e-2)
+    # unit weights: the condensed product is the plain SpMM of the 0/1 matrix
+    ones = np.zeros((g.m, feat), np.float32)
+    orc.csrmm(np.ones(g.nnz, np.float32), x16.astype(np.float32), ones, g.indptr, g.indices, g.m, g.n, feat)
+    np.testing.assert_allclose(got[:g.m], ones, rtol=1e-2, atol=1e-2)
+
+
+def test_tcspmm_half_output_weights_and_empty_tiles(cuda_device):
+    # the reference's output dtype (float16), non-unit weights, and row tiles without any entry
+    deg = np.zeros(640, np.int64)
+    deg[:200] = np.random.default_rng(2).integers(1, 40, size=200)
+    deg[600:] = 3
+    rng = np.random.default_rng(3)
+    ix = dg.sorted_distinct_columns(rng, deg, 640)
+    g = dg.CSR(640, 640, np.concatenate([[0], np.cumsum(deg)]).astype(np.int32), ix, np.ones(len(ix), np.float32))
+    x16 = dg.dense_operand(4, g.n, 128).astype(np.float16)
+    wts = lambda mk: (mk * np.random.default_rng(5).uniform(0.5, 1.5, size=mk.shape)).astype(np.float16)  # noqa: E731
+    got, want = run_tcspmm(g, x16, 16, 16, cuda_device, torch.float16, weights=wts)
+    np.testing.assert_allclose(got, want, rtol=1e-2, atol=3e-2)  # one rounding to half on top
+    assert np.all(got[16 * 13:16 * 37] == 0)  # tiles 13..36 have no entries
+
+
 # ------------------------------------------------------------------------------ streams
 def test_calls_run_on_the_current_torch_stream(cuda_device):
     c = dg.csr_poisson(m=2000, n=2000, mean_deg=10, seed=30)

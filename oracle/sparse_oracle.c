@@ -23,7 +23,7 @@
  *     (tests/python/sparsetir/sparse_tir_lowered_buffer_scripts.py:530-549),
  *     which this file follows statement by statement, and by numpy
  *     searchsorted in the test-suite.
- *   - csrmm / ell_spmm / sddmm / bsrmm / rgms : parity unpinned.  The
+ *   - csrmm / ell_spmm / sddmm / bsrmm / rgms / rgms_ell3d / tcspmm : parity unpinned.  The
  *     reference stores no numeric vectors for them and cannot be built or
  *     imported on this machine; the test-suite bounds their error against an
  *     independent fp64 scipy/numpy computation instead.

@@ -172,3 +172,36 @@ def test_ell_spmm_sums_to_csrmm():
             orc.ell_spmm(w, rows[p][b], cols[p][b], x, y, 16)
     np.testing.assert_allclose(y, refimpl.spmm_f64(c.indptr, c.indices, c.data, x, c.m, c.n),
                                rtol=RTOL, atol=ATOL)
+
+
+def test_tcspmm_oracle_equals_fp64_spmm_of_the_condensed_matrix():
+    # condensing (pinned above) followed by the condensed product must give the plain product
+    c = dg.csr_powerlaw(n=700, max_deg=400, seed=8)
+    feat = 24
+    x16 = dg.dense_operand(9, c.n, feat).astype(np.float16)
+    for t, g in ((16, 16), (8, 16), (4, 2)):
+        gi, ti, mk = orc.condense(c.indptr, c.indices, t, g)
+        nb = -(-c.n // g)
+        xb = np.zeros((nb * g, feat), np.float16)
+        xb[:c.n] = x16
+        got = orc.tcspmm_f16(mk.astype(np.float16), xb, gi, ti.reshape(-1), len(gi) - 1, t, g, feat)
+        want = refimpl.spmm_f64(c.indptr, c.indices, np.ones(c.nnz), x16.astype(np.float64), c.m, c.n)
+        np.testing.assert_allclose(got[:c.m], want, rtol=1e-5, atol=1e-4)
+        assert np.all(got[c.m:] == 0)  # rows of the last tile past the matrix
+
+
+def test_rgms_ell3d_oracle_equals_fp64_rgms_of_the_csf_form():
+    cf = dg.csf_relational(n=500, num_rels=5, num_edges=6000, seed=9)
+    feat = 8
+    x = dg.dense_operand(1, cf.n, feat)
+    w = dg.relation_weights(2, cf.num_rels, feat)
+    cols_bkt = [1, 2, 4]
+    rows_bkt = [8, 4, 2]
+    ip, rows, cols, mask = orc.csf_to_ell3d(cf.indptr_i, cf.indices_i, cf.indptr_j, cf.indices_j,
+                                            rows_bkt, cols_bkt)
+    buckets = [(mask[b].astype(np.float32), rows[b], cols[b],
+                np.repeat(np.arange(cf.num_rels, dtype=np.int32), np.diff(ip[b]))) for b in range(3)]
+    got = orc.rgms_ell3d(w, x, np.zeros((cf.m, feat), np.float32), buckets, feat)
+    want = refimpl.rgms_f64(np.ones(cf.nnz_j), w, x, cf.indptr_i, cf.indices_i, cf.indptr_j,
+                            cf.indices_j, cf.m)
+    np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL * 4)

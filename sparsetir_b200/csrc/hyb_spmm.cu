@@ -51,6 +51,7 @@ struct HybTable {
   int32_t rows_per_item[kMaxB];    // >= 1; 1 for chunked buckets
   int32_t chunks_per_row[kMaxB];   // 1 unless width > item_slots
   int32_t block_start[kMaxB + 1];
+  int32_t row_base[kMaxB];         // buckets without a row-id array: ELL row r -> output row base + r
   int32_t nb;
 };
 
@@ -60,9 +61,9 @@ __device__ __forceinline__ int find_bucket(const HybTable& tb, int block) {
   return q;
 }
 
-// A bucket without a row-id array (`rows == nullptr`) writes ELL row r to output row r.
-__device__ __forceinline__ int row_id(const int32_t* __restrict__ rows, int r) {
-  return rows != nullptr ? __ldg(rows + r) : r;
+// A bucket without a row-id array (`rows == nullptr`) writes ELL row r to output row base + r.
+__device__ __forceinline__ int row_id(const int32_t* __restrict__ rows, int r, int base) {
+  return rows != nullptr ? __ldg(rows + r) : base + r;
 }
 
 __device__ __forceinline__ bool is_split_row(const int32_t* __restrict__ rows, int r, int nrows,
@@ -113,7 +114,7 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
   const int32_t* __restrict__ rows = tb.rows[q];
   for (int j = lane; j < nr + 2; j += LPR) {
     const int idx = r0 - 1 + j;
-    s_rows[sub][j] = (idx >= 0 && idx < nrows) ? row_id(rows, idx) : -1;
+    s_rows[sub][j] = (idx >= 0 && idx < nrows) ? row_id(rows, idx, tb.row_base[q]) : -1;
   }
   __syncwarp(mask);
   const FeatLane<LPR, VPL, VEC> fl(feat, blockIdx.y, lane);
@@ -188,7 +189,7 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
   // row id of ELL row g of the bucket, sign bit set when it must be accumulated atomically
   auto row_flag = [&](int g) -> int {
     if (g >= nrows) return 0;
-    const int rid = row_id(rows, g);
+    const int rid = row_id(rows, g, 0);  // a bucket without row ids has its base folded into cl
     const bool split = is_split_row(rows, g, nrows, rid);
     return rid | ((always_atomic || split) ? 0x80000000 : 0);
   };
@@ -324,6 +325,7 @@ hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const float* __restric
   const int32_t* cols = tb.cols[q] + first;
   const float* wts = tb.w[q] + first;
   const int32_t* rows = tb.rows[q];
+  if (rows == nullptr) cl += static_cast<size_t>(tb.row_base[q]) * stride;
   const bool always_atomic = all_atomic || cpr > 1;
   if (width == 1)
     lean_item<LPR, 1, W>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
@@ -398,7 +400,7 @@ hyb_spmm_async_kernel(const __grid_constant__ HybTable tb, const float* __restri
     }
     for (int j = lane; j < nr + 2; j += LPR) {
       const int idx = r0 - 1 + j;
-      s_rows[j] = (idx >= 0 && idx < nrows) ? row_id(rows, idx) : -1;
+      s_rows[j] = (idx >= 0 && idx < nrows) ? row_id(rows, idx, tb.row_base[q]) : -1;
     }
   }
   __syncwarp(mask);
@@ -451,7 +453,7 @@ hyb_rearm_kernel(const __grid_constant__ HybTable tb, float* __restrict__ c, int
   int row = -1;
   bool clear = false;
   if (r < nrows) {
-    row = row_id(rows, static_cast<int>(r));
+    row = row_id(rows, static_cast<int>(r), tb.row_base[q]);
     clear = tb.chunks_per_row[q] > 1 || is_split_row(rows, static_cast<int>(r), nrows, row);
     // of a run of equal ids only the first ELL row clears
     if (clear && r > 0 && rows != nullptr && __ldg(rows + r - 1) == row) clear = false;
@@ -572,10 +574,11 @@ int launch(HybTable& tb, const float* b, float* c, int feat, int all_atomic, cud
 }  // namespace
 }  // namespace sptir
 
-extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirEllBucket* buckets,
-                                      int num_buckets, int m, int n, int feat, int flags,
-                                      int device_id, void* stream) {
-  using namespace sptir;
+namespace sptir {
+// The launcher behind sparsetir_hyb_spmm_raw.  row_bases (may be null): for buckets whose `rows`
+// array is null, ELL row r of bucket q is written to output row row_bases[q] + r.
+int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, const int32_t* row_bases,
+                  int num_buckets, int m, int n, int feat, int flags, int device_id, void* stream) {
   if (num_buckets < 0 || num_buckets > kMaxB)
     return fail("sparsetir_hyb_spmm: %d buckets exceed the maximum of %d", num_buckets, kMaxB);
   if (m < 0 || feat < 0) return fail("sparsetir_hyb_spmm: negative size");
@@ -605,6 +608,7 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
     const SparsetirEllBucket& bk = buckets[order[k]];
     tb.w[k] = bk.w; tb.rows[k] = bk.rows; tb.cols[k] = bk.cols;
     tb.nrows[k] = bk.nrows; tb.width[k] = bk.width;
+    tb.row_base[k] = row_bases ? row_bases[order[k]] : 0;
   }
   const bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
   // the lean kernel takes whole feature tiles and ELL widths of 1, 2, 4 or a multiple of 8; with
@@ -664,4 +668,11 @@ extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirE
   if (feat <= 16) return launch<16, 1, 1>(tb, b, c, feat, all_atomic, st);
   if (feat <= 32) return launch<32, 1, 1>(tb, b, c, feat, all_atomic, st);
   return launch<32, 4, 1>(tb, b, c, feat, all_atomic, st);
+}
+}  // namespace sptir
+
+extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirEllBucket* buckets,
+                                      int num_buckets, int m, int n, int feat, int flags,
+                                      int device_id, void* stream) {
+  return sptir::hyb_spmm_impl(b, c, buckets, nullptr, num_buckets, m, n, feat, flags, device_id, stream);
 }

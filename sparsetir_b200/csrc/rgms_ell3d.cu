@@ -8,14 +8,19 @@
 // (the mask cast to float in the example), row ids and column ids, then per bucket the relation id
 // of every group.
 //
-// Like the CSF form (rgms.cu) it aggregates first and transforms once per ELL row: per bucket
-//   (1) Z[q, :] = sum_j A[q,j] X[cols[q,j], :]   — the hyb SpMM kernel on one bucket whose ELL row
-//       q writes output row q (the bucket's width is the compile-time-friendly 1/2/4/8...);
-//   (2) Y[rows[q], :] += Z[q, :] W_{mid[q / rows_per_group]}^T — for feat 64 the TMA-fed tcgen05
-//       kernel of rgms_tc.cu (relation ranges over Z rows are computed from `mid` by a small
-//       kernel), otherwise a CUDA-core tile kernel.
-// Padding rows (A = 0) contribute zeros.  Z lives in the per-(device, stream) workspace.
+// Like the CSF form (rgms.cu) it aggregates first and transforms once per ELL row:
+//   (1) Z[q, :] = sum_j A[q,j] X[cols[q,j], :]   — the hyb SpMM kernel, ELL row q of bucket b
+//       writing row base_b + q of one Z array that holds all buckets (the widths are the
+//       compile-time-friendly 1/2/4/8...);
+//   (2) Y[rows[q], :] += Z[q, :] W_{mid[q / rows_per_group]}^T.
+// For feat 64 this is three launches whatever the number of buckets: one SpMM launch over all
+// buckets, one small kernel that turns the `mid` arrays into the Z-row range of every (bucket,
+// relation) pair and copies the row ids next to each other, one launch of the TMA-fed tcgen05
+// kernel of rgms_tc.cu over those ranges.  Other feature sizes go bucket by bucket through a
+// CUDA-core tile kernel.  Padding rows (A = 0) contribute zeros.  Z, the ranges and the row ids
+// live in the per-(device, stream) workspace.
 #include <algorithm>
+#include <vector>
 
 #include "common.h"
 
@@ -26,9 +31,55 @@ int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,
                    const int32_t* indices_j, int num_rels, int feat, int nnz_i, const float* z,
                    cudaStream_t stream);
 
+int rgms_tma_launch_ranges(const float* w, float* y, const int32_t* indptr_i, const int32_t* indices_i,
+                           int num_ranges, int rel_mod, int nnz_i, const float* z, cudaStream_t stream);
+int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, const int32_t* row_bases,
+                  int num_buckets, int m, int n, int feat, int flags, int device_id, void* stream);
+
 namespace {
 
 constexpr int kThreads = 256;
+constexpr int kMaxBuckets = SPARSETIR_HYB_MAX_BUCKETS;
+
+// what the preparation kernel needs to know about the buckets (passed by value)
+struct Ell3dTable {
+  const int32_t* mid[kMaxBuckets];
+  const int32_t* rows[kMaxBuckets];
+  int32_t num_groups[kMaxBuckets];
+  int32_t rows_per_group[kMaxBuckets];
+  int32_t z_base[kMaxBuckets + 1];  // first Z row of every bucket; [nb] = total rows
+  int32_t nb;
+};
+
+// ranges[b * R + r] = first Z row of relation r inside bucket b (ranges[nb * R] = total rows), and
+// all_rows = the buckets' row ids one after the other.  Blocks 0.. cover the row ids; the last
+// block computes the ranges.
+__global__ void __launch_bounds__(kThreads)
+ell3d_prepare_kernel(const __grid_constant__ Ell3dTable tb, int num_rels, int32_t* __restrict__ ranges,
+                     int32_t* __restrict__ all_rows) {
+  if (blockIdx.x == gridDim.x - 1) {
+    for (int e = threadIdx.x; e <= tb.nb * num_rels; e += kThreads) {
+      if (e == tb.nb * num_rels) {
+        ranges[e] = tb.z_base[tb.nb];
+        continue;
+      }
+      const int b = e / num_rels, r = e % num_rels;
+      int lo = 0, hi = tb.num_groups[b];  // first group of the bucket with mid >= r
+      while (lo < hi) {
+        const int m = lo + (hi - lo) / 2;
+        if (__ldg(tb.mid[b] + m) < r) lo = m + 1; else hi = m;
+      }
+      ranges[e] = tb.z_base[b] + lo * tb.rows_per_group[b];
+    }
+    return;
+  }
+  const int total = tb.z_base[tb.nb];
+  for (int q = blockIdx.x * kThreads + threadIdx.x; q < total; q += (gridDim.x - 1) * kThreads) {
+    int b = 0;
+    while (b + 1 < tb.nb && q >= tb.z_base[b + 1]) ++b;
+    all_rows[q] = __ldg(tb.rows[b] + (q - tb.z_base[b]));
+  }
+}
 
 // indptr[r] = rows_per_group * (number of groups whose relation is < r), r = 0..num_rels:
 // the Z-row range of every relation, from the ascending per-group relation ids
@@ -98,6 +149,49 @@ extern "C" int sparsetir_rgms_ell3d_raw(const float* w, const float* x, float* y
   if (num_rels == 0) return fail("sparsetir_rgms_ell3d: rows but no relations");
   if (use_device(device_id) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  if (feat == 64 && num_buckets <= kMaxBuckets) {
+    // ---- three launches for all buckets
+    Ell3dTable tb{};
+    std::vector<SparsetirEllBucket> ell;
+    std::vector<int32_t> bases;
+    long long total = 0;
+    int flags = 0;
+    for (int b = 0; b < num_buckets; ++b) {
+      const SparsetirEll3dBucket& bk = buckets[b];
+      const int nrows = bk.num_groups * bk.rows_per_group;
+      if (nrows == 0) continue;
+      const int k = tb.nb++;
+      tb.mid[k] = bk.mid; tb.rows[k] = bk.rows;
+      tb.num_groups[k] = bk.num_groups; tb.rows_per_group[k] = bk.rows_per_group;
+      tb.z_base[k] = static_cast<int32_t>(total);
+      ell.push_back(SparsetirEllBucket{bk.a, nullptr, bk.cols, nrows, bk.cols_per_row});
+      bases.push_back(static_cast<int32_t>(total));
+      if (bk.cols_per_row > 32) flags = SPARSETIR_HYB_ZERO_C;  // rows cut into pieces accumulate
+      total += nrows;
+    }
+    const long long num_ranges = static_cast<long long>(tb.nb) * num_rels;
+    if (total <= INT32_MAX && num_ranges < INT32_MAX) {
+      tb.z_base[tb.nb] = static_cast<int32_t>(total);
+      const size_t zb = (static_cast<size_t>(total) * feat * sizeof(float) + 255) & ~static_cast<size_t>(255);
+      const size_t rb = (static_cast<size_t>(num_ranges + 1) * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
+      char* wsp = static_cast<char*>(workspace(device_id, st, zb + rb + static_cast<size_t>(total) * sizeof(int32_t)));
+      if (!wsp) return -1;
+      float* zall = reinterpret_cast<float*>(wsp);
+      int32_t* rng = reinterpret_cast<int32_t*>(wsp + zb);
+      int32_t* all_rows = reinterpret_cast<int32_t*>(wsp + zb + rb);
+      if (hyb_spmm_impl(x, zall, ell.data(), bases.data(), tb.nb, static_cast<int>(total), n, feat, flags,
+                        device_id, stream) != 0)
+        return -1;
+      const int copy_blocks = static_cast<int>(std::min<long long>(ceil_div(static_cast<int>(total), kThreads), 4 * kNumSMs));
+      ell3d_prepare_kernel<<<copy_blocks + 1, kThreads, 0, st>>>(tb, num_rels, rng, all_rows);
+      SPTIR_LAUNCH_OK("ell3d_prepare_kernel");
+      const int rc = rgms_tma_launch_ranges(w, y, rng, all_rows, static_cast<int>(num_ranges), num_rels,
+                                            static_cast<int>(total), zall, st);
+      if (rc <= 0) return rc;
+      // not taken by the tensor-core path: fall through to the per-bucket form (Z is recomputed)
+    }
+  }
 
   // workspace: Z of the largest bucket, then the relation ranges
   const size_t z_bytes = (static_cast<size_t>(max_rows) * feat * sizeof(float) + 255) & ~static_cast<size_t>(255);

@@ -311,7 +311,8 @@ struct TileWalk {
 __global__ void __launch_bounds__(kPThreads, 1)
 rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restrict__ w,
                 float* __restrict__ y, const int32_t* __restrict__ indptr_i,
-                const int32_t* __restrict__ indices_i, int num_rels, int nnz_i, int tiles_per_cta) {
+                const int32_t* __restrict__ indices_i, int num_rels, int nnz_i, int tiles_per_cta,
+                int rel_mod) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kZStages];   // z rows of the stage have landed
   __shared__ __align__(8) uint64_t bar_conv[kZStages];   // remainders written (128 arrivals)
@@ -408,11 +409,13 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
     int staged_rel = -1;
     for (int k = 0; k < tiles_per_cta; ++k) {
       const int s = k % kZStages, use = k / kZStages;
-      if (tw.rel != staged_rel) {
+      // rel_mod > 0: the row ranges are (bucket, relation) pairs, W is indexed by the relation
+      const int wrel = rel_mod > 0 ? tw.rel % rel_mod : tw.rel;
+      if (wrel != staged_rel) {
         // the MMAs of the previous tile are the last readers of the staged W
         if (k > 0 && !tc05::mbar_wait(&bar_empty[(k - 1) % kZStages], ((k - 1) / kZStages) & 1)) { ok = false; break; }
-        staged_rel = tw.rel;
-        const float4* wr = reinterpret_cast<const float4*>(w + static_cast<size_t>(tw.rel) * kF * kF);
+        staged_rel = wrel;
+        const float4* wr = reinterpret_cast<const float4*>(w + static_cast<size_t>(wrel) * kF * kF);
         for (int ch = ct; ch < kF * kF / 4; ch += 128) {
           const int fo = ch >> 4, kc = ch & 15;
           const float4 v = __ldg(wr + ch);
@@ -504,7 +507,7 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
 
 // 0 when launched, 1 when this path cannot take the call (caller falls back), -1 on error
 int rgms_tma_launch(const float* w, float* y, const int32_t* indptr_i, const int32_t* indices_i,
-                    int num_rels, int nnz_i, const float* z, cudaStream_t stream) {
+                    int num_rels, int nnz_i, const float* z, cudaStream_t stream, int rel_mod = 0) {
   if (nnz_i <= 0 || num_rels <= 0) return 1;
   if ((reinterpret_cast<uintptr_t>(z) & 15u) || (reinterpret_cast<uintptr_t>(y) & 15u) ||
       (reinterpret_cast<uintptr_t>(w) & 15u))
@@ -524,12 +527,25 @@ int rgms_tma_launch(const float* w, float* y, const int32_t* indptr_i, const int
   const long long grid = tiles < kNumSMs ? tiles : kNumSMs;
   const int tiles_per_cta = static_cast<int>((tiles + grid - 1) / grid);
   rgms_tma_kernel<<<static_cast<unsigned>(grid), kPThreads, kPSmemBytes, stream>>>(
-      tm_z, w, y, indptr_i, indices_i, num_rels, nnz_i, tiles_per_cta);
+      tm_z, w, y, indptr_i, indices_i, num_rels, nnz_i, tiles_per_cta, rel_mod);
   SPTIR_LAUNCH_OK("rgms_tma_kernel");
   return 0;
 }
 
 }  // namespace
+
+// The TMA-fed kernel over `num_ranges` row ranges of z (indptr_i) whose W is W[range % rel_mod]:
+// several buckets' (bucket, relation) ranges in one launch.  0 when launched, 1 when this path
+// cannot take the call, -1 on error.
+int rgms_tma_launch_ranges(const float* w, float* y, const int32_t* indptr_i, const int32_t* indices_i,
+                           int num_ranges, int rel_mod, int nnz_i, const float* z, cudaStream_t stream) {
+  static const bool use_tma = [] {
+    const char* e = std::getenv("SPARSETIR_RGMS_PATH");
+    return !(e && std::strcmp(e, "regs") == 0);
+  }();
+  if (!use_tma) return 1;
+  return rgms_tma_launch(w, y, indptr_i, indices_i, num_ranges, nnz_i, z, stream, rel_mod);
+}
 
 // Returns 0 when launched, 1 when the shape is not handled here, -1 on error.
 // z: rows already aggregated by a preceding launch (two-kernel form), or nullptr (fused form).

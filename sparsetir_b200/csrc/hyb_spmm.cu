@@ -52,6 +52,7 @@ struct HybTable {
   int32_t chunks_per_row[kMaxB];   // 1 unless width > item_slots
   int32_t block_start[kMaxB + 1];
   int32_t row_base[kMaxB];         // buckets without a row-id array: ELL row r -> output row base + r
+  int32_t item;                    // lean kernel: stored slots per work item
   int32_t nb;
 };
 
@@ -290,7 +291,7 @@ __global__ void __launch_bounds__(kThreads, 4)
 hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b,
                      float* __restrict__ c, int feat, int all_atomic) {
   constexpr int SUBS = kThreads / LPR;
-  constexpr int ITEM = lean_item_slots(LPR, W);
+  const int ITEM = tb.item;
   const int lane = threadIdx.x % LPR;
   const int sub = threadIdx.x / LPR;
   const unsigned mask = group_mask<LPR>();
@@ -494,6 +495,17 @@ int lanes_per_row(int feat, bool vec4, int n, int lane_w) {
       return static_cast<size_t>(mb > 0 ? mb : 48) << 20;
     }();
     while (lanes > min_lanes && static_cast<size_t>(n) * lanes * lane_w * 4 > l2_budget) lanes /= 2;
+    // Up to `narrow_passes` passes over the index arrays the narrowest tile wins even when a
+    // wider slice would fit L2: twice the independent sub-warps per block keep more gathers in
+    // flight (measured on B200: F = 64 38 vs 41 us, F = 128 60 vs 66 us, F = 256 equal, F = 512
+    // 211 vs 197 us, where the 16 passes re-read 120 MB of ids).
+    static const int narrow_passes = [] {
+      const char* e = std::getenv("SPARSETIR_HYB_NARROW_PASSES");
+      const int v = e ? std::atoi(e) : -1;
+      return v >= 0 ? v : 4;
+    }();
+    if (lanes > min_lanes && feat % (min_lanes * lane_w) == 0 && feat / (min_lanes * lane_w) <= narrow_passes)
+      lanes = min_lanes;
   }
   return lanes;
 }
@@ -625,7 +637,15 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
     lanes = lanes_per_row(feat, vec4, n, lane_w);
   }
   lean = lean && feat % (lane_w * lanes) == 0;
-  plan_items(tb, lean ? lean_item_slots(lanes, lane_w) : item_slots(lanes));
+  // lean kernel: SPARSETIR_HYB_ITEM_BATCHES (2, 4 or 8 id batches of `lanes` slots per work item)
+  // overrides the default for tuning; 8 is the most the row-id registers of an item hold
+  static const int item_batches = [] {
+    const char* e = std::getenv("SPARSETIR_HYB_ITEM_BATCHES");
+    const int v = e ? std::atoi(e) : 0;
+    return (v == 2 || v == 4 || v == 8) ? v : 0;
+  }();
+  tb.item = item_batches > 0 ? item_batches * lanes : lean_item_slots(lanes, lane_w);
+  plan_items(tb, lean ? tb.item : item_slots(lanes));
 
   bool after_rearm = false;  // this call's re-arm kernel directly precedes the SpMM launch
   if (flags & SPARSETIR_HYB_ZERO_C) {

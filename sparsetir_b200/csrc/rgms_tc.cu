@@ -229,8 +229,9 @@ rgms_tc_kernel(const float* __restrict__ a, const float* __restrict__ w,
 //               the raw tile serves as the "high" part as it is; the converters compute the
 //               remainder z - tf32(z) element by element into a second buffer at the same
 //               (swizzled) offsets, and stage W_r (raw and remainder) when the relation changes;
-//   warp 1      issues the 8 K-steps x 3 products (3xTF32 as above) into one of two TMEM
-//               accumulators, tcgen05.commit frees the stage and publishes the accumulator;
+//   warp 1      issues the 8 K-steps of the 3xTF32 product as two instructions each (W and its
+//               remainders stacked into one 128-row operand) into one of two TMEM accumulators
+//               of 128 columns, tcgen05.commit frees the stage and publishes the accumulator;
 //   warps 4-7, 12-15  epilogue (even / odd tiles): TMEM -> registers -> one padded half row of
 //               shared memory per thread -> read back 8 lanes per row -> 16-byte vector atomics
 //               into Y[I[t], :], four whole 128-byte lines per warp instruction.  (One bulk reduce-add per row, cp.reduce.async.bulk, was
@@ -241,14 +242,15 @@ constexpr int kPThreads = 512;
 constexpr int kZStages = 2;
 constexpr int kZBox = kTM * 128;     // one swizzled box: 128 rows x 32 floats
 constexpr int kZTile = 2 * kZBox;    // 32 KB
-constexpr int kWBox = kF * 128;      // 64 rows x 32 floats
-constexpr int kWPart = 2 * kWBox;    // 16 KB
+// W_r as ONE operand of 128 rows: rows 0..63 = W (its upper 19 bits are what the tensor core
+// reads), rows 64..127 = the remainders W - tf32(W); two boxes of 128 rows x 32 floats
+constexpr int kWBox = 2 * kF * 128;  // 16 KB
+constexpr int kWAll = 2 * kWBox;     // 32 KB
 constexpr int kOutStride = 128 + 16;  // padded half row: 16-byte stores of 32 rows spread over all banks
 constexpr int kOffZRaw = 0;
 constexpr int kOffZLo = kOffZRaw + kZStages * kZTile;
-constexpr int kOffWHi = kOffZLo + kZStages * kZTile;
-constexpr int kOffWLo = kOffWHi + kWPart;
-constexpr int kOffOut = kOffWLo + kWPart;
+constexpr int kOffW = kOffZLo + kZStages * kZTile;
+constexpr int kOffOut = kOffW + kWAll;
 constexpr int kPSmemBytes = kOffOut + 2 * kTM * kOutStride + 1024;  // two epilogue groups; + slack to align to 1024 bytes
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -342,13 +344,13 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
       tc05::prefetch_tensormap(&tm_z);
     }
     __syncwarp();
-    tc05::tmem_alloc(&s_tmem, 2 * kF);
+    tc05::tmem_alloc(&s_tmem, 4 * kF);
   }
   tc05::fence_before_sync();
   __syncthreads();
   tc05::fence_after_sync();
   if (s_tile[0] == 0) {  // no tile for this block (uniform)
-    if (warp == 0) tc05::tmem_dealloc(s_tmem, 2 * kF);
+    if (warp == 0) tc05::tmem_dealloc(s_tmem, 4 * kF);
     return;
   }
   const uint32_t tmem = s_tmem;
@@ -373,12 +375,15 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
   } else if (warp == 1) {
     // ---- MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtTF32, kTM, kF, /*a_mn=*/0, /*b_mn=*/0);
+      // Two instructions per K-step instead of three: z * [W; Wlo]^T (N = 128: columns 0..63
+      // receive z*W, columns 64..127 z*Wlo) and zlo * W^T (N = 64, added to columns 0..63); the
+      // epilogue adds the two column halves.  An MMA of this size costs about the same whatever
+      // N <= 128, so the instruction count is what the issue warp is bound by.
+      constexpr uint32_t idesc128 = tc05::instr_desc(tc05::kFmtTF32, kTM, 2 * kF, /*a_mn=*/0, /*b_mn=*/0);
+      constexpr uint32_t idesc64 = tc05::instr_desc(tc05::kFmtTF32, kTM, kF, /*a_mn=*/0, /*b_mn=*/0);
       // descriptors are built once; the loop only advances their address fields (a lone thread
-      // issues one dependent instruction every few clocks, so rebuilding four descriptors per
-      // K-step made this warp the slowest role)
-      const uint64_t dwh0 = tc05::smem_desc_swizzled(tc05::smem_u32(base + kOffWHi), 0, 1024, tc05::kSwizzle128B);
-      const uint64_t dwl0 = tc05::smem_desc_swizzled(tc05::smem_u32(base + kOffWLo), 0, 1024, tc05::kSwizzle128B);
+      // issues one dependent instruction every few clocks)
+      const uint64_t dw0 = tc05::smem_desc_swizzled(tc05::smem_u32(base + kOffW), 0, 1024, tc05::kSwizzle128B);
       const uint64_t dzh0 = tc05::smem_desc_swizzled(tc05::smem_u32(base + kOffZRaw), 0, 1024, tc05::kSwizzle128B);
       const uint64_t dzl0 = tc05::smem_desc_swizzled(tc05::smem_u32(base + kOffZLo), 0, 1024, tc05::kSwizzle128B);
       for (int k = 0; k < tiles_per_cta; ++k) {
@@ -388,15 +393,13 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
         tc05::fence_after_sync();
         const uint64_t dzh_s = tc05::desc_advance(dzh0, s * kZTile);
         const uint64_t dzl_s = tc05::desc_advance(dzl0, s * kZTile);
-        const uint32_t acc = tmem + buf * kF;
+        const uint32_t acc = tmem + buf * 2 * kF;
 #pragma unroll
         for (int ks = 0; ks < kF / 8; ++ks) {  // K = 8 floats = 32 bytes inside the swizzled row
           const uint32_t zo = (ks >> 2) * kZBox + (ks & 3) * 32, wo = (ks >> 2) * kWBox + (ks & 3) * 32;
-          const uint64_t dzh = tc05::desc_advance(dzh_s, zo), dzl = tc05::desc_advance(dzl_s, zo);
-          const uint64_t dwh = tc05::desc_advance(dwh0, wo), dwl = tc05::desc_advance(dwl0, wo);
-          tc05::mma_tf32(acc, dzl, dwh, idesc, ks > 0 ? 1u : 0u);  // small terms first
-          tc05::mma_tf32(acc, dzh, dwl, idesc, 1u);
-          tc05::mma_tf32(acc, dzh, dwh, idesc, 1u);
+          const uint64_t dw = tc05::desc_advance(dw0, wo);
+          tc05::mma_tf32(acc, tc05::desc_advance(dzh_s, zo), dw, idesc128, ks > 0 ? 1u : 0u);
+          tc05::mma_tf32(acc, tc05::desc_advance(dzl_s, zo), dw, idesc64, 1u);
         }
         tc05::mma_commit(&bar_empty[s]);
         tc05::mma_commit(&bar_acc_full[buf]);
@@ -420,9 +423,8 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
           const int fo = ch >> 4, kc = ch & 15;
           const float4 v = __ldg(wr + ch);
           const float4 l = make_float4(v.x - tf32_hi(v.x), v.y - tf32_hi(v.y), v.z - tf32_hi(v.z), v.w - tf32_hi(v.w));
-          const int off = swz_off(fo, kc, kWBox);
-          *reinterpret_cast<float4*>(base + kOffWHi + off) = v;
-          *reinterpret_cast<float4*>(base + kOffWLo + off) = l;
+          *reinterpret_cast<float4*>(base + kOffW + swz_off(fo, kc, kWBox)) = v;
+          *reinterpret_cast<float4*>(base + kOffW + swz_off(kF + fo, kc, kWBox)) = l;
         }
       }
       if (!tc05::mbar_wait(&bar_full[s], use & 1)) { ok = false; break; }
@@ -461,11 +463,14 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
       const int dst_next = __ldg(indices_i + min(tw.row0 + t, nnz_i - 1));
       if (!tc05::mbar_wait(&bar_acc_full[grp], buse & 1)) { ok = false; break; }
       tc05::fence_after_sync();
-      const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + grp * kF;
+      const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + grp * 2 * kF;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {  // 32 columns at a time
-        uint32_t r[32];
-        tc05::tmem_ld32(taddr + half * 32, r);
+      for (int half = 0; half < 2; ++half) {  // 32 output columns at a time
+        uint32_t r[32], r2[32];
+        tc05::tmem_ld32(taddr + half * 32, r);            // z*W + zlo*W
+        tc05::tmem_ld32(taddr + kF + half * 32, r2);      // z*Wlo
+#pragma unroll
+        for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) + __uint_as_float(r2[q]));
         if (half == 1) {  // both halves are in registers or on their way to Y: accumulator free
           tc05::fence_before_sync();
           mbar_arrive(&bar_acc_empty[grp]);
@@ -502,7 +507,7 @@ rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restric
   }
   tc05::fence_before_sync();
   __syncthreads();
-  if (warp == 0) tc05::tmem_dealloc(tmem, 2 * kF);
+  if (warp == 0) tc05::tmem_dealloc(tmem, 4 * kF);
 }
 
 // 0 when launched, 1 when this path cannot take the call (caller falls back), -1 on error

@@ -52,7 +52,6 @@ struct HybTable {
   int32_t chunks_per_row[kMaxB];   // 1 unless width > item_slots
   int32_t block_start[kMaxB + 1];
   int32_t row_base[kMaxB];         // buckets without a row-id array: ELL row r -> output row base + r
-  int32_t item;                    // lean kernel: stored slots per work item
   int32_t nb;
 };
 
@@ -291,7 +290,7 @@ __global__ void __launch_bounds__(kThreads, 4)
 hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b,
                      float* __restrict__ c, int feat, int all_atomic) {
   constexpr int SUBS = kThreads / LPR;
-  const int ITEM = tb.item;
+  constexpr int ITEM = lean_item_slots(LPR, W);
   const int lane = threadIdx.x % LPR;
   const int sub = threadIdx.x / LPR;
   const unsigned mask = group_mask<LPR>();
@@ -637,15 +636,7 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
     lanes = lanes_per_row(feat, vec4, n, lane_w);
   }
   lean = lean && feat % (lane_w * lanes) == 0;
-  // lean kernel: SPARSETIR_HYB_ITEM_BATCHES (2, 4 or 8 id batches of `lanes` slots per work item)
-  // overrides the default for tuning; 8 is the most the row-id registers of an item hold
-  static const int item_batches = [] {
-    const char* e = std::getenv("SPARSETIR_HYB_ITEM_BATCHES");
-    const int v = e ? std::atoi(e) : 0;
-    return (v == 2 || v == 4 || v == 8) ? v : 0;
-  }();
-  tb.item = item_batches > 0 ? item_batches * lanes : lean_item_slots(lanes, lane_w);
-  plan_items(tb, lean ? tb.item : item_slots(lanes));
+  plan_items(tb, lean ? lean_item_slots(lanes, lane_w) : item_slots(lanes));
 
   bool after_rearm = false;  // this call's re-arm kernel directly precedes the SpMM launch
   if (flags & SPARSETIR_HYB_ZERO_C) {

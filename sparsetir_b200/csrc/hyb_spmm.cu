@@ -33,7 +33,7 @@ namespace {
 #ifndef SPTIR_HYB_MIN_BLOCKS
 #define SPTIR_HYB_MIN_BLOCKS 3  // resident blocks per SM the register budget is sized for
 #endif
-constexpr int kThreads = 256;
+constexpr int kThreads = 128;
 constexpr int kMaxB = SPARSETIR_HYB_MAX_BUCKETS;
 
 // Stored slots covered by one work item (one sub-warp of `lpr` lanes): four id batches, so that
@@ -286,7 +286,7 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
 }
 
 template <int LPR, int W>
-__global__ void __launch_bounds__(kThreads, 4)
+__global__ void __launch_bounds__(kThreads, 8)
 hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b,
                      float* __restrict__ c, int feat, int all_atomic) {
   constexpr int SUBS = kThreads / LPR;

@@ -361,6 +361,31 @@ def ours_arm(args, rank, world, local_rank):
     h2d = sum(4 * g.n * f for f in FEATS)
     d2h = sum(4 * g.m * f for f in FEATS)
 
+    # ---- N > 1: the shard kernels followed by the all-gather of the output rows (device-resident X)
+    gather_ms = None
+    if world > 1:
+        shard_rows = [int(cuts[k + 1] - cuts[k]) for k in range(world)]
+        y_all = {f: torch.empty(g.m * f, device=device) for f in FEATS}
+
+        def gather_step():
+            for f in FEATS:
+                calls[f]()
+                sdist.all_gather_rows(y_dev[f], shard_rows, f, out=y_all[f])
+
+        for _ in range(2):
+            gather_step()
+        barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(e_steps):
+            gather_step()
+        a1.record()
+        barrier()
+        t = torch.tensor([a0.elapsed_time(a1) / e_steps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        gather_ms = float(t.item())
+        del y_all
+
     # ---- the largest graph of the benchmark set (SDDMM, 1.2e8 positions) sharded the same way:
     # collective, so every rank runs it; rank 0 reports it
     ops_sharded = None
@@ -441,6 +466,7 @@ def ours_arm(args, rank, world, local_rank):
         "gpu_launches": launches_per_call * len(FEATS) * args.steps,
         "roofline": roofline, "cpu_baseline": cpu, "clocks": clocks, "per_feat": per_f,
         "graph_replay_ms_per_step": graph_ms, "eager_ms_per_step": eager_ms_step,
+        "ms_per_step_with_allgather_of_y": gather_ms,
         "alg_gbs": sum(spmm_bytes(m_loc, g.n, nnz_loc, f) for f in FEATS) / (ms_step * 1e-3) / 1e9,
     }
     if ops_sharded is not None:

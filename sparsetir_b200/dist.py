@@ -90,17 +90,22 @@ def all_gather_blocks(local: torch.Tensor, sizes: Sequence[int], out: Optional[t
     if local.is_cuda and biggest * world == total:  # equal blocks: gather straight into place
         dist.all_gather_into_tensor(out, local.contiguous(), group=group)
         return out
-    if local.is_cuda and biggest * world <= 2 * total + 1024:
-        # Nearly equal blocks (the nnz-balanced cuts give that) on GPUs: ONE all-gather of blocks
-        # padded to the largest, then the pieces are copied to their places — one collective
-        # instead of one broadcast per rank.
-        padded = torch.empty(biggest, dtype=local.dtype, device=local.device)
-        padded[:local.numel()].copy_(local)
-        staged = torch.empty(world * biggest, dtype=local.dtype, device=local.device)
-        dist.all_gather_into_tensor(staged, padded, group=group)
+    if local.is_cuda:
+        # Unequal blocks on GPUs: every rank sends its block to every other rank and receives
+        # theirs straight into place, all in ONE batched group of point-to-point operations
+        # (NCCL runs them concurrently over NVLink; nothing is staged or padded).
+        pieces[rank].copy_(local)
+        to_global = (lambda k: dist.get_global_rank(group, k)) if group is not None else (lambda k: k)
+        p2p = []
         for k in range(world):
+            if k == rank:
+                continue
+            if sizes[rank] > 0:
+                p2p.append(dist.P2POp(dist.isend, pieces[rank], to_global(k), group))
             if sizes[k] > 0:
-                pieces[k].copy_(staged[k * biggest:k * biggest + int(sizes[k])])
+                p2p.append(dist.P2POp(dist.irecv, pieces[k], to_global(k), group))
+        for req in (dist.batch_isend_irecv(p2p) if p2p else []):
+            req.wait()
         return out
     # Otherwise an all-gather of unequal blocks is one broadcast per block (the library all-gather
     # wants equal sizes on some backends); the broadcasts are issued together and waited for together.

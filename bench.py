@@ -415,7 +415,7 @@ def ours_arm(args, rank, world, local_rank):
                 "frac": achieved / peaks["hbm_gbs"],
                 # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the committed ncu
                 # capture of the same workload (profiles/hyb_spmm_lean_kernel_F512.md), one GPU
-                "traffic": 690.9e6 if (world == 1 and FEATS[-1] == 512) else None,
+                "traffic": 703.8e6 if (world == 1 and FEATS[-1] == 512) else None,
                 "peak_source": peaks["source"],
                 "kernel": "hyb_spmm_lean_kernel<32> (+ hyb_rearm_kernel), F=512 call",
                 "algorithmic_bytes": alg_bytes, "launch_ms": per_f_ms[f_dom]}

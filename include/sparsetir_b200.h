@@ -176,6 +176,30 @@ SPARSETIR_API int sparsetir_bsrmm(SPARSETIR_PACKED_ARGS);
  * examples/rgms/rgcn/bench_rgcn_non_composable.py:108). */
 SPARSETIR_API int sparsetir_rgms(SPARSETIR_PACKED_ARGS);
 
+/* Row sums of a CSR matrix: b[i] = sum of the stored entries of row i.
+ * args: (a f32[nnz], b f32[n], indptr i32[n+1] [, indices i32[nnz]] [, n [, m], nnz]).  Replaces the
+ * functions built from `segment_reduce` and `csr_reduce`
+ * (tests/python/sparsetir/sparse_tir_scripts.py:74-110). */
+SPARSETIR_API int sparsetir_csr_reduce(SPARSETIR_PACKED_ARGS);
+
+/* Row-wise softmax over the stored entries, exactly as the reference defines it:
+ *   b[i,j] = exp(a[i,j]) / sum_j exp(a[i,j] - max_j a[i,j])
+ * (the numerator is not shifted by the row maximum: tests/python/sparsetir/sparse_tir_scripts.py:503-528).
+ * args: (a f32[nnz], b f32[nnz], indptr i32[n+1], indices i32[nnz] [, n, nnz]). */
+SPARSETIR_API int sparsetir_sparse_softmax(SPARSETIR_PACKED_ARGS);
+
+/* Scatter of the entries of a CSR matrix into the blocks of a BSR matrix with a given block
+ * structure; elements no entry maps to are left untouched.
+ * args: (a f32[nnz_in], b f32[nnz_out*blk*blk], indptr_in, indices_in, indptr_out, indices_out,
+ *        [m_in, n_in, m_out, n_out, nnz_in, nnz_out,] blk_size)
+ * (`csr2bsr`, tests/python/sparsetir/sparse_tir_scripts.py:532-557). */
+SPARSETIR_API int sparsetir_csr2bsr(SPARSETIR_PACKED_ARGS);
+
+/* Block-ELL SpMM, fp32: c[i,bi,f] = sum_{j<col} sum_bj a[i,j,bi,bj] * b[indices[i,j],bj,f].
+ * args: (a f32[nb*col*blk*blk], b f32[mb*blk*feat], c f32[nb*blk*feat], indices i32[nb*col],
+ *        nb, mb, feat_size, col, blk)   (`ellmm`, tests/python/sparsetir/sparse_tir_scripts.py:150-181). */
+SPARSETIR_API int sparsetir_ellmm(SPARSETIR_PACKED_ARGS);
+
 /* Condensed tensor-core SpMM ("tcspmm"), fp16 operands, fp32 accumulation:
  *   C[io*t + ii, f] = sum_{jo in [indptr[io], indptr[io+1])} sum_{ji < g} A[jo,ii,ji] * B[indices[jo*g+ji], f]
  * args: (a f16[nnzb*t*g], b f16[nb*g*feat], c f16 or f32 [mb*t*feat], indptr i32[mb+1],
@@ -224,6 +248,17 @@ SPARSETIR_API int sparsetir_rgms_raw(const float* a, const float* w, const float
                                      int n, int num_rels, int feat, int nnz_i, int nnz_j,
                                      int device_id, void* stream);
 
+SPARSETIR_API int sparsetir_csr_reduce_raw(const float* a, float* b, const int32_t* indptr, int n,
+                                           int nnz, int device_id, void* stream);
+SPARSETIR_API int sparsetir_sparse_softmax_raw(const float* a, float* b, const int32_t* indptr, int n,
+                                               int nnz, int device_id, void* stream);
+SPARSETIR_API int sparsetir_csr2bsr_raw(const float* a, float* b, const int32_t* indptr_in,
+                                        const int32_t* indices_in, const int32_t* indptr_out,
+                                        const int32_t* indices_out, int m_in, int nnz_in, int blk,
+                                        int device_id, void* stream);
+SPARSETIR_API int sparsetir_ellmm_raw(const float* a, const float* b, float* c, const int32_t* indices,
+                                      int nb, int mb, int feat, int col, int blk, int device_id,
+                                      void* stream);
 SPARSETIR_API int sparsetir_tcspmm_raw(const void* a_f16, const void* b_f16, void* c, int c_is_f16,
                                        const int32_t* indptr, const int32_t* indices, int mb, int nb,
                                        int nnzb, int feat, int tile_size, int group_size,

@@ -227,3 +227,36 @@ def tcspmm_f16(a, b, indptr, indices, mb, t, g, feat) -> np.ndarray:
     lib().oracle_tcspmm_f16(a.ctypes.data_as(u16p), b.ctypes.data_as(u16p), _p(c, _f32p), _p(indptr, _i32p),
                             _p(indices, _i32p), int(mb), int(t), int(g), int(feat))
     return c
+
+
+def csr_reduce(a, indptr) -> np.ndarray:
+    a, indptr = _f32(a), _i32(indptr)
+    n = len(indptr) - 1
+    b = np.empty((n,), np.float32)
+    lib().oracle_csr_reduce(_p(a, _f32p), _p(b, _f32p), _p(indptr, _i32p), int(n))
+    return b
+
+
+def sparse_softmax(a, indptr) -> np.ndarray:
+    a, indptr = _f32(a), _i32(indptr)
+    b = np.empty_like(a)
+    lib().oracle_sparse_softmax(_p(a, _f32p), _p(b, _f32p), _p(indptr, _i32p), int(len(indptr) - 1))
+    return b
+
+
+def csr2bsr(a, b, indptr_in, indices_in, indptr_out, indices_out, blk) -> np.ndarray:
+    """Writes the stored entries into (and returns) the block array ``b`` [nnzb, blk, blk]."""
+    a = _f32(a)
+    assert b.dtype == np.float32 and b.flags.c_contiguous
+    ip, ix, op, ox = map(_i32, (indptr_in, indices_in, indptr_out, indices_out))
+    lib().oracle_csr2bsr(_p(a, _f32p), _p(b, _f32p), _p(ip, _i32p), _p(ix, _i32p), _p(op, _i32p),
+                         _p(ox, _i32p), int(len(ip) - 1), int(blk))
+    return b
+
+
+def ellmm(a, b, indices, nb, col, blk, feat) -> np.ndarray:
+    a, b, indices = _f32(a), _f32(b), _i32(indices)
+    c = np.empty((nb * blk, feat), np.float32)
+    lib().oracle_ellmm(_p(a, _f32p), _p(b, _f32p), _p(c, _f32p), _p(indices, _i32p), int(nb), int(col),
+                       int(blk), int(feat))
+    return c

@@ -23,6 +23,8 @@
  *     (tests/python/sparsetir/sparse_tir_lowered_buffer_scripts.py:530-549),
  *     which this file follows statement by statement, and by numpy
  *     searchsorted in the test-suite.
+ *   - csr_reduce / sparse_softmax / csr2bsr / ellmm : follow the lowered code; checked against
+ *     numpy in the test-suite; parity unpinned (the reference stores no vectors for them).
  *   - csrmm / ell_spmm / sddmm / bsrmm / rgms / rgms_ell3d / tcspmm : parity unpinned.  The
  *     reference stores no numeric vectors for them and cannot be built or
  *     imported on this machine; the test-suite bounds their error against an
@@ -604,5 +606,79 @@ ORACLE_API void oracle_tcspmm_f16(const uint16_t* a, const uint16_t* b, float* c
           const _Float16* br = bh + (size_t)indices[(size_t)jo * g + ji] * feat;
           for (int f = 0; f < feat; ++f) cr[f] += av * (float)br[f];
         }
+    }
+}
+
+/* --------------------------------------- csr_reduce / segment_reduce, sparse_softmax, csr2bsr, ellmm */
+/*
+ * B[i] = sum_j A[i, j] over the stored entries of row i, init 0
+ * (tests/python/sparsetir/sparse_tir_scripts.py:74-110: segment_reduce and csr_reduce; the
+ * column indices take no part in the arithmetic).
+ */
+ORACLE_API void oracle_csr_reduce(const float* a, float* b, const int32_t* indptr, int n) {
+  for (int i = 0; i < n; ++i) {
+    float s = 0.f;
+    for (int p = indptr[i]; p < indptr[i + 1]; ++p) s += a[p];
+    b[i] = s;
+  }
+}
+
+/*
+ * sparse_softmax, tests/python/sparsetir/sparse_tir_scripts.py:503-528, lowered
+ * sparse_tir_lowered_buffer_scripts.py:997-1046, statement by statement:
+ *   TMP[i]  = max_j A[i,j]            (init: lowest float)
+ *   TMP1[i] = sum_j exp(A[i,j] - TMP[i])
+ *   B[i,j]  = exp(A[i,j]) / TMP1[i]   (the numerator is NOT shifted by the maximum there)
+ */
+#include <float.h>
+#include <math.h>
+ORACLE_API void oracle_sparse_softmax(const float* a, float* b, const int32_t* indptr, int n) {
+  for (int i = 0; i < n; ++i) {
+    float mx = -FLT_MAX, sum = 0.f;
+    for (int p = indptr[i]; p < indptr[i + 1]; ++p) mx = a[p] > mx ? a[p] : mx;
+    for (int p = indptr[i]; p < indptr[i + 1]; ++p) sum += expf(a[p] - mx);
+    for (int p = indptr[i]; p < indptr[i + 1]; ++p) b[p] = expf(a[p]) / sum;
+  }
+}
+
+/*
+ * csr2bsr, sparse_tir_scripts.py:532-557, lowered sparse_tir_lowered_buffer_scripts.py:1049-1135:
+ * every stored entry (i, j) is written to block (i / blk, j / blk), element (i % blk, j % blk);
+ * the block's position in its block row is the lower bound of j / blk in indices_out.
+ * Elements of B that no entry maps to are left as they are.
+ */
+ORACLE_API void oracle_csr2bsr(const float* a, float* b, const int32_t* indptr_in,
+                               const int32_t* indices_in, const int32_t* indptr_out,
+                               const int32_t* indices_out, int m_in, int blk) {
+  for (int i = 0; i < m_in; ++i)
+    for (int p = indptr_in[i]; p < indptr_in[i + 1]; ++p) {
+      int bo = indptr_out[i / blk];
+      int low = 0, high = indptr_out[i / blk + 1] - bo;
+      int key = indices_in[p] / blk;
+      while (low < high) {
+        int mid = low + (high - low) / 2;
+        if (indices_out[mid + bo] < key) low = mid + 1; else high = mid;
+      }
+      b[((size_t)(low + bo) * blk + i % blk) * blk + indices_in[p] % blk] = a[p];
+    }
+}
+
+/*
+ * Block-ELL SpMM `ellmm`, sparse_tir_scripts.py:150-181, lowered
+ * sparse_tir_lowered_buffer_scripts.py:252-288:
+ *   C[i, bi, f] = sum_{j < col} sum_bj A[i, j, bi, bj] * B[indices[i, j], bj, f]   (init 0)
+ */
+ORACLE_API void oracle_ellmm(const float* a, const float* b, float* c, const int32_t* indices,
+                             int nb, int col, int blk, int feat) {
+  for (int i = 0; i < nb; ++i)
+    for (int bi = 0; bi < blk; ++bi) {
+      float* cr = c + ((size_t)i * blk + bi) * feat;
+      for (int f = 0; f < feat; ++f) cr[f] = 0.f;
+      for (int j = 0; j < col; ++j) {
+        const float* ab = a + (((size_t)i * col + j) * blk + bi) * blk;
+        const float* bb = b + (size_t)indices[(size_t)i * col + j] * blk * feat;
+        for (int bj = 0; bj < blk; ++bj)
+          for (int f = 0; f < feat; ++f) cr[f] += ab[bj] * bb[(size_t)bj * feat + f];
+      }
     }
 }

@@ -72,6 +72,10 @@ PACKED_SYMBOLS = (
     "sparsetir_rgms",
     "sparsetir_rgms_ell3d",
     "sparsetir_tcspmm",
+    "sparsetir_csr_reduce",
+    "sparsetir_sparse_softmax",
+    "sparsetir_csr2bsr",
+    "sparsetir_ellmm",
 )
 
 # every other exported symbol: name -> (restype, argtypes)
@@ -92,6 +96,10 @@ PLAIN_SYMBOLS = {
     "sparsetir_sddmm_edge_to_row_raw": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "sparsetir_bsrmm_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_raw": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),
+    "sparsetir_csr_reduce_raw": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "sparsetir_sparse_softmax_raw": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
+    "sparsetir_csr2bsr_raw": (_i, [_vp] * 6 + [_i, _i, _i, _i, _vp]),
+    "sparsetir_ellmm_raw": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_tcspmm_raw": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_ell3d_raw": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_noalloc": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),

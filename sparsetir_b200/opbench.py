@@ -162,6 +162,18 @@ def bench_sddmm(device, peaks, feats=(32, 64, 128, 256)) -> dict:
     err = (c[e].double() - want).abs().max().item()
     out["spot_check_max_abs_err"] = err
     assert err < 1e-4, err
+    # the row-wise operators that follow SDDMM in attention-style pipelines, on the same graph:
+    # row sums and the reference's sparse softmax of the per-position values (streaming, HBM-bound)
+    del a, b
+    rs = torch.empty(n, device=device)
+    fn = ops.csr_reduce.prepare(scale, rs, indptr, indices)
+    ms = _time(fn, number=5, repeat=3, warmup=2)
+    byts = 4 * nnz + 4 * (n + 1) + 4 * n
+    out["csr_reduce"] = _entry(ms, float(nnz), byts, peaks)
+    fn = ops.sparse_softmax.prepare(scale, c, indptr, indices)
+    ms = _time(fn, number=5, repeat=3, warmup=2)
+    byts = 8 * nnz + 4 * (n + 1)
+    out["sparse_softmax"] = _entry(ms, 4.0 * nnz, byts, peaks)
     return out
 
 

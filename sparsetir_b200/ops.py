@@ -173,6 +173,10 @@ bsrmm = PackedFunc("sparsetir_bsrmm")
 rgms = PackedFunc("sparsetir_rgms")
 rgms_ell3d = PackedFunc("sparsetir_rgms_ell3d")
 tcspmm = PackedFunc("sparsetir_tcspmm")
+csr_reduce = PackedFunc("sparsetir_csr_reduce")
+sparse_softmax = PackedFunc("sparsetir_sparse_softmax")
+csr2bsr = PackedFunc("sparsetir_csr2bsr")
+ellmm = PackedFunc("sparsetir_ellmm")
 
 
 def hyb_args(x: torch.Tensor, y: torch.Tensor, buckets: Sequence[Sequence[torch.Tensor]],

@@ -509,6 +509,60 @@ def test_tcspmm_half_output_weights_and_empty_tiles(cuda_device):
     assert np.all(got[16 * 13:16 * 37] == 0)  # tiles 13..36 have no entries
 
 
+# ------------------------------------------------------------------ reduce / softmax / csr2bsr / ellmm
+@pytest.mark.parametrize("gen", ["short", "long"])
+def test_csr_reduce_and_sparse_softmax(cuda_device, gen):
+    c = (dg.csr_powerlaw(n=5000, max_deg=3000, seed=2) if gen == "short"
+         else dg.csr_lognormal(n=800, mu=4.5, sigma=0.8, max_deg=700, seed=3))
+    a = (dg.dense_operand(1, c.nnz, 1).reshape(-1) * 4).astype(np.float32)
+    ip, ix = dev(c.indptr, cuda_device), dev(c.indices, cuda_device)
+    b = torch.full((c.m,), 9.0, device=cuda_device)
+    ops.csr_reduce(dev(a, cuda_device), b, ip, ix, c.m, c.n, c.nnz)   # csr_reduce signature
+    b2 = torch.full((c.m,), 9.0, device=cuda_device)
+    ops.csr_reduce(dev(a, cuda_device), b2, ip)                        # segment_reduce, sizes inferred
+    torch.cuda.synchronize()
+    want = orc.csr_reduce(a, c.indptr)
+    close(b, want, atol=1e-4)
+    close(b2, want, atol=1e-4)
+    sm = torch.full((c.nnz,), -1.0, device=cuda_device)
+    ops.sparse_softmax(dev(a, cuda_device), sm, ip, ix)
+    torch.cuda.synchronize()
+    close(sm, orc.sparse_softmax(a, c.indptr), rtol=1e-4, atol=1e-6)
+
+
+def test_csr2bsr_bit_exact(cuda_device):
+    c = dg.csr_powerlaw(n=1000, max_deg=400, seed=6)
+    for blk in (4, 32):
+        rows = np.repeat(np.arange(c.m), np.diff(c.indptr))
+        mb, nbk = -(-c.m // blk), -(-c.n // blk)
+        pattern = np.zeros((mb, nbk), bool)
+        pattern[rows // blk, c.indices // blk] = True
+        pattern[np.arange(mb), np.arange(mb) % nbk] = True  # blocks that receive nothing stay as they are
+        ip_out = np.concatenate([[0], np.cumsum(pattern.sum(1))]).astype(np.int32)
+        ix_out = np.nonzero(pattern)[1].astype(np.int32)
+        b = torch.full((len(ix_out) * blk * blk,), -2.0, device=cuda_device)
+        ops.csr2bsr(dev(c.data, cuda_device), b, dev(c.indptr, cuda_device), dev(c.indices, cuda_device),
+                    dev(ip_out, cuda_device), dev(ix_out, cuda_device), c.m, c.n, mb, nbk, c.nnz, len(ix_out), blk)
+        torch.cuda.synchronize()
+        want = orc.csr2bsr(c.data, np.full((len(ix_out), blk, blk), -2.0, np.float32), c.indptr, c.indices,
+                           ip_out, ix_out, blk)
+        assert np.array_equal(b.cpu().numpy().reshape(want.shape), want)
+
+
+@pytest.mark.parametrize("nb,mb,col,blk,feat", [(40, 50, 3, 16, 128), (9, 9, 5, 32, 96), (17, 30, 1, 4, 200),
+                                                (6, 6, 0, 8, 32)])
+def test_ellmm_matches_oracle(cuda_device, nb, mb, col, blk, feat):
+    rng = np.random.default_rng(nb + feat)
+    a = rng.standard_normal((nb, col, blk, blk)).astype(np.float32)
+    ix = rng.integers(0, mb, size=(nb, col)).astype(np.int32)
+    b = rng.standard_normal((mb * blk, feat)).astype(np.float32)
+    c = torch.full((nb * blk * feat,), 5.0, device=cuda_device)
+    ops.ellmm(dev(a.reshape(-1), cuda_device), dev(b.reshape(-1), cuda_device), c, dev(ix.reshape(-1), cuda_device),
+              nb, mb, feat, col, blk)
+    torch.cuda.synchronize()
+    close(c, orc.ellmm(a, b, ix, nb, col, blk, feat), atol=ATOL * 8)
+
+
 # ------------------------------------------------------------------------------ streams
 def test_calls_run_on_the_current_torch_stream(cuda_device):
     c = dg.csr_poisson(m=2000, n=2000, mean_deg=10, seed=30)

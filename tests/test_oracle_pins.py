@@ -205,3 +205,45 @@ def test_rgms_ell3d_oracle_equals_fp64_rgms_of_the_csf_form():
     want = refimpl.rgms_f64(np.ones(cf.nnz_j), w, x, cf.indptr_i, cf.indices_i, cf.indptr_j,
                             cf.indices_j, cf.m)
     np.testing.assert_allclose(got, want, rtol=RTOL, atol=ATOL * 4)
+
+
+def test_small_operators_against_numpy():
+    c = dg.csr_lognormal(n=300, mu=2.0, sigma=1.0, max_deg=100, seed=5)
+    # csr_reduce / segment_reduce
+    want = np.add.reduceat(np.concatenate([c.data.astype(np.float64), [0.0]]), c.indptr[:-1])
+    want[np.diff(c.indptr) == 0] = 0.0
+    np.testing.assert_allclose(orc.csr_reduce(c.data, c.indptr), want, rtol=1e-5, atol=1e-6)
+    # sparse_softmax as the reference writes it: exp(a) / sum exp(a - max)
+    a = (dg.dense_operand(1, c.nnz, 1).reshape(-1) * 3).astype(np.float32)
+    got = orc.sparse_softmax(a, c.indptr)
+    for i in (0, 7, 150, 299):
+        seg = a[c.indptr[i]:c.indptr[i + 1]].astype(np.float64)
+        np.testing.assert_allclose(got[c.indptr[i]:c.indptr[i + 1]], np.exp(seg) / np.exp(seg - seg.max()).sum(),
+                                   rtol=1e-5)
+    # csr2bsr: dense views of both matrices agree
+    blk = 4
+    dense = np.zeros((c.m, c.n), np.float32)
+    rows = np.repeat(np.arange(c.m), np.diff(c.indptr))
+    dense[rows, c.indices] = c.data
+    mb = -(-c.m // blk)
+    pattern = np.zeros((mb, -(-c.n // blk)), bool)
+    pattern[rows // blk, c.indices // blk] = True
+    ip_out = np.concatenate([[0], np.cumsum(pattern.sum(1))]).astype(np.int32)
+    ix_out = np.nonzero(pattern)[1].astype(np.int32)
+    b = orc.csr2bsr(c.data, np.zeros((len(ix_out), blk, blk), np.float32), c.indptr, c.indices, ip_out, ix_out, blk)
+    back = np.zeros((mb * blk, pattern.shape[1] * blk), np.float32)
+    for br in range(mb):
+        for p in range(ip_out[br], ip_out[br + 1]):
+            back[br * blk:(br + 1) * blk, ix_out[p] * blk:(ix_out[p] + 1) * blk] = b[p]
+    assert np.array_equal(back[:c.m, :c.n], dense)
+    # block-ELL product against a dense fp64 product
+    nb, mbk, col, bk, feat = 5, 7, 3, 4, 6
+    rng = np.random.default_rng(2)
+    ea = rng.standard_normal((nb, col, bk, bk)).astype(np.float32)
+    ei = rng.integers(0, mbk, size=(nb, col)).astype(np.int32)
+    eb = rng.standard_normal((mbk * bk, feat)).astype(np.float32)
+    want = np.zeros((nb * bk, feat))
+    for i in range(nb):
+        for j in range(col):
+            want[i * bk:(i + 1) * bk] += ea[i, j].astype(np.float64) @ eb[ei[i, j] * bk:(ei[i, j] + 1) * bk]
+    np.testing.assert_allclose(orc.ellmm(ea, eb, ei, nb, col, bk, feat), want, rtol=RTOL, atol=ATOL)

@@ -22,6 +22,8 @@
 namespace sptir {
 
 // defined in rgms_tc.cu
+int csrmm_impl(const float* a, const float* b, float* c, const int32_t* indptr, const int32_t* indices,
+               int m, int n, int feat, int nnz, int device_id, void* stream, bool hub_rows);
 int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,
                    const int32_t* indptr_i, const int32_t* indices_i, const int32_t* indptr_j,
                    const int32_t* indices_j, int num_rels, int feat, int nnz_i,
@@ -79,7 +81,7 @@ extern "C" int sparsetir_rgms_noalloc(const float* a, const float* w, const floa
   if (scratch_address(device_id, &z) != 0) return -1;
   // launch 1: Z = A_csf * X, every one of the nnz_i rows is written (rows without entries get
   // zeros), so nothing left in the array by an earlier call is ever read
-  if (sparsetir_csrmm_raw(a, x, z, indptr_j, indices_j, nnz_i, n, kFeat, nnz_j, device_id, stream) != 0)
+  if (sptir::csrmm_impl(a, x, z, indptr_j, indices_j, nnz_i, n, kFeat, nnz_j, device_id, stream, /*hub_rows=*/false) != 0)
     return -1;
   // launch 2: Y[I[i], :] += Z[i, :] * W_r^T on the tensor cores
   const int rc = rgms_tc_launch(a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, kFeat,

@@ -97,10 +97,24 @@ def bench_csrmm(device, peaks, flush) -> dict:
     warm = _time(fn, number=1000)
     cold = _time_cold(fn, flush)
     graph = _time_graph(fn, number=200)
-    return {"workload": "csr_spmm_4096_poisson10_F64", "nnz": c.nnz,
-            "warm": _entry(warm, flops, byts, peaks), "cold_l2": _entry(cold, flops, byts, peaks),
-            "graph_replay": _entry(graph, flops, byts, peaks),
-            "bound": "launch latency (ideal 0.4 us at the HBM peak)"}
+    out = {"workload": "csr_spmm_4096_poisson10_F64", "nnz": c.nnz,
+           "warm": _entry(warm, flops, byts, peaks), "cold_l2": _entry(cold, flops, byts, peaks),
+           "graph_replay": _entry(graph, flops, byts, peaks),
+           "bound": "launch latency (ideal 0.4 us at the HBM peak)"}
+    # the same kernel on the graph of the headline workload (no format decomposition): what the
+    # hyb format buys can be read off against the per-F times of the main bench line
+    g = dg.csr_powerlaw(seed=0)
+    gd = (dv(g.data), dv(g.indptr), dv(g.indices))
+    out["powerlaw_169343"] = {"nnz": g.nnz, "per_feat": {}}
+    for f in (32, 128, 512):
+        xg = dv(dg.dense_operand(100 + f, g.n, f).reshape(-1))
+        yg = torch.zeros(g.m * f, device=device)
+        fn = ops.csrmm.prepare(gd[0], xg, yg, gd[1], gd[2])
+        ms = _time_cold(fn, flush, repeat=10)
+        out["powerlaw_169343"]["per_feat"][str(f)] = _entry(
+            ms, 2.0 * g.nnz * f, 4 * (g.m + 1) + 8 * g.nnz + 4 * g.n * f + 4 * g.m * f, peaks)
+        del xg, yg
+    return out
 
 
 def sddmm_graph_on_device(device, n=232_965, mu=5.5, sigma=1.2, max_deg=21_000, seed=0):

@@ -621,3 +621,17 @@ def test_spmm_32_byte_lane_variants_in_child_process(cuda_device):
     code = _WIDE_LANE_CHILD.format(root=root, tests=os.path.join(root, "tests"))
     r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "wide lanes ok" in r.stdout, r.stdout + r.stderr
+
+
+def test_csrmm_hub_rows_take_the_long_row_launches(cuda_device):
+    # a matrix large enough for the hub-row path, with rows far beyond the 2048-entry threshold
+    # next to short and empty ones; the atomically added chunks need a tolerance, not equality
+    deg = np.random.default_rng(4).integers(0, 6, size=9000).astype(np.int64)
+    deg[[0, 4000, 4001, 8999]] = [5000, 2049, 2048, 7001]
+    rng = np.random.default_rng(5)
+    ix = dg.sorted_distinct_columns(rng, deg, 9000)
+    c = dg.CSR(9000, 9000, np.concatenate([[0], np.cumsum(deg)]).astype(np.int32), ix,
+               rng.uniform(-1, 1, size=len(ix)).astype(np.float32))
+    for feat in (32, 128, 512):
+        x = dg.dense_operand(feat, c.n, feat)
+        close(run_csrmm(c, x, cuda_device), oracle_csrmm(c, x), atol=ATOL * 20)

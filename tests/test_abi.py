@@ -162,3 +162,33 @@ def test_other_ops_validation_messages():
         ops.rgms(f32(3), f32(2 * 10), f32(8), f32(8), i32(3), i32(2), i32(3), i32(3))
     with pytest.raises(ops.SparseTIRError, match="indptr_j.shape"):
         ops.rgms(f32(3), f32(2 * 16), f32(8), f32(8), i32(3), i32(2), i32(4), i32(3))
+
+
+def f16(n, **kw):
+    return _fake_cuda(n, L.kDLFloat, 16, **kw)
+
+
+def test_later_operators_validation_messages():
+    # condensed SpMM: lengths must match the scalars; the output may be float16 or float32
+    with pytest.raises(ops.SparseTIRError, match="num_args should be 11"):
+        ops.tcspmm(f16(4), f16(4), f16(4), i32(2), i32(4))
+    with pytest.raises(ops.SparseTIRError, match="a.shape"):
+        ops.tcspmm(f16(5), f16(16 * 8), f16(16 * 8), i32(2), i32(16), 1, 1, 1, 8, 16, 16)
+    with pytest.raises(ops.SparseTIRError, match="c.dtype is expected to be float16"):
+        ops.tcspmm(f16(256), f16(16 * 8), _fake_cuda(16 * 8, L.kDLFloat, 64), i32(2), i32(16), 1, 1, 1, 8, 16, 16)
+    # ELL3D RGMS: (w, x, y) + 4 tensors per bucket + feat_size
+    with pytest.raises(ops.SparseTIRError, match="expected \\(w, x, y"):
+        ops.rgms_ell3d(f32(16), f32(8), f32(8), f32(4), i32(2), 4)
+    with pytest.raises(ops.SparseTIRError, match="do not describe groups x rows x columns"):
+        ops.rgms_ell3d(f32(16), f32(8), f32(8), f32(6), i32(3), i32(6), i32(2), 4)
+    # the small row-wise operators
+    with pytest.raises(ops.SparseTIRError, match="indptr.shape"):
+        ops.csr_reduce(f32(5), f32(3), i32(5))
+    with pytest.raises(ops.SparseTIRError, match="b.shape"):
+        ops.sparse_softmax(f32(5), f32(4), i32(4), i32(5))
+    with pytest.raises(ops.SparseTIRError, match="blk_size must be positive"):
+        ops.csr2bsr(f32(5), f32(4), i32(4), i32(5), i32(2), i32(1), 0)
+    with pytest.raises(ops.SparseTIRError, match="fewer block rows"):
+        ops.csr2bsr(f32(5), f32(4), i32(10), i32(5), i32(2), i32(1), 2)
+    with pytest.raises(ops.SparseTIRError, match="indices.shape"):
+        ops.ellmm(f32(2 * 3 * 16), f32(5 * 4 * 8), f32(2 * 4 * 8), i32(5), 2, 5, 8, 3, 4)

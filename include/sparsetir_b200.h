@@ -200,6 +200,14 @@ SPARSETIR_API int sparsetir_csr2bsr(SPARSETIR_PACKED_ARGS);
  *        nb, mb, feat_size, col, blk)   (`ellmm`, tests/python/sparsetir/sparse_tir_scripts.py:150-181). */
 SPARSETIR_API int sparsetir_ellmm(SPARSETIR_PACKED_ARGS);
 
+/* Sparse attention over the stored positions of a CSR pattern, fp32, one pass:
+ *   o[i,:] = sum_j P[i,j] v[j,:],  P[i,j] = exp(<q[i,:],k[j,:]>) / sum_j exp(<q[i,:],k[j,:]> - row max)
+ * (SDDMM, the reference's sparse softmax and SpMM as one function).
+ * args: (q f32[m*feat], k f32[n*feat], v f32[n*feat], o f32[m*feat], indptr i32[m+1],
+ *        indices i32[nnz] [, m, n, nnz, feat_size]).  Replaces the function built from `fusedmm`
+ * (examples/flash_graph_attention/fusedmm.py:37-96). */
+SPARSETIR_API int sparsetir_fusedmm(SPARSETIR_PACKED_ARGS);
+
 /* Condensed tensor-core SpMM ("tcspmm"), fp16 operands, fp32 accumulation:
  *   C[io*t + ii, f] = sum_{jo in [indptr[io], indptr[io+1])} sum_{ji < g} A[jo,ii,ji] * B[indices[jo*g+ji], f]
  * args: (a f16[nnzb*t*g], b f16[nb*g*feat], c f16 or f32 [mb*t*feat], indptr i32[mb+1],
@@ -259,6 +267,9 @@ SPARSETIR_API int sparsetir_csr2bsr_raw(const float* a, float* b, const int32_t*
 SPARSETIR_API int sparsetir_ellmm_raw(const float* a, const float* b, float* c, const int32_t* indices,
                                       int nb, int mb, int feat, int col, int blk, int device_id,
                                       void* stream);
+SPARSETIR_API int sparsetir_fusedmm_raw(const float* q, const float* k, const float* v, float* o,
+                                        const int32_t* indptr, const int32_t* indices, int m, int n,
+                                        int nnz, int feat, int device_id, void* stream);
 SPARSETIR_API int sparsetir_tcspmm_raw(const void* a_f16, const void* b_f16, void* c, int c_is_f16,
                                        const int32_t* indptr, const int32_t* indices, int mb, int nb,
                                        int nnzb, int feat, int tile_size, int group_size,

@@ -260,3 +260,11 @@ def ellmm(a, b, indices, nb, col, blk, feat) -> np.ndarray:
     lib().oracle_ellmm(_p(a, _f32p), _p(b, _f32p), _p(c, _f32p), _p(indices, _i32p), int(nb), int(col),
                        int(blk), int(feat))
     return c
+
+
+def fusedmm(q, k, v, indptr, indices, m, feat) -> np.ndarray:
+    q, k, v, indptr, indices = _f32(q), _f32(k), _f32(v), _i32(indptr), _i32(indices)
+    o = np.empty((m, feat), np.float32)
+    lib().oracle_fusedmm(_p(q, _f32p), _p(k, _f32p), _p(v, _f32p), _p(o, _f32p), _p(indptr, _i32p),
+                         _p(indices, _i32p), int(m), int(feat))
+    return o

@@ -682,3 +682,38 @@ ORACLE_API void oracle_ellmm(const float* a, const float* b, float* c, const int
       }
     }
 }
+
+/* ----------------------------------------------------------------- fusedmm */
+/*
+ * Sparse attention `fusedmm` of examples/flash_graph_attention/fusedmm.py:37-96, stage by stage:
+ *   score[i,j] = sum_f Q[i,f] K[j,f]                      over the stored positions (i, j)
+ *   temp[i]  = max_j score[i,j];  temp1[i] = sum_j exp(score[i,j] - temp[i])
+ *   softmax[i,j] = exp(score[i,j]) / temp1[i]             (numerator not shifted, as written there)
+ *   O[i,f] = sum_j softmax[i,j] V[j,f]                    (init 0)
+ */
+ORACLE_API void oracle_fusedmm(const float* q, const float* k, const float* v, float* o,
+                               const int32_t* indptr, const int32_t* indices, int m, int feat) {
+#pragma omp parallel for schedule(dynamic, 16)
+  for (int i = 0; i < m; ++i) {
+    int p0 = indptr[i], p1 = indptr[i + 1];
+    float* orow = o + (size_t)i * feat;
+    for (int f = 0; f < feat; ++f) orow[f] = 0.f;
+    if (p1 == p0) continue;
+    float* score = (float*)malloc(sizeof(float) * (size_t)(p1 - p0));
+    float mx = -FLT_MAX, sum = 0.f;
+    for (int p = p0; p < p1; ++p) {
+      const float* kr = k + (size_t)indices[p] * feat;
+      float s = 0.f;
+      for (int f = 0; f < feat; ++f) s += q[(size_t)i * feat + f] * kr[f];
+      score[p - p0] = s;
+      mx = s > mx ? s : mx;
+    }
+    for (int p = p0; p < p1; ++p) sum += expf(score[p - p0] - mx);
+    for (int p = p0; p < p1; ++p) {
+      float w = expf(score[p - p0]) / sum;
+      const float* vr = v + (size_t)indices[p] * feat;
+      for (int f = 0; f < feat; ++f) orow[f] += w * vr[f];
+    }
+    free(score);
+  }
+}

@@ -76,6 +76,7 @@ PACKED_SYMBOLS = (
     "sparsetir_sparse_softmax",
     "sparsetir_csr2bsr",
     "sparsetir_ellmm",
+    "sparsetir_fusedmm",
 )
 
 # every other exported symbol: name -> (restype, argtypes)
@@ -100,6 +101,7 @@ PLAIN_SYMBOLS = {
     "sparsetir_sparse_softmax_raw": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "sparsetir_csr2bsr_raw": (_i, [_vp] * 6 + [_i, _i, _i, _i, _vp]),
     "sparsetir_ellmm_raw": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "sparsetir_fusedmm_raw": (_i, [_vp] * 6 + [_i, _i, _i, _i, _i, _vp]),
     "sparsetir_tcspmm_raw": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_ell3d_raw": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_noalloc": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),

@@ -188,6 +188,29 @@ def bench_sddmm(device, peaks, feats=(32, 64, 128, 256)) -> dict:
     ms = _time(fn, number=5, repeat=3, warmup=2)
     byts = 8 * nnz + 4 * (n + 1)
     out["sparse_softmax"] = _entry(ms, 4.0 * nnz, byts, peaks)
+    # sparse attention in one pass (fusedmm) against the same three operators one after the other
+    f = 64
+    gen.manual_seed(2)
+    qf = (torch.rand(n * f, device=device, generator=gen) * 2 - 1) * (2.0 / math.sqrt(f))
+    kf = torch.rand(n * f, device=device, generator=gen) * 2 - 1
+    vf = torch.rand(n * f, device=device, generator=gen) * 2 - 1
+    of = torch.empty(n * f, device=device)
+    fn = ops.fusedmm.prepare(qf, kf, vf, of, indptr, indices)
+    ms = _time(fn, number=3, repeat=3, warmup=2)
+    flops = 4.0 * nnz * f
+    byts = 4 * (n + 1) + 4 * nnz + 16 * n * f
+    out["fusedmm_F64"] = _entry(ms, flops, byts, peaks, gather_gbs=(8.0 * nnz * f) / (ms * 1e-3) / 1e9)
+    prob = torch.empty(nnz, device=device)
+    o2 = torch.empty(n * f, device=device)
+    s1 = ops.sddmm.prepare(qf, kf, c, indptr, indices)
+    s2 = ops.sparse_softmax.prepare(c, prob, indptr, indices)
+    s3 = ops.csrmm.prepare(prob, vf, o2, indptr, indices)
+
+    def three():
+        s1(); s2(); s3()
+
+    out["fusedmm_F64"]["ms_three_operators"] = _time(three, number=3, repeat=3, warmup=2)
+    out["fusedmm_F64"]["max_abs_diff_vs_three_operators"] = (of - o2).abs().max().item()
     return out
 
 

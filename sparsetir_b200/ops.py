@@ -177,6 +177,7 @@ csr_reduce = PackedFunc("sparsetir_csr_reduce")
 sparse_softmax = PackedFunc("sparsetir_sparse_softmax")
 csr2bsr = PackedFunc("sparsetir_csr2bsr")
 ellmm = PackedFunc("sparsetir_ellmm")
+fusedmm = PackedFunc("sparsetir_fusedmm")
 
 
 def hyb_args(x: torch.Tensor, y: torch.Tensor, buckets: Sequence[Sequence[torch.Tensor]],

@@ -563,6 +563,41 @@ def test_ellmm_matches_oracle(cuda_device, nb, mb, col, blk, feat):
     close(c, orc.ellmm(a, b, ix, nb, col, blk, feat), atol=ATOL * 8)
 
 
+# ------------------------------------------------------------------------------ fusedmm
+@pytest.mark.parametrize("feat", [16, 32, 64, 128, 256, 512, 24])
+def test_fusedmm_matches_oracle(cuda_device, feat):
+    c = dg.csr_lognormal(n=1500, mu=3.0, sigma=1.2, max_deg=1200, seed=feat)
+    deg = np.diff(c.indptr)
+    scale = 1.0 / np.sqrt(feat)
+    q = (dg.dense_operand(1, c.m, feat) * scale * 2).astype(np.float32)
+    k = dg.dense_operand(2, c.n, feat)
+    v = dg.dense_operand(3, c.n, feat)
+    o = torch.full((c.m * feat,), 7.0, device=cuda_device)
+    ops.fusedmm(dev(q.reshape(-1), cuda_device), dev(k.reshape(-1), cuda_device), dev(v.reshape(-1), cuda_device),
+                o, dev(c.indptr, cuda_device), dev(c.indices, cuda_device))
+    torch.cuda.synchronize()
+    want = orc.fusedmm(q, k, v, c.indptr, c.indices, c.m, feat)
+    close(o, want, rtol=2e-4, atol=2e-5)
+    assert deg.max() > 64
+
+
+def test_fusedmm_empty_rows_and_scalars(cuda_device):
+    deg = np.zeros(300, np.int64)
+    deg[[3, 4, 100, 299]] = [2, 70, 1, 33]
+    rng = np.random.default_rng(1)
+    ix = dg.sorted_distinct_columns(rng, deg, 300)
+    ip = np.concatenate([[0], np.cumsum(deg)]).astype(np.int32)
+    feat = 64
+    q, k, v = (dg.dense_operand(s, 300, feat) * 0.3 for s in (4, 5, 6))
+    o = torch.full((300 * feat,), 7.0, device=cuda_device)
+    ops.fusedmm(dev(q.reshape(-1), cuda_device), dev(k.reshape(-1), cuda_device), dev(v.reshape(-1), cuda_device),
+                o, dev(ip, cuda_device), dev(ix, cuda_device), 300, 300, len(ix), feat)
+    torch.cuda.synchronize()
+    want = orc.fusedmm(q, k, v, ip, ix, 300, feat)
+    close(o, want, rtol=2e-4, atol=2e-5)
+    assert np.all(want[0] == 0) and torch.all(o.view(300, feat)[0] == 0)
+
+
 # ------------------------------------------------------------------------------ streams
 def test_calls_run_on_the_current_torch_stream(cuda_device):
     c = dg.csr_poisson(m=2000, n=2000, mean_deg=10, seed=30)

@@ -247,3 +247,15 @@ def test_small_operators_against_numpy():
         for j in range(col):
             want[i * bk:(i + 1) * bk] += ea[i, j].astype(np.float64) @ eb[ei[i, j] * bk:(ei[i, j] + 1) * bk]
     np.testing.assert_allclose(orc.ellmm(ea, eb, ei, nb, col, bk, feat), want, rtol=RTOL, atol=ATOL)
+
+
+def test_fusedmm_oracle_against_fp64_numpy():
+    c = dg.csr_lognormal(n=200, mu=2.0, sigma=1.0, max_deg=80, seed=11)
+    feat = 12
+    q, k, v = (dg.dense_operand(s, c.n, feat) * 0.5 for s in (1, 2, 3))
+    got = orc.fusedmm(q, k, v, c.indptr, c.indices, c.m, feat)
+    for i in (0, 5, 99, 199):
+        js = c.indices[c.indptr[i]:c.indptr[i + 1]]
+        s = k[js].astype(np.float64) @ q[i].astype(np.float64)
+        p = np.exp(s) / np.exp(s - s.max()).sum()
+        np.testing.assert_allclose(got[i], p @ v[js].astype(np.float64), rtol=1e-4, atol=1e-5)

@@ -414,7 +414,7 @@ def ours_arm(args, rank, world, local_rank):
     roofline = {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                 "frac": achieved / peaks["hbm_gbs"],
                 # dram__bytes_read.sum + dram__bytes_write.sum of this launch from the committed ncu
-                # capture of the same workload (profiles/hyb_spmm_lean_kernel_F512.md), one GPU
+                # capture of the same workload (the F = 512 summary in the profiles folder), one GPU
                 "traffic": 703.8e6 if (world == 1 and FEATS[-1] == 512) else None,
                 "peak_source": peaks["source"],
                 "kernel": "hyb_spmm_lean_kernel<32> (+ hyb_rearm_kernel), F=512 call",

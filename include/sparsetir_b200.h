@@ -225,6 +225,17 @@ SPARSETIR_API int sparsetir_tcspmm(SPARSETIR_PACKED_ARGS);
  * of every group, :40-45), plus feat_size.  Accumulates into the caller's zero-filled y. */
 SPARSETIR_API int sparsetir_rgms_ell3d(SPARSETIR_PACKED_ARGS);
 
+/* The same over half-precision operands with rectangular weights:
+ *   Y[rows_b[g,ii], fo] += A_b[g,ii,j] * sum_fi X[cols_b[g,ii,j], fi] * W[mid_b[g], fi, fo]
+ * args: (w f16[R*feat_in*feat_out], x f16[n*feat_in], y f16 or f32 [m*feat_out],
+ *        {a f16[G_b*rows_b*cols_b], rows i32[G_b*rows_b], cols i32[G_b*rows_b*cols_b]} x K,
+ *        {mid i32[G_b]} x K, feat_in, feat_out) — the argument list of the function built by
+ * rgcn_tensorcore (examples/rgms/rgcn/bench_rgcn_tensorcore.py:842-852; computation :564-609),
+ * which the sparse convolution driver calls with one relation per kernel offset and buckets = [1]
+ * (examples/rgms/sparse_conv/sparse_conv.py:93-125), plus the two feature sizes.  Products are
+ * accumulated in fp32; accumulates into the caller's zero-filled y. */
+SPARSETIR_API int sparsetir_rgms_ell3d_f16(SPARSETIR_PACKED_ARGS);
+
 /* ---- operators, plain-pointer form (device pointers; stream is a cudaStream_t) -------- */
 SPARSETIR_API int sparsetir_csrmm_raw(const float* a, const float* b, float* c,
                                       const int32_t* indptr, const int32_t* indices, int m, int n,
@@ -292,6 +303,22 @@ SPARSETIR_API int sparsetir_rgms_ell3d_raw(const float* w, const float* x, float
                                            const SparsetirEll3dBucket* buckets, int num_buckets,
                                            int m, int n, int num_rels, int feat, int device_id,
                                            void* stream);
+
+/* Half-precision operands, rectangular weights w[num_rels][feat_in][feat_out]; y is fp16 when
+ * y_is_f16 is non-zero, fp32 otherwise.  `a` points to fp16 values. */
+typedef struct {
+  const void* a;
+  const int32_t* rows;
+  const int32_t* cols;
+  const int32_t* mid;
+  int32_t num_groups;
+  int32_t rows_per_group;
+  int32_t cols_per_row;
+} SparsetirEll3dBucketH;
+SPARSETIR_API int sparsetir_rgms_ell3d_f16_raw(const void* w, const void* x, void* y, int y_is_f16,
+                                               const SparsetirEll3dBucketH* buckets, int num_buckets,
+                                               int m, int n, int num_rels, int feat_in, int feat_out,
+                                               int device_id, void* stream);
 
 /* RGMS that never allocates device memory.  No counterpart in the reference: it exists for
  * hosts that may not call the CUDA allocator when they need the operator (loops that forbid

@@ -217,6 +217,31 @@ def rgms_ell3d(w, x, y, buckets, feat) -> np.ndarray:
     return y
 
 
+def rgms_ell3d_f16(w, x, y, buckets, feat_in: int, feat_out: int) -> np.ndarray:
+    """RGMS over ELL3D buckets with fp16 operands and rectangular weights ``w[r, fi, fo]``:
+    ``y[rows[g,ii], fo] += a[g,ii,j] * sum_fi x[cols[g,ii,j], fi] * w[mid[g], fi, fo]`` — the two
+    iterations of rgcn_hetero_forward in examples/rgms/rgcn/bench_rgcn_tensorcore.py:593-607 with
+    every product and sum in fp32 (numpy; parity unpinned: the reference holds no fixture for it
+    and cannot run here).  ``y`` is fp32, accumulated into and returned."""
+    w = np.asarray(w, dtype=np.float16).astype(np.float32).reshape(-1, feat_in, feat_out)
+    x = np.asarray(x, dtype=np.float16).astype(np.float32).reshape(-1, feat_in)
+    assert y.dtype == np.float32 and y.flags.c_contiguous
+    y2 = y.reshape(-1, feat_out)
+    for a, rows, cols, mid in buckets:
+        mid = _i32(mid)
+        ng = int(mid.shape[0])
+        if ng == 0:
+            continue
+        rows = _i32(rows).reshape(ng, -1)
+        cols = _i32(cols).reshape(ng, rows.shape[1], -1)
+        a = np.asarray(a, dtype=np.float16).astype(np.float32).reshape(cols.shape)
+        for r in np.unique(mid):
+            sel = mid == r
+            z = (a[sel][..., None] * x[cols[sel]]).sum(axis=2, dtype=np.float32)  # groups x rows x feat_in
+            np.add.at(y2, rows[sel].reshape(-1), z.reshape(-1, feat_in) @ w[r])
+    return y
+
+
 def tcspmm_f16(a, b, indptr, indices, mb, t, g, feat) -> np.ndarray:
     """Condensed SpMM: fp16 ``a`` [groups, t, g] and ``b`` [rows, feat], fp32 sums [mb * t, feat]."""
     a = np.ascontiguousarray(a, dtype=np.float16)

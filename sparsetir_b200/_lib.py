@@ -71,6 +71,7 @@ PACKED_SYMBOLS = (
     "sparsetir_bsrmm",
     "sparsetir_rgms",
     "sparsetir_rgms_ell3d",
+    "sparsetir_rgms_ell3d_f16",
     "sparsetir_tcspmm",
     "sparsetir_csr_reduce",
     "sparsetir_sparse_softmax",
@@ -104,6 +105,7 @@ PLAIN_SYMBOLS = {
     "sparsetir_fusedmm_raw": (_i, [_vp] * 6 + [_i, _i, _i, _i, _i, _vp]),
     "sparsetir_tcspmm_raw": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_ell3d_raw": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
+    "sparsetir_rgms_ell3d_f16_raw": (_i, [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_noalloc": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),
     "sparsetir_column_part_hyb": (_vp, [_i, _i, _i32p, _i32p, _i, _i32p, _i, _i]),
     "sparsetir_hyb_num_rows": (_i64, [_vp, _i, _i]),

@@ -38,6 +38,7 @@ namespace sptir {
 __device__ unsigned int g_tc_timeouts = 0;  // bounded waits that ran out, since module load
 int rgms_tc_timeouts(unsigned int* count);  // the same counter of rgms_tc.cu
 int tcspmm_timeouts(unsigned int* count);   // ... and of tcspmm.cu
+int rgms_f16_timeouts(unsigned int* count);  // ... and of rgms_f16.cu
 
 namespace {
 
@@ -381,6 +382,8 @@ extern "C" int sparsetir_tc_timeouts(int device_id, unsigned int* count) {
   if (rgms_tc_timeouts(&rgms) != 0) return -1;
   unsigned int tcs = 0;
   if (tcspmm_timeouts(&tcs) != 0) return -1;
-  *count = bsr + rgms + tcs;
+  unsigned int rh = 0;
+  if (rgms_f16_timeouts(&rh) != 0) return -1;
+  *count = bsr + rgms + tcs + rh;
   return 0;
 }

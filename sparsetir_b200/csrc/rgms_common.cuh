@@ -107,5 +107,57 @@ __device__ __forceinline__ void gather_tile_rows(const float* __restrict__ a,
   for (int t = max(r_lo, nrows); t < r_lo + RPS; ++t) write_row(t, make_float4(0.f, 0.f, 0.f, 0.f));
 }
 
+// ---- warp-level tile lookup and walk for the kernels whose tiles are 128 rows
+constexpr int kTileRows128 = 128;
+
+// Which relation and row range tile `tile_id` covers; called by the 32 lanes of one warp.
+__device__ inline bool locate_tile_warp(const int32_t* __restrict__ indptr_i, int num_rels,
+                                        int tile_id, int lane, int* rel, int* row0, int* row1) {
+  int base = 0;
+  for (int r0 = 0; r0 < num_rels; r0 += 32) {
+    const int r = r0 + lane;
+    int s = 0, e = 0, nt = 0;
+    if (r < num_rels) {
+      s = __ldg(indptr_i + r);
+      e = __ldg(indptr_i + r + 1);
+      nt = (e - s + kTileRows128 - 1) / kTileRows128;
+    }
+    int incl = nt;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const int excl = base + incl - nt;
+    const bool mine = tile_id >= excl && tile_id < excl + nt;
+    const unsigned hit = __ballot_sync(0xffffffffu, mine);
+    if (hit != 0) {
+      const int src = __ffs(hit) - 1;
+      *rel = __shfl_sync(0xffffffffu, r, src);
+      *row0 = __shfl_sync(0xffffffffu, s + (tile_id - excl) * kTileRows128, src);
+      *row1 = __shfl_sync(0xffffffffu, min(e, s + (tile_id - excl + 1) * kTileRows128), src);
+      return true;
+    }
+    base += __shfl_sync(0xffffffffu, incl, 31);
+  }
+  return false;
+}
+
+struct TileWalk {
+  int rel, row0, row1, rel_end;  // rel_end: first row past the relation (cached indptr_i[rel + 1])
+  // steps to the tile after this one; false when there is none.  Inside a relation this costs no
+  // memory access; the row pointer is read again only when the relation changes.
+  __device__ __forceinline__ bool next(const int32_t* __restrict__ indptr_i, int num_rels) {
+    const int nrow0 = row1;
+    while (nrow0 >= rel_end) {
+      if (++rel >= num_rels) return false;
+      rel_end = __ldg(indptr_i + rel + 1);
+    }
+    row0 = nrow0;
+    row1 = min(rel_end, nrow0 + kTileRows128);
+    return true;
+  }
+};
+
 }  // namespace sptir
 #endif  // SPARSETIR_B200_RGMS_COMMON_CUH_

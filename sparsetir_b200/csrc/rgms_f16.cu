@@ -1,0 +1,466 @@
+// RGMS over ELL3D buckets with half-precision operands and rectangular weights:
+//   for every bucket b, group g (relation r = mid_b[g]), row slot ii, column slot j
+//     Y[rows_b[g,ii], fo] += A_b[g,ii,j] * sum_fi X[cols_b[g,ii,j], fi] * W[r, fi, fo]
+// X is n x feat_in, W is num_rels x feat_in x feat_out, both fp16; Y is m x feat_out, fp16 or fp32;
+// products are accumulated in fp32.  Replaces the kernel the reference builds from
+// rgcn_hetero_forward with its ELL3D decomposition and tensor-core intrinsics
+// (examples/rgms/rgcn/bench_rgcn_tensorcore.py:564-609 the computation, :651-858 schedule, buffers
+// and argument list W, X, Y, {mask, rows, cols} per bucket, {mid} per bucket), which is also what
+// the sparse convolution driver calls with one relation per kernel offset and buckets = [1]
+// (examples/rgms/sparse_conv/sparse_conv.py:93-125).
+//
+// Two launches whatever the number of buckets:
+//   (1) Z[q, :] = sum_j A[q,j] X[cols[q,j], :] for every ELL row q of every bucket (fp32 sums,
+//       stored as fp16), the buckets' rows one after the other in one Z array; the same launch
+//       copies the row ids next to each other and turns the ascending `mid` arrays into the Z-row
+//       range of every (bucket, relation) pair;
+//   (2) Y[rows[q], :] += Z[q, :] W_r over those ranges: a persistent tcgen05 kernel, one tile =
+//       128 Z rows of one range.  A producer warp streams, per 64-wide slice of feat_in, the Z
+//       box (128 x 64, K-major, 128-byte swizzle) and the matching 64 x feat_out slice of W_r
+//       (N-major boxes of 64 x 64) through a 4-stage ring with TMA; one thread issues 4 MMAs
+//       (M = 128, N = feat_out, K = 16) per slice into one of two TMEM accumulators; two groups
+//       of four warps take the even / odd tiles out of TMEM and add them to Y.
+// Shapes the tensor-core launch does not take (feat_in or feat_out not a multiple of 64, feat_out
+// above 256, unaligned operands) go through a CUDA-core transform with the same Z.
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cstdlib>
+#include <cstring>
+
+#include "common.h"
+#include "rgms_common.cuh"
+#include "tc05.cuh"
+#include "tmap.h"
+
+namespace sptir {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxBuckets = SPARSETIR_HYB_MAX_BUCKETS;
+
+__device__ unsigned int g_rgms_f16_timeouts = 0;
+
+struct BucketTable {
+  const __half* a[kMaxBuckets];
+  const int32_t* cols[kMaxBuckets];
+  const int32_t* rows[kMaxBuckets];
+  const int32_t* mid[kMaxBuckets];
+  int32_t num_groups[kMaxBuckets];
+  int32_t rows_per_group[kMaxBuckets];
+  int32_t width[kMaxBuckets];
+  int32_t z_base[kMaxBuckets + 1];  // first Z row of every bucket; [nb] = total rows
+  int32_t nb;
+};
+
+__device__ __forceinline__ int bucket_of(const BucketTable& tb, int q) {
+  int b = 0;
+  while (b + 1 < tb.nb && q >= tb.z_base[b + 1]) ++b;
+  return b;
+}
+
+// ---- launch (1).  A thread owns VEC consecutive features of one Z row; consecutive threads own
+// consecutive pieces of the same row.  The last block computes the (bucket, relation) ranges:
+// ranges[b * R + r] = first Z row of relation r inside bucket b, ranges[nb * R] = total rows.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+gather_rows_f16_kernel(const __grid_constant__ BucketTable tb, const __half* __restrict__ x,
+                       __half* __restrict__ z, int32_t* __restrict__ all_rows,
+                       int32_t* __restrict__ ranges, int num_rels, int feat_in) {
+  if (blockIdx.x == gridDim.x - 1) {
+    for (int e = threadIdx.x; e <= tb.nb * num_rels; e += kThreads) {
+      if (e == tb.nb * num_rels) {
+        ranges[e] = tb.z_base[tb.nb];
+        continue;
+      }
+      const int b = e / num_rels, r = e % num_rels;
+      int lo = 0, hi = tb.num_groups[b];  // first group of the bucket with mid >= r
+      while (lo < hi) {
+        const int m = lo + (hi - lo) / 2;
+        if (__ldg(tb.mid[b] + m) < r) lo = m + 1; else hi = m;
+      }
+      ranges[e] = tb.z_base[b] + lo * tb.rows_per_group[b];
+    }
+    return;
+  }
+  const int chunks = feat_in / VEC;
+  const long long work = static_cast<long long>(tb.z_base[tb.nb]) * chunks;
+  const long long step = static_cast<long long>(gridDim.x - 1) * kThreads;
+  for (long long idx = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; idx < work; idx += step) {
+    const int q = static_cast<int>(idx / chunks), ch = static_cast<int>(idx % chunks);
+    const int b = bucket_of(tb, q);
+    const int e = q - tb.z_base[b], width = tb.width[b];
+    const __half* ap = tb.a[b] + static_cast<size_t>(e) * width;
+    const int32_t* cp = tb.cols[b] + static_cast<size_t>(e) * width;
+    float acc[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+    for (int j = 0; j < width; ++j) {
+      const float av = __half2float(__ldg(ap + j));
+      const __half* xr = x + static_cast<size_t>(__ldg(cp + j)) * feat_in + ch * VEC;
+      if (VEC == 8) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(xr));
+        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const float2 f = __half22float2(h[v]);
+          acc[2 * v] = fmaf(av, f.x, acc[2 * v]);
+          acc[2 * v + 1] = fmaf(av, f.y, acc[2 * v + 1]);
+        }
+      } else {
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) acc[v] = fmaf(av, __half2float(__ldg(xr + v)), acc[v]);
+      }
+    }
+    __half* zr = z + static_cast<size_t>(q) * feat_in + ch * VEC;
+    if (VEC == 8) {
+      uint4 out;
+      __half2* h = reinterpret_cast<__half2*>(&out);
+#pragma unroll
+      for (int v = 0; v < 4; ++v) h[v] = __floats2half2_rn(acc[2 * v], acc[2 * v + 1]);
+      *reinterpret_cast<uint4*>(zr) = out;
+    } else {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) zr[v] = __float2half_rn(acc[v]);
+    }
+    if (ch == 0) all_rows[q] = __ldg(tb.rows[b] + e);
+  }
+}
+
+// ---- additions to Y
+__device__ __forceinline__ void add_out(float* y, float v) { atomicAdd(y, v); }
+__device__ __forceinline__ void add_out(__half* y, float v) { atomicAdd(y, __float2half_rn(v)); }
+// 32 consecutive outputs of one row (16-byte aligned destination)
+__device__ __forceinline__ void add_out32(float* y, const uint32_t (&r)[32]) {
+#pragma unroll
+  for (int q = 0; q < 8; ++q)
+    atomicAdd(reinterpret_cast<float4*>(y) + q,
+              make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
+}
+__device__ __forceinline__ void add_out32(__half* y, const uint32_t (&r)[32]) {
+#pragma unroll
+  for (int q = 0; q < 16; ++q)
+    atomicAdd(reinterpret_cast<__half2*>(y) + q,
+              __floats2half2_rn(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1])));
+}
+
+// ---- CUDA-core form of launch (2): a block owns 32 consecutive Z rows (staged in shared memory
+// as fp32); a thread computes outputs (row, fo), consecutive threads consecutive fo.
+constexpr int kSimtRows = 32;
+template <typename OutT>
+__global__ void __launch_bounds__(kThreads)
+transform_scatter_f16_kernel(const __grid_constant__ BucketTable tb, const __half* __restrict__ z,
+                             const __half* __restrict__ w, OutT* __restrict__ y,
+                             const int32_t* __restrict__ all_rows, int feat_in, int feat_out) {
+  extern __shared__ float s_z[];  // kSimtRows x feat_in
+  __shared__ int s_rel[kSimtRows];
+  const int total = tb.z_base[tb.nb];
+  const int q0 = blockIdx.x * kSimtRows;
+  const int nq = min(kSimtRows, total - q0);
+  for (int i = threadIdx.x; i < nq * feat_in; i += kThreads)
+    s_z[i] = __half2float(__ldg(z + static_cast<size_t>(q0) * feat_in + i));
+  if (threadIdx.x < nq) {
+    const int q = q0 + threadIdx.x;
+    const int b = bucket_of(tb, q);
+    s_rel[threadIdx.x] = __ldg(tb.mid[b] + (q - tb.z_base[b]) / tb.rows_per_group[b]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < nq * feat_out; i += kThreads) {
+    const int t = i / feat_out, fo = i % feat_out;
+    const __half* wr = w + static_cast<size_t>(s_rel[t]) * feat_in * feat_out + fo;
+    const float* zr = s_z + t * feat_in;
+    float acc = 0.f;
+    for (int fi = 0; fi < feat_in; ++fi)
+      acc = fmaf(zr[fi], __half2float(__ldg(wr + static_cast<size_t>(fi) * feat_out)), acc);
+    add_out(y + static_cast<size_t>(__ldg(all_rows + q0 + t)) * feat_out + fo, acc);
+  }
+}
+
+// ---- tensor-core form of launch (2)
+constexpr int kTM = kTileRows128;
+constexpr int kKC = 64;                       // slice of feat_in per stage (one 128-byte swizzled row)
+constexpr int kZBoxB = kTM * kKC * 2;         // 16 KB
+constexpr int kWBoxB = kKC * 64 * 2;          // 8 KB: 64 K rows x 64 outputs
+constexpr int kMaxOut = 256;
+constexpr int kStageB = kZBoxB + (kMaxOut / 64) * kWBoxB;  // 48 KB
+constexpr int kStagesH = 4;
+constexpr int kSmemH = kStagesH * kStageB + 1024;          // + slack to align to 1024 bytes
+constexpr int kTcThreads = 384;               // warp 0 loads, warp 1 MMAs, warps 4-7 / 8-11 epilogue
+
+__device__ __forceinline__ void mbar_arrive_local(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc05::smem_u32(bar)) : "memory");
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kTcThreads, 1)
+rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_w,
+                   OutT* __restrict__ y, const int32_t* __restrict__ ranges,
+                   const int32_t* __restrict__ all_rows, int num_ranges, int num_rels, int total_rows,
+                   int tiles_per_cta, int feat_in, int feat_out, int tmem_cols) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kStagesH];   // the stage's boxes have landed
+  __shared__ __align__(8) uint64_t bar_empty[kStagesH];  // the tensor core has read the stage
+  __shared__ __align__(8) uint64_t bar_acc_full[2];      // accumulator holds a finished tile
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];     // epilogue has read it (128 arrivals)
+  __shared__ uint32_t s_tmem;
+  __shared__ int s_tile[4];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  unsigned char* base = smem_raw + ((1024u - (tc05::smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int nkc = feat_in / kKC, nwb = feat_out / 64;
+
+  if (warp == 0) {
+    int rel, row0, row1;
+    const bool found = locate_tile_warp(ranges, num_ranges, blockIdx.x * tiles_per_cta, lane, &rel, &row0, &row1);
+    if (lane == 0) {
+      s_tile[0] = found ? 1 : 0; s_tile[1] = rel; s_tile[2] = row0; s_tile[3] = row1;
+      for (int s = 0; s < kStagesH; ++s) {
+        tc05::mbar_init(&bar_full[s], 1);
+        tc05::mbar_init(&bar_empty[s], 1);
+      }
+      for (int b = 0; b < 2; ++b) {
+        tc05::mbar_init(&bar_acc_full[b], 1);
+        tc05::mbar_init(&bar_acc_empty[b], 128);
+      }
+      tc05::fence_mbar_init();
+      tc05::prefetch_tensormap(&tm_z);
+      tc05::prefetch_tensormap(&tm_w);
+    }
+    __syncwarp();
+    tc05::tmem_alloc(&s_tmem, tmem_cols);
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  if (s_tile[0] == 0) {  // no tile for this block (uniform)
+    if (warp == 0) tc05::tmem_dealloc(s_tmem, tmem_cols);
+    return;
+  }
+  const uint32_t tmem = s_tmem;
+  TileWalk tw{s_tile[1], s_tile[2], s_tile[3], __ldg(ranges + s_tile[1] + 1)};
+  bool ok = true;
+  int armed = 0;  // producer: stages whose loads have been issued
+
+  if (warp == 0) {
+    // ---- producer
+    if (lane == 0) {
+      int it = 0;
+      const uint32_t stage_bytes = kZBoxB + nwb * kWBoxB;
+      for (int k = 0; k < tiles_per_cta && ok; ++k) {
+        const int wrow = (tw.rel % num_rels) * feat_in;
+        for (int c = 0; c < nkc; ++c, ++it) {
+          const int s = it % kStagesH, use = it / kStagesH;
+          if (use > 0 && !tc05::mbar_wait(&bar_empty[s], (use - 1) & 1)) { ok = false; break; }
+          unsigned char* st = base + s * kStageB;
+          tc05::mbar_arrive_expect_tx(&bar_full[s], stage_bytes);
+          tc05::tma_load_2d(st, &tm_z, c * kKC, tw.row0, &bar_full[s]);
+          for (int j = 0; j < nwb; ++j)
+            tc05::tma_load_2d(st + kZBoxB + j * kWBoxB, &tm_w, j * 64, wrow + c * kKC, &bar_full[s]);
+          armed = it + 1;
+        }
+        if (k + 1 == tiles_per_cta || !tw.next(ranges, num_ranges)) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = tc05::instr_desc(tc05::kFmtF16, kTM, feat_out, /*a_mn=*/0, /*b_mn=*/1);
+      // Z box, K-major: rows of 128 bytes, groups of 8 rows 1024 bytes apart; 16 columns = 32 bytes per step
+      const uint64_t dz0 = tc05::smem_desc_swizzled(tc05::smem_u32(base), 0, 1024, tc05::kSwizzle128B);
+      // W boxes, N-major: 64 outputs per 128-byte row, boxes (atoms of 64 outputs) kWBoxB apart,
+      // groups of 8 K rows 1024 bytes apart; 16 K rows = 2048 bytes per step
+      const uint64_t dw0 = tc05::smem_desc_swizzled(tc05::smem_u32(base) + kZBoxB, kWBoxB, 1024, tc05::kSwizzle128B);
+      int it = 0;
+      for (int k = 0; k < tiles_per_cta && ok; ++k) {
+        const int buf = k & 1, buse = k >> 1;
+        if (buse > 0 && !tc05::mbar_wait(&bar_acc_empty[buf], (buse - 1) & 1)) { ok = false; break; }
+        const uint32_t acc = tmem + buf * feat_out;
+        for (int c = 0; c < nkc; ++c, ++it) {
+          const int s = it % kStagesH, use = it / kStagesH;
+          if (!tc05::mbar_wait(&bar_full[s], use & 1)) { ok = false; break; }
+          tc05::fence_after_sync();
+          const uint64_t dz = tc05::desc_advance(dz0, s * kStageB);
+          const uint64_t dw = tc05::desc_advance(dw0, s * kStageB);
+#pragma unroll
+          for (int ks = 0; ks < kKC / 16; ++ks)
+            tc05::mma_f16(acc, tc05::desc_advance(dz, ks * 32), tc05::desc_advance(dw, ks * 2048), idesc,
+                          (c > 0 || ks > 0) ? 1u : 0u);
+          tc05::mma_commit(&bar_empty[s]);
+        }
+        if (!ok) break;
+        tc05::mma_commit(&bar_acc_full[buf]);
+        if (k + 1 == tiles_per_cta || !tw.next(ranges, num_ranges)) break;
+      }
+    }
+  } else if (warp >= 4) {
+    // ---- epilogue: group 0 (warps 4-7) takes the even tiles and accumulator 0, group 1 (warps
+    // 8-11) the odd ones; thread = tile row = TMEM lane
+    const int grp = warp >= 8 ? 1 : 0;
+    const int t = (warp & 3) * 32 + lane;
+    bool have = true;
+    if (grp == 1) have = tiles_per_cta > 1 && tw.next(ranges, num_ranges);
+    for (int k = grp; have && k < tiles_per_cta; k += 2) {
+      const int buse = k >> 1;
+      const bool live = tw.row0 + t < tw.row1;
+      const int dst = __ldg(all_rows + min(tw.row0 + t, total_rows - 1));
+      if (!tc05::mbar_wait(&bar_acc_full[grp], buse & 1)) { ok = false; break; }
+      tc05::fence_after_sync();
+      const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + grp * feat_out;
+      OutT* yrow = y + static_cast<size_t>(dst) * feat_out;
+      for (int c0 = 0; c0 < feat_out; c0 += 32) {
+        uint32_t r[32];
+        tc05::tmem_ld32(taddr + c0, r);
+        if (c0 + 32 >= feat_out) {  // the accumulator is in registers: the next tile may overwrite it
+          tc05::fence_before_sync();
+          mbar_arrive_local(&bar_acc_empty[grp]);
+        }
+        if (live) add_out32(yrow + c0, r);
+      }
+      bool has_next = (k + 2 < tiles_per_cta) && tw.next(ranges, num_ranges);
+      has_next = has_next && tw.next(ranges, num_ranges);
+      if (!has_next) break;
+    }
+  }
+
+  const bool all_ok = !__syncthreads_or(!ok);
+  if (!all_ok && tid == 0) {
+    atomicAdd(&g_rgms_f16_timeouts, 1u);
+    // gave up: let the loads already issued land (bounded) before the block's memory is released
+    for (int it = max(0, armed - kStagesH); it < armed; ++it)
+      tc05::mbar_wait(&bar_full[it % kStagesH], (it / kStagesH) & 1);
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc05::tmem_dealloc(tmem, tmem_cols);
+}
+
+}  // namespace
+
+int rgms_f16_timeouts(unsigned int* count) {
+  SPTIR_CUDA_OK(cudaMemcpyFromSymbol(count, g_rgms_f16_timeouts, sizeof(unsigned int)));
+  return 0;
+}
+
+namespace {
+
+// 0 when launched, 1 when this path cannot take the call (caller falls back), -1 on error
+template <typename OutT>
+int launch_tc(const __half* z, const __half* w, OutT* y, const int32_t* ranges, const int32_t* all_rows,
+              int num_ranges, int num_rels, int total_rows, int feat_in, int feat_out, cudaStream_t st) {
+  CUtensorMap tm_z, tm_w;
+  if (make_tmap_2d(&tm_z, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, z, static_cast<uint64_t>(feat_in),
+                   static_cast<uint64_t>(total_rows), static_cast<uint64_t>(feat_in) * 2, kKC, kTM,
+                   CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return 1;
+  if (make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w, static_cast<uint64_t>(feat_out),
+                   static_cast<uint64_t>(num_rels) * feat_in, static_cast<uint64_t>(feat_out) * 2, 64, kKC,
+                   CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return 1;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  SPTIR_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(rgms_f16_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemH));
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(rgms_f16_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemH));
+    configured_device = dev;
+  }
+  int tmem_cols = 32;
+  while (tmem_cols < 2 * feat_out) tmem_cols *= 2;
+  const long long tiles = static_cast<long long>(total_rows) / kTM + num_ranges;  // upper bound
+  const long long grid = tiles < kNumSMs ? tiles : kNumSMs;
+  const int tiles_per_cta = static_cast<int>((tiles + grid - 1) / grid);
+  rgms_f16_tc_kernel<OutT><<<static_cast<unsigned>(grid), kTcThreads, kSmemH, st>>>(
+      tm_z, tm_w, y, ranges, all_rows, num_ranges, num_rels, total_rows, tiles_per_cta, feat_in, feat_out,
+      tmem_cols);
+  SPTIR_LAUNCH_OK("rgms_f16_tc_kernel");
+  return 0;
+}
+
+template <typename OutT>
+int run(const BucketTable& tb, const __half* w, const __half* x, OutT* y, int num_rels, int feat_in,
+        int feat_out, int device_id, cudaStream_t st) {
+  const int total = tb.z_base[tb.nb];
+  const long long num_ranges = static_cast<long long>(tb.nb) * num_rels;
+  if (num_ranges >= INT32_MAX) return fail("sparsetir_rgms_ell3d_f16: too many (bucket, relation) pairs");
+  const size_t zb = (static_cast<size_t>(total) * feat_in * sizeof(__half) + 255) & ~static_cast<size_t>(255);
+  const size_t rb = (static_cast<size_t>(num_ranges + 1) * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
+  char* ws = static_cast<char*>(workspace(device_id, st, zb + rb + static_cast<size_t>(total) * sizeof(int32_t)));
+  if (!ws) return -1;
+  __half* z = reinterpret_cast<__half*>(ws);
+  int32_t* ranges = reinterpret_cast<int32_t*>(ws + zb);
+  int32_t* all_rows = reinterpret_cast<int32_t*>(ws + zb + rb);
+
+  const bool vec = feat_in % 8 == 0 && aligned16(x);
+  const long long work = static_cast<long long>(total) * (vec ? feat_in / 8 : feat_in);
+  const int blocks = static_cast<int>(std::min<long long>((work + kThreads - 1) / kThreads, 16ll * kNumSMs));
+  if (vec)
+    gather_rows_f16_kernel<8><<<blocks + 1, kThreads, 0, st>>>(tb, x, z, all_rows, ranges, num_rels, feat_in);
+  else
+    gather_rows_f16_kernel<1><<<blocks + 1, kThreads, 0, st>>>(tb, x, z, all_rows, ranges, num_rels, feat_in);
+  SPTIR_LAUNCH_OK("gather_rows_f16_kernel");
+
+  // SPARSETIR_RGMS_F16_PATH=simt keeps the transform on the CUDA cores (comparison switch)
+  static const bool use_tc = [] {
+    const char* e = std::getenv("SPARSETIR_RGMS_F16_PATH");
+    return !(e && std::strcmp(e, "simt") == 0);
+  }();
+  if (use_tc && feat_in % kKC == 0 && feat_out % 64 == 0 && feat_out <= kMaxOut && aligned16(w) && aligned16(y)) {
+    const int rc = launch_tc<OutT>(z, w, y, ranges, all_rows, static_cast<int>(num_ranges), num_rels, total,
+                                   feat_in, feat_out, st);
+    if (rc <= 0) return rc;
+  }
+  const size_t smem = static_cast<size_t>(kSimtRows) * feat_in * sizeof(float);
+  if (smem > 48 * 1024) return fail("sparsetir_rgms_ell3d_f16: feat_in %d is too large", feat_in);
+  transform_scatter_f16_kernel<OutT><<<ceil_div(total, kSimtRows), kThreads, smem, st>>>(
+      tb, z, w, y, all_rows, feat_in, feat_out);
+  SPTIR_LAUNCH_OK("transform_scatter_f16_kernel");
+  return 0;
+}
+
+}  // namespace
+}  // namespace sptir
+
+extern "C" int sparsetir_rgms_ell3d_f16_raw(const void* w, const void* x, void* y, int y_is_f16,
+                                            const SparsetirEll3dBucketH* buckets, int num_buckets, int m,
+                                            int n, int num_rels, int feat_in, int feat_out, int device_id,
+                                            void* stream) {
+  using namespace sptir;
+  if (num_buckets < 0 || m < 0 || n < 0 || num_rels < 0 || feat_in < 0 || feat_out < 0)
+    return fail("sparsetir_rgms_ell3d_f16: negative size");
+  if (num_buckets > kMaxBuckets)
+    return fail("sparsetir_rgms_ell3d_f16: %d buckets, at most %d are supported", num_buckets, kMaxBuckets);
+  if (num_buckets > 0 && !buckets) return fail("sparsetir_rgms_ell3d_f16: null bucket list");
+  BucketTable tb{};
+  long long total = 0;
+  for (int b = 0; b < num_buckets; ++b) {
+    const SparsetirEll3dBucketH& bk = buckets[b];
+    if (bk.num_groups < 0 || bk.rows_per_group < 0 || bk.cols_per_row < 0)
+      return fail("sparsetir_rgms_ell3d_f16: bucket %d has a negative size", b);
+    const long long nrows = static_cast<long long>(bk.num_groups) * bk.rows_per_group;
+    if (nrows == 0) continue;
+    if (bk.cols_per_row == 0) return fail("sparsetir_rgms_ell3d_f16: bucket %d has rows but no columns", b);
+    if (!bk.a || !bk.rows || !bk.cols || !bk.mid)
+      return fail("sparsetir_rgms_ell3d_f16: bucket %d has a null array", b);
+    if (nrows * bk.cols_per_row > INT32_MAX || total + nrows > INT32_MAX)
+      return fail("sparsetir_rgms_ell3d_f16: the buckets are too large for 32-bit indices");
+    const int k = tb.nb++;
+    tb.a[k] = static_cast<const __half*>(bk.a);
+    tb.cols[k] = bk.cols; tb.rows[k] = bk.rows; tb.mid[k] = bk.mid;
+    tb.num_groups[k] = bk.num_groups; tb.rows_per_group[k] = bk.rows_per_group;
+    tb.width[k] = bk.cols_per_row;
+    tb.z_base[k] = static_cast<int32_t>(total);
+    total += nrows;
+  }
+  tb.z_base[tb.nb] = static_cast<int32_t>(total);
+  if (total == 0 || feat_out == 0 || m == 0) return 0;
+  if (!w || !x || !y) return fail("sparsetir_rgms_ell3d_f16: null pointer argument");
+  if (num_rels == 0) return fail("sparsetir_rgms_ell3d_f16: rows but no relations");
+  if (feat_in == 0) return 0;  // empty sums: Y is left as it is
+  if (use_device(device_id) != 0) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (y_is_f16)
+    return run<__half>(tb, static_cast<const __half*>(w), static_cast<const __half*>(x), static_cast<__half*>(y),
+                       num_rels, feat_in, feat_out, device_id, st);
+  return run<float>(tb, static_cast<const __half*>(w), static_cast<const __half*>(x), static_cast<float*>(y),
+                    num_rels, feat_in, feat_out, device_id, st);
+}

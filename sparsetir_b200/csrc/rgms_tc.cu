@@ -261,55 +261,6 @@ __device__ __forceinline__ int swz_off(int row, int kc, int box_bytes) {
   return (kc >> 3) * box_bytes + (row >> 3) * 1024 + (row & 7) * 128 + (((kc & 7) ^ (row & 7)) << 4);
 }
 
-// Which relation and row range tile `tile_id` covers; called by the 32 lanes of one warp.
-__device__ inline bool locate_tile_warp(const int32_t* __restrict__ indptr_i, int num_rels,
-                                        int tile_id, int lane, int* rel, int* row0, int* row1) {
-  int base = 0;
-  for (int r0 = 0; r0 < num_rels; r0 += 32) {
-    const int r = r0 + lane;
-    int s = 0, e = 0, nt = 0;
-    if (r < num_rels) {
-      s = __ldg(indptr_i + r);
-      e = __ldg(indptr_i + r + 1);
-      nt = (e - s + kTM - 1) / kTM;
-    }
-    int incl = nt;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
-    }
-    const int excl = base + incl - nt;
-    const bool mine = tile_id >= excl && tile_id < excl + nt;
-    const unsigned hit = __ballot_sync(0xffffffffu, mine);
-    if (hit != 0) {
-      const int src = __ffs(hit) - 1;
-      *rel = __shfl_sync(0xffffffffu, r, src);
-      *row0 = __shfl_sync(0xffffffffu, s + (tile_id - excl) * kTM, src);
-      *row1 = __shfl_sync(0xffffffffu, min(e, s + (tile_id - excl + 1) * kTM), src);
-      return true;
-    }
-    base += __shfl_sync(0xffffffffu, incl, 31);
-  }
-  return false;
-}
-
-struct TileWalk {
-  int rel, row0, row1, rel_end;  // rel_end: first row past the relation (cached indptr_i[rel + 1])
-  // steps to the tile after this one; false when there is none.  Inside a relation this costs no
-  // memory access; the row pointer is read again only when the relation changes.
-  __device__ __forceinline__ bool next(const int32_t* __restrict__ indptr_i, int num_rels) {
-    const int nrow0 = row1;
-    while (nrow0 >= rel_end) {
-      if (++rel >= num_rels) return false;
-      rel_end = __ldg(indptr_i + rel + 1);
-    }
-    row0 = nrow0;
-    row1 = min(rel_end, nrow0 + kTM);
-    return true;
-  }
-};
-
 __global__ void __launch_bounds__(kPThreads, 1)
 rgms_tma_kernel(const __grid_constant__ CUtensorMap tm_z, const float* __restrict__ w,
                 float* __restrict__ y, const int32_t* __restrict__ indptr_i,

@@ -172,6 +172,7 @@ sddmm_edge_to_row = PackedFunc("sparsetir_sddmm_edge_to_row")
 bsrmm = PackedFunc("sparsetir_bsrmm")
 rgms = PackedFunc("sparsetir_rgms")
 rgms_ell3d = PackedFunc("sparsetir_rgms_ell3d")
+rgms_ell3d_f16 = PackedFunc("sparsetir_rgms_ell3d_f16")
 tcspmm = PackedFunc("sparsetir_tcspmm")
 csr_reduce = PackedFunc("sparsetir_csr_reduce")
 sparse_softmax = PackedFunc("sparsetir_sparse_softmax")
@@ -204,4 +205,18 @@ def rgms_ell3d_args(w: torch.Tensor, x: torch.Tensor, y: torch.Tensor,
         args += [a.reshape(-1), rows.reshape(-1), cols.reshape(-1)]
     args += [mid.reshape(-1) for _, _, _, mid in buckets]
     args.append(int(feat_size))
+    return args
+
+
+def rgms_ell3d_f16_args(w: torch.Tensor, x: torch.Tensor, y: torch.Tensor,
+                        buckets: Sequence[Sequence[torch.Tensor]], feat_in: int, feat_out: int) -> list:
+    """Argument list of ``rgms_ell3d_f16`` in the reference's layout
+    (examples/rgms/rgcn/bench_rgcn_tensorcore.py:842-852): ``[w, x, y]``, then ``a, rows, cols`` per
+    bucket, then ``mid`` per bucket, then the two feature sizes.  ``buckets`` holds
+    ``(a, rows, cols, mid)`` with ``a`` in float16."""
+    args = [w.reshape(-1), x.reshape(-1), y.reshape(-1)]
+    for a, rows, cols, _ in buckets:
+        args += [a.reshape(-1), rows.reshape(-1), cols.reshape(-1)]
+    args += [mid.reshape(-1) for _, _, _, mid in buckets]
+    args += [int(feat_in), int(feat_out)]
     return args

@@ -465,6 +465,78 @@ def test_rgms_ell3d_wide_and_empty_buckets(cuda_device):
         close(run_rgms_ell3d(cf, x, w, buckets, cuda_device, feat), want, atol=ATOL * 8)
 
 
+# ------------------------------------------------------------------------------ rgms, fp16, rectangular
+def run_rgms_ell3d_f16(cf, x16, w16, buckets, device, feat_in, feat_out, out_dtype):
+    y = torch.zeros(cf.m * feat_out, device=device, dtype=out_dtype)
+    devb = [(dev(a.astype(np.float16), device), dev(r, device), dev(c, device), dev(m, device))
+            for a, r, c, m in buckets]
+    ops.rgms_ell3d_f16(*ops.rgms_ell3d_f16_args(dev(w16, device), dev(x16, device), y, devb, feat_in, feat_out))
+    torch.cuda.synchronize()
+    return y.float()
+
+
+def rect_weights(seed, num_rels, feat_in, feat_out):
+    return (np.random.default_rng(seed).standard_normal((num_rels, feat_in, feat_out)) /
+            np.sqrt(feat_in)).astype(np.float16)
+
+
+@pytest.mark.parametrize("feat_in,feat_out", [(64, 64), (64, 128), (128, 64), (128, 256), (256, 128), (192, 192),
+                                              (32, 64), (64, 32), (48, 80), (16, 8), (320, 64)])
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
+def test_rgms_ell3d_f16_matches_oracle(cuda_device, feat_in, feat_out, out_dtype):
+    cf = dg.csf_relational(n=2500, num_rels=7, num_edges=30000, seed=feat_in + feat_out)
+    x16 = dg.dense_operand(1, cf.n, feat_in).astype(np.float16)
+    w16 = rect_weights(2, cf.num_rels, feat_in, feat_out)
+    buckets = ell3d_buckets(cf, [1, 2, 4, 8])
+    want = orc.rgms_ell3d_f16(w16, x16, np.zeros((cf.m, feat_out), np.float32), buckets, feat_in, feat_out)
+    got = run_rgms_ell3d_f16(cf, x16, w16, buckets, cuda_device, feat_in, feat_out, out_dtype)
+    # fp16 operands, fp32 sums (the aggregated rows pass through fp16 once): rtol 1e-2; a float16
+    # result also rounds every addition into Y
+    close(got, want, rtol=1e-2, atol=2e-2 if out_dtype == torch.float32 else 6e-2)
+
+
+def test_rgms_ell3d_f16_sparse_convolution_shape(cuda_device):
+    # what the sparse convolution driver builds: one relation per kernel offset (27), every
+    # (input, output) pair its own ELL row (buckets = [1]), unit values, 64 -> 128 channels
+    cf = dg.csf_relational(n=4000, num_rels=27, num_edges=60000, zipf_a=0.3, seed=5)
+    feat_in, feat_out = 64, 128
+    x16 = dg.dense_operand(3, cf.n, feat_in).astype(np.float16)
+    w16 = rect_weights(4, cf.num_rels, feat_in, feat_out)
+    buckets = ell3d_buckets(cf, [1], group=1)
+    assert all(c.shape[-1] == 1 for _, _, c, _ in buckets)
+    want = orc.rgms_ell3d_f16(w16, x16, np.zeros((cf.m, feat_out), np.float32), buckets, feat_in, feat_out)
+    got = run_rgms_ell3d_f16(cf, x16, w16, buckets, cuda_device, feat_in, feat_out, torch.float32)
+    close(got, want, rtol=1e-2, atol=2e-2)
+    # the same as a dense computation: Y[o] = sum over (r, i -> o) of X[i] W_r
+    y = np.zeros((cf.m, feat_out), np.float64)
+    xs, ws = x16.astype(np.float64), w16.astype(np.float64)
+    for r in range(cf.num_rels):
+        for t in range(cf.indptr_i[r], cf.indptr_i[r + 1]):
+            src = cf.indices_j[cf.indptr_j[t]:cf.indptr_j[t + 1]]
+            y[cf.indices_i[t]] += xs[src].sum(0) @ ws[r]
+    close(got, y.astype(np.float32), rtol=1e-2, atol=2e-2)
+
+
+def test_rgms_ell3d_f16_empty_buckets_and_accumulation(cuda_device):
+    cf = dg.csf_relational(n=300, num_rels=3, num_edges=4000, seed=8)
+    feat_in, feat_out = 64, 64
+    x16 = dg.dense_operand(5, cf.n, feat_in).astype(np.float16)
+    w16 = rect_weights(6, cf.num_rels, feat_in, feat_out)
+    buckets = ell3d_buckets(cf, [1, 16, 64], group=64)  # bucket 16 or 64 may stay empty
+    want = orc.rgms_ell3d_f16(w16, x16, np.ones((cf.m, feat_out), np.float32), buckets, feat_in, feat_out)
+    y = torch.ones(cf.m * feat_out, device=cuda_device)
+    devb = [(dev(a.astype(np.float16), cuda_device), dev(r, cuda_device), dev(c, cuda_device), dev(m, cuda_device))
+            for a, r, c, m in buckets]
+    ops.rgms_ell3d_f16(*ops.rgms_ell3d_f16_args(dev(w16, cuda_device), dev(x16, cuda_device), y, devb, feat_in, feat_out))
+    torch.cuda.synchronize()
+    close(y, want, rtol=1e-2, atol=3e-2)
+    # no buckets at all: nothing happens
+    y0 = torch.full((cf.m * feat_out,), 2.0, device=cuda_device)
+    ops.rgms_ell3d_f16(dev(w16.reshape(-1), cuda_device), dev(x16.reshape(-1), cuda_device), y0, feat_in, feat_out)
+    torch.cuda.synchronize()
+    assert torch.all(y0 == 2.0)
+
+
 # ------------------------------------------------------------------------------ tcspmm
 def run_tcspmm(g: dg.CSR, x16, t, gs, device, out_dtype, weights=None):
     """Condense the graph on the host (ConDense), then the condensed SpMM on the GPU."""

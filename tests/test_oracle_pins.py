@@ -259,3 +259,35 @@ def test_fusedmm_oracle_against_fp64_numpy():
         s = k[js].astype(np.float64) @ q[i].astype(np.float64)
         p = np.exp(s) / np.exp(s - s.max()).sum()
         np.testing.assert_allclose(got[i], p @ v[js].astype(np.float64), rtol=1e-4, atol=1e-5)
+
+
+def test_rgms_ell3d_f16_oracle_against_plain_loops_and_the_fp32_form():
+    """The numpy restatement against the triple loop of the script, and — for square weights —
+    against the fp32 ELL3D oracle fed with the transposed weights (that script indexes W[r, fo, fi])."""
+    from sparsetir_b200 import datagen as dg
+    from sparsetir_b200 import format as fmt
+    cf = dg.csf_relational(n=60, num_rels=4, num_edges=500, seed=1)
+    fi, fo = 8, 12
+    rng = np.random.default_rng(0)
+    x = rng.uniform(-1, 1, (cf.n, fi)).astype(np.float16)
+    w = rng.standard_normal((cf.num_rels, fi, fo)).astype(np.float16)
+    ip, rows, cols, mask = fmt.csf_to_ell3d(cf.indptr_i, cf.indices_i, cf.indptr_j, cf.indices_j, [4, 2], [2, 8])
+    buckets = []
+    for b in range(2):
+        mid = np.repeat(np.arange(cf.num_rels, dtype=np.int32), np.diff(ip[b]))
+        buckets.append((mask[b].astype(np.float16), rows[b], cols[b], mid))
+    got = orc.rgms_ell3d_f16(w, x, np.zeros((cf.m, fo), np.float32), buckets, fi, fo)
+    want = np.zeros((cf.m, fo), np.float64)
+    for a, r, c, mid in buckets:
+        for g in range(len(mid)):
+            for ii in range(r.shape[1]):
+                for j in range(c.shape[2]):
+                    want[r[g, ii]] += float(a[g, ii, j]) * (x[c[g, ii, j]].astype(np.float64) @ w[mid[g]].astype(np.float64))
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-5)
+    # square: same numbers as the fp32 ELL3D oracle with W transposed
+    ws = rng.standard_normal((cf.num_rels, fi, fi)).astype(np.float16)
+    got2 = orc.rgms_ell3d_f16(ws, x, np.zeros((cf.m, fi), np.float32), buckets, fi, fi)
+    b32 = [(a.astype(np.float32), r, c, m) for a, r, c, m in buckets]
+    ref = orc.rgms_ell3d(np.ascontiguousarray(ws.astype(np.float32).transpose(0, 2, 1)), x.astype(np.float32),
+                         np.zeros((cf.m, fi), np.float32), b32, fi)
+    np.testing.assert_allclose(got2, ref, rtol=1e-4, atol=1e-5)

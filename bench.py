@@ -493,7 +493,7 @@ def main():
                     help="comma-separated feature sizes (default: the workload's 32,64,128,256,512)")
     ap.add_argument("--kernels-only", action="store_true",
                     help="time the device-resident steps and stop (for profiler captures)")
-    ap.add_argument("--only-op", default=None, choices=["csrmm", "bsrmm", "rgms", "rgms_ell3d", "tcspmm", "sddmm"],
+    ap.add_argument("--only-op", default=None, choices=["csrmm", "bsrmm", "rgms", "rgms_ell3d", "rgms_f16", "tcspmm", "sddmm"],
                     help="measure one of the other operators alone and stop (for profiler captures)")
     args = ap.parse_args()
     if args.feats:

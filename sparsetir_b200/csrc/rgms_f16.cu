@@ -17,7 +17,7 @@
 //   (2) Y[rows[q], :] += Z[q, :] W_r over those ranges: a persistent tcgen05 kernel, one tile =
 //       128 Z rows of one range.  A producer warp streams, per 64-wide slice of feat_in, the Z
 //       box (128 x 64, K-major, 128-byte swizzle) and the matching 64 x feat_out slice of W_r
-//       (N-major boxes of 64 x 64) through a 4-stage ring with TMA; one thread issues 4 MMAs
+//       (N-major boxes of 64 x 64) through a 3-stage ring with TMA; one thread issues 4 MMAs
 //       (M = 128, N = feat_out, K = 16) per slice into one of two TMEM accumulators; two groups
 //       of four warps take the even / odd tiles out of TMEM and add them to Y.
 // Shapes the tensor-core launch does not take (feat_in or feat_out not a multiple of 64, feat_out
@@ -130,19 +130,13 @@ gather_rows_f16_kernel(const __grid_constant__ BucketTable tb, const __half* __r
 // ---- additions to Y
 __device__ __forceinline__ void add_out(float* y, float v) { atomicAdd(y, v); }
 __device__ __forceinline__ void add_out(__half* y, float v) { atomicAdd(y, __float2half_rn(v)); }
-// 32 consecutive outputs of one row (16-byte aligned destination)
-__device__ __forceinline__ void add_out32(float* y, const uint32_t (&r)[32]) {
-#pragma unroll
-  for (int q = 0; q < 8; ++q)
-    atomicAdd(reinterpret_cast<float4*>(y) + q,
-              make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
-                          __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3])));
-}
-__device__ __forceinline__ void add_out32(__half* y, const uint32_t (&r)[32]) {
-#pragma unroll
-  for (int q = 0; q < 16; ++q)
-    atomicAdd(reinterpret_cast<__half2*>(y) + q,
-              __floats2half2_rn(__uint_as_float(r[2 * q]), __uint_as_float(r[2 * q + 1])));
+// 4 consecutive outputs of one row (destination aligned to 4 elements)
+__device__ __forceinline__ void add_out4(float* y, const float4& v) { atomicAdd(reinterpret_cast<float4*>(y), v); }
+__device__ __forceinline__ void add_out4(__half* y, const float4& v) {  // one 8-byte vector reduction
+  const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+  asm volatile("red.global.add.noftz.v2.f16x2 [%0], {%1,%2};" ::"l"(y),
+               "r"(*reinterpret_cast<const uint32_t*>(&lo)), "r"(*reinterpret_cast<const uint32_t*>(&hi))
+               : "memory");
 }
 
 // ---- CUDA-core form of launch (2): a block owns 32 consecutive Z rows (staged in shared memory
@@ -184,8 +178,10 @@ constexpr int kZBoxB = kTM * kKC * 2;         // 16 KB
 constexpr int kWBoxB = kKC * 64 * 2;          // 8 KB: 64 K rows x 64 outputs
 constexpr int kMaxOut = 256;
 constexpr int kStageB = kZBoxB + (kMaxOut / 64) * kWBoxB;  // 48 KB
-constexpr int kStagesH = 4;
-constexpr int kSmemH = kStagesH * kStageB + 1024;          // + slack to align to 1024 bytes
+constexpr int kStagesH = 3;
+constexpr int kOutStride = 128 + 16;          // padded row of 32 floats: 16-byte stores of 32 rows spread over all banks
+constexpr int kOffOut = kStagesH * kStageB;
+constexpr int kSmemH = kOffOut + 2 * kTM * kOutStride + 1024;  // two epilogue groups; + slack to align to 1024 bytes
 constexpr int kTcThreads = 384;               // warp 0 loads, warp 1 MMAs, warps 4-7 / 8-11 epilogue
 
 __device__ __forceinline__ void mbar_arrive_local(uint64_t* bar) {
@@ -294,19 +290,23 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
     }
   } else if (warp >= 4) {
     // ---- epilogue: group 0 (warps 4-7) takes the even tiles and accumulator 0, group 1 (warps
-    // 8-11) the odd ones; thread = tile row = TMEM lane
+    // 8-11) the odd ones; thread = tile row = TMEM lane.  32 columns at a time go through a
+    // padded shared-memory buffer so that 8 lanes add one row's 128 bytes (whole lines per
+    // request instead of 32 rows x 16 bytes).
     const int grp = warp >= 8 ? 1 : 0;
     const int t = (warp & 3) * 32 + lane;
+    unsigned char* gbuf = base + kOffOut + grp * (kTM * kOutStride);
+    unsigned char* my_row = gbuf + t * kOutStride;
+    const unsigned char* wbase = gbuf + (warp & 3) * 32 * kOutStride;
     bool have = true;
     if (grp == 1) have = tiles_per_cta > 1 && tw.next(ranges, num_ranges);
     for (int k = grp; have && k < tiles_per_cta; k += 2) {
       const int buse = k >> 1;
-      const bool live = tw.row0 + t < tw.row1;
-      const int dst = __ldg(all_rows + min(tw.row0 + t, total_rows - 1));
+      const int nrows = tw.row1 - tw.row0;
+      const int dst_row = __ldg(all_rows + min(tw.row0 + t, total_rows - 1));
       if (!tc05::mbar_wait(&bar_acc_full[grp], buse & 1)) { ok = false; break; }
       tc05::fence_after_sync();
       const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + grp * feat_out;
-      OutT* yrow = y + static_cast<size_t>(dst) * feat_out;
       for (int c0 = 0; c0 < feat_out; c0 += 32) {
         uint32_t r[32];
         tc05::tmem_ld32(taddr + c0, r);
@@ -314,7 +314,20 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
           tc05::fence_before_sync();
           mbar_arrive_local(&bar_acc_empty[grp]);
         }
-        if (live) add_out32(yrow + c0, r);
+        __syncwarp();  // the warp's reads of the previous 32 columns are over
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(my_row + q * 16) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+        __syncwarp();
+#pragma unroll 4
+        for (int i = 0; i < 8; ++i) {
+          const int lr = 4 * i + (lane >> 3);  // row inside the warp's 32
+          const int drow = __shfl_sync(0xffffffffu, dst_row, lr);
+          if ((warp & 3) * 32 + lr < nrows) {
+            const float4 v = *reinterpret_cast<const float4*>(wbase + lr * kOutStride + (lane & 7) * 16);
+            add_out4(y + static_cast<size_t>(drow) * feat_out + c0 + (lane & 7) * 4, v);
+          }
+        }
       }
       bool has_next = (k + 2 < tiles_per_cta) && tw.next(ranges, num_ranges);
       has_next = has_next && tw.next(ranges, num_ranges);

@@ -102,26 +102,7 @@ template <int W> struct LaneVec;
 template <> struct LaneVec<4> {
   using type = float4;
   static __device__ __forceinline__ float4 zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
-  static __device__ __forceinline__ float4 ldg(const void* p) {
-#if defined(SPTIR_GATHER_HINT) && SPTIR_GATHER_HINT == 1
-    float4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
-#elif defined(SPTIR_GATHER_HINT) && SPTIR_GATHER_HINT == 2
-    float4 v;
-    asm volatile("ld.global.nc.L1::evict_last.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
-#elif defined(SPTIR_GATHER_HINT) && SPTIR_GATHER_HINT == 3
-    float4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::256B.v4.f32 {%0,%1,%2,%3}, [%4];"
-                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
-    return v;
-#else
-    return __ldg(reinterpret_cast<const float4*>(p));
-#endif
-  }
+  static __device__ __forceinline__ float4 ldg(const void* p) { return __ldg(reinterpret_cast<const float4*>(p)); }
   static __device__ __forceinline__ void stcs(void* p, const float4& v) { __stcs(reinterpret_cast<float4*>(p), v); }
   static __device__ __forceinline__ void fma(float4& acc, float w, const float4& x) { Vec<4>::fma(acc, w, x); }
   static __device__ __forceinline__ void atomic_add(void* p, const float4& v) { atomicAdd(reinterpret_cast<float4*>(p), v); }

@@ -379,6 +379,52 @@ def bench_rgms_ell3d(device, peaks, flush) -> dict:
             "warm": _entry(warm, flops_ref, byts, peaks), "cold_l2": _entry(cold, flops_ref, byts, peaks)}
 
 
+def bench_rgms_f16(device, peaks, flush) -> dict:
+    """fp16 RGMS with rectangular weights on ELL3D buckets: (a) config 5's graph in buckets of
+    1..32 columns, 64 -> 64; (b) the shape the sparse convolution driver builds — 27 relations
+    (kernel offsets), every (input, output) pair its own ELL row (buckets = [1]), unit values —
+    at 64 -> 128 and 128 -> 128 channels on 100,000 points with 1.6 M pairs."""
+    from . import format as fmt
+    dv = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)  # noqa: E731
+    out = {"workload": "rgms_ell3d_f16", "cases": {}}
+
+    def one(name, cf, cols_bkt, group, feat_in, feat_out, number, out_dtype=torch.float32):
+        rows_bkt = [max(1, group // c) for c in cols_bkt]
+        ip, rows, cols, mask = fmt.csf_to_ell3d(cf.indptr_i, cf.indices_i, cf.indptr_j, cf.indices_j,
+                                                rows_bkt, cols_bkt)
+        buckets = []
+        for b in range(len(cols_bkt)):
+            mid = np.repeat(np.arange(cf.num_rels, dtype=np.int32), np.diff(ip[b]))
+            buckets.append((dv(mask[b].astype(np.float16)), dv(rows[b]), dv(cols[b]), dv(mid)))
+        x = dv(dg.dense_operand(1, cf.n, feat_in).astype(np.float16).reshape(-1))
+        w = dv((np.random.default_rng(2).standard_normal((cf.num_rels, feat_in, feat_out)) /
+                np.sqrt(feat_in)).astype(np.float16).reshape(-1))
+        y = torch.zeros(cf.m * feat_out, device=device, dtype=out_dtype)
+        call = ops.rgms_ell3d_f16.prepare(*ops.rgms_ell3d_f16_args(w, x, y, buckets, feat_in, feat_out))
+
+        def fn():
+            y.zero_()
+            call()
+
+        ell_rows = int(sum(r.size for r in rows))
+        slots = int(sum(m.size for m in mask))
+        flops = 2.0 * ell_rows * feat_in * feat_out + 2.0 * slots * feat_in   # executed: transform + gather
+        byts = (6 * slots + 8 * ell_rows + 2 * cf.num_rels * feat_in * feat_out + 2 * cf.n * feat_in
+                + y.element_size() * cf.m * feat_out)
+        warm = _time(fn, number=number)
+        cold = _time_cold(fn, flush)
+        out["cases"][name] = {"ell_rows": ell_rows, "slots": slots, "feat_in": feat_in, "feat_out": feat_out,
+                              "warm": _entry(warm, flops, byts, peaks), "cold_l2": _entry(cold, flops, byts, peaks)}
+
+    cf = dg.csf_relational(seed=0)
+    one("config5_graph_buckets_1_32_64x64", cf, [1, 2, 4, 8, 16, 32], 32, 64, 64, 20)
+    conv = dg.csf_relational(n=100_000, num_rels=27, num_edges=1_600_000, zipf_a=0.3, seed=1)
+    one("sparse_conv_27_offsets_64x128", conv, [1], 1, 64, 128, 20)
+    one("sparse_conv_27_offsets_128x128", conv, [1], 1, 128, 128, 20)
+    one("sparse_conv_27_offsets_128x128_f16_out", conv, [1], 1, 128, 128, 20, torch.float16)
+    return out
+
+
 def bench_tcspmm(device, peaks, flush, feats=(128, 512), t: int = 16, g: int = 16) -> dict:
     """The power-law graph of the headline workload, condensed (ConDense, t x g = 16 x 16) and
     multiplied in fp16 with fp32 accumulation and fp16 output, as the reference example does."""
@@ -411,6 +457,7 @@ def run_all(device, peaks, log=print) -> Dict[str, dict]:
                      ("bsrmm", lambda: bench_bsrmm(device, peaks, flush)),
                      ("rgms", lambda: bench_rgms(device, peaks, flush)),
                      ("rgms_ell3d", lambda: bench_rgms_ell3d(device, peaks, flush)),
+                     ("rgms_f16", lambda: bench_rgms_f16(device, peaks, flush)),
                      ("tcspmm", lambda: bench_tcspmm(device, peaks, flush)),
                      ("sddmm", lambda: bench_sddmm(device, peaks))):
         try:

@@ -164,3 +164,23 @@ def test_fuzz_row_wise_operators_and_attention(cuda_device, seed):
     ops.fusedmm(T.dev(q.reshape(-1), d), T.dev(k.reshape(-1), d), T.dev(v.reshape(-1), d), o, ip, T.dev(c.indices, d))
     torch.cuda.synchronize()
     T.close(o, orc.fusedmm(q, k, v, c.indptr, c.indices, n, feat), rtol=2e-4, atol=2e-5)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_fuzz_rgms_f16_rectangular(cuda_device, seed):
+    rng = np.random.default_rng(8000 + seed)
+    n = int(rng.integers(50, 3000))
+    rels = int(rng.integers(1, 40))
+    edges = int(rng.integers(2 * rels, 30000))
+    feat_in = int(rng.choice([64, 128, 192, 256, 32, 16, 40, 8]))
+    feat_out = int(rng.choice([64, 128, 192, 256, 32, 96, 24, 320]))
+    cf = dg.csf_relational(n=n, num_rels=rels, num_edges=edges, zipf_a=float(rng.uniform(0.3, 2.5)), seed=seed)
+    x16 = dg.dense_operand(seed, cf.n, feat_in).astype(np.float16)
+    w16 = T.rect_weights(seed + 1, cf.num_rels, feat_in, feat_out)
+    cols_bkt = sorted(set(int(b) for b in rng.choice([1, 2, 4, 8, 16, 32], size=int(rng.integers(1, 5)))))
+    buckets = T.ell3d_buckets(cf, cols_bkt, group=int(rng.choice([1, 8, 32])))
+    want = orc.rgms_ell3d_f16(w16, x16, np.zeros((cf.m, feat_out), np.float32), buckets, feat_in, feat_out)
+    out_dtype = torch.float32 if seed & 1 else torch.float16
+    got = T.run_rgms_ell3d_f16(cf, x16, w16, buckets, cuda_device, feat_in, feat_out, out_dtype)
+    scale = max(1.0, float(np.abs(want).max()))
+    T.close(got, want, rtol=1e-2, atol=(2e-2 if out_dtype == torch.float32 else 6e-2) * scale)

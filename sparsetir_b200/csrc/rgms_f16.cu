@@ -83,18 +83,28 @@ gather_rows_f16_kernel(const __grid_constant__ BucketTable tb, const __half* __r
     }
     return;
   }
+  // a block walks tiles of kThreads / chunks consecutive rows; 32-bit index arithmetic only
   const int chunks = feat_in / VEC;
-  const long long work = static_cast<long long>(tb.z_base[tb.nb]) * chunks;
-  const long long step = static_cast<long long>(gridDim.x - 1) * kThreads;
-  for (long long idx = static_cast<long long>(blockIdx.x) * kThreads + threadIdx.x; idx < work; idx += step) {
-    const int q = static_cast<int>(idx / chunks), ch = static_cast<int>(idx % chunks);
+  const int rows_per_tile = max(1, kThreads / chunks);
+  const int total = tb.z_base[tb.nb];
+  const int rl = static_cast<int>(threadIdx.x) / chunks, ch = static_cast<int>(threadIdx.x) % chunks;
+  if (rl >= rows_per_tile && chunks <= kThreads) return;
+  for (long long row0 = static_cast<long long>(blockIdx.x) * rows_per_tile; row0 < total;
+       row0 += static_cast<long long>(gridDim.x - 1) * rows_per_tile) {
+   for (int c0 = ch; c0 < chunks; c0 += kThreads) {  // more pieces than threads: rows of > 2048 features
+    const int ch = c0;
+    if (row0 + rl >= total) continue;
+    const int q = static_cast<int>(row0) + rl;
     const int b = bucket_of(tb, q);
     const int e = q - tb.z_base[b], width = tb.width[b];
     const __half* ap = tb.a[b] + static_cast<size_t>(e) * width;
     const int32_t* cp = tb.cols[b] + static_cast<size_t>(e) * width;
+    __half* zr = z + static_cast<size_t>(q) * feat_in + ch * VEC;
+    if (ch == 0) all_rows[q] = __ldg(tb.rows[b] + e);
     float acc[VEC];
 #pragma unroll
     for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+#pragma unroll 4
     for (int j = 0; j < width; ++j) {
       const float av = __half2float(__ldg(ap + j));
       const __half* xr = x + static_cast<size_t>(__ldg(cp + j)) * feat_in + ch * VEC;
@@ -112,7 +122,6 @@ gather_rows_f16_kernel(const __grid_constant__ BucketTable tb, const __half* __r
         for (int v = 0; v < VEC; ++v) acc[v] = fmaf(av, __half2float(__ldg(xr + v)), acc[v]);
       }
     }
-    __half* zr = z + static_cast<size_t>(q) * feat_in + ch * VEC;
     if (VEC == 8) {
       uint4 out;
       __half2* h = reinterpret_cast<__half2*>(&out);
@@ -123,7 +132,75 @@ gather_rows_f16_kernel(const __grid_constant__ BucketTable tb, const __half* __r
 #pragma unroll
       for (int v = 0; v < VEC; ++v) zr[v] = __float2half_rn(acc[v]);
     }
-    if (ch == 0) all_rows[q] = __ldg(tb.rows[b] + e);
+   }
+  }
+}
+
+// ---- launch (1) when every bucket has one column per row (the sparse-convolution shape): the Z
+// row is the X row times one value.  A thread owns one 16-byte piece of R rows that lie
+// kThreads / chunks rows apart and keeps the R chains (value, column id -> X row) in flight
+// together.  Same outputs as gather_rows_f16_kernel.
+constexpr int kCopyR = 4;
+__global__ void __launch_bounds__(kThreads)
+scale_rows_f16_kernel(const __grid_constant__ BucketTable tb, const __half* __restrict__ x,
+                      __half* __restrict__ z, int32_t* __restrict__ all_rows,
+                      int32_t* __restrict__ ranges, int num_rels, int feat_in) {
+  if (blockIdx.x == gridDim.x - 1) {
+    for (int e = threadIdx.x; e <= tb.nb * num_rels; e += kThreads) {
+      if (e == tb.nb * num_rels) {
+        ranges[e] = tb.z_base[tb.nb];
+        continue;
+      }
+      const int b = e / num_rels, r = e % num_rels;
+      int lo = 0, hi = tb.num_groups[b];
+      while (lo < hi) {
+        const int m = lo + (hi - lo) / 2;
+        if (__ldg(tb.mid[b] + m) < r) lo = m + 1; else hi = m;
+      }
+      ranges[e] = tb.z_base[b] + lo * tb.rows_per_group[b];
+    }
+    return;
+  }
+  const int chunks = feat_in / 8;                     // <= kThreads (checked by the caller)
+  const int rows_per_pass = kThreads / chunks;
+  const int total = tb.z_base[tb.nb];
+  const int rl = static_cast<int>(threadIdx.x) / chunks, ch = static_cast<int>(threadIdx.x) % chunks;
+  if (rl >= rows_per_pass) return;
+  for (long long row0 = static_cast<long long>(blockIdx.x) * rows_per_pass * kCopyR; row0 < total;
+       row0 += static_cast<long long>(gridDim.x - 1) * rows_per_pass * kCopyR) {
+    float av[kCopyR];
+    int col[kCopyR], q[kCopyR];
+#pragma unroll
+    for (int r = 0; r < kCopyR; ++r) {
+      const long long row = row0 + r * rows_per_pass + rl;
+      q[r] = row < total ? static_cast<int>(row) : -1;
+      av[r] = 0.f;
+      col[r] = 0;
+      if (q[r] >= 0) {
+        const int b = bucket_of(tb, q[r]);
+        const int e = q[r] - tb.z_base[b];
+        av[r] = __half2float(__ldg(tb.a[b] + e));
+        col[r] = __ldg(tb.cols[b] + e);
+        if (ch == 0) all_rows[q[r]] = __ldg(tb.rows[b] + e);
+      }
+    }
+    uint4 raw[kCopyR];
+#pragma unroll
+    for (int r = 0; r < kCopyR; ++r)
+      raw[r] = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(col[r]) * feat_in) + ch);
+#pragma unroll
+    for (int r = 0; r < kCopyR; ++r) {
+      if (q[r] < 0) continue;
+      if (av[r] != 1.f) {
+        __half2* h = reinterpret_cast<__half2*>(&raw[r]);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const float2 f = __half22float2(h[v]);
+          h[v] = __floats2half2_rn(av[r] * f.x, av[r] * f.y);
+        }
+      }
+      *(reinterpret_cast<uint4*>(z + static_cast<size_t>(q[r]) * feat_in) + ch) = raw[r];
+    }
   }
 }
 
@@ -132,11 +209,41 @@ __device__ __forceinline__ void add_out(float* y, float v) { atomicAdd(y, v); }
 __device__ __forceinline__ void add_out(__half* y, float v) { atomicAdd(y, __float2half_rn(v)); }
 // 4 consecutive outputs of one row (destination aligned to 4 elements)
 __device__ __forceinline__ void add_out4(float* y, const float4& v) { atomicAdd(reinterpret_cast<float4*>(y), v); }
-__device__ __forceinline__ void add_out4(__half* y, const float4& v) {  // one 8-byte vector reduction
-  const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
-  asm volatile("red.global.add.noftz.v2.f16x2 [%0], {%1,%2};" ::"l"(y),
-               "r"(*reinterpret_cast<const uint32_t*>(&lo)), "r"(*reinterpret_cast<const uint32_t*>(&hi))
+// 8 consecutive float16 outputs of one row (16-byte aligned destination): one vector reduction
+__device__ __forceinline__ void add_out8(__half* y, const float4& a, const float4& b) {
+  const __half2 h0 = __floats2half2_rn(a.x, a.y), h1 = __floats2half2_rn(a.z, a.w);
+  const __half2 h2 = __floats2half2_rn(b.x, b.y), h3 = __floats2half2_rn(b.z, b.w);
+  asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(y),
+               "r"(*reinterpret_cast<const uint32_t*>(&h0)), "r"(*reinterpret_cast<const uint32_t*>(&h1)),
+               "r"(*reinterpret_cast<const uint32_t*>(&h2)), "r"(*reinterpret_cast<const uint32_t*>(&h3))
                : "memory");
+}
+// the 32 staged columns of the warp's rows go to Y: 8 lanes x 16 bytes per row for a float32 Y,
+// 4 lanes x 16 bytes per row for a float16 Y
+__device__ __forceinline__ void scatter32(float* y, const unsigned char* wbase, int stride, int dst_row, int row_base,
+                                          int nrows, int feat_out, int c0, int lane) {
+#pragma unroll 4
+  for (int i = 0; i < 8; ++i) {
+    const int lr = 4 * i + (lane >> 3);  // row inside the warp's 32
+    const int drow = __shfl_sync(0xffffffffu, dst_row, lr);
+    if (row_base + lr < nrows) {
+      const float4 v = *reinterpret_cast<const float4*>(wbase + lr * stride + (lane & 7) * 16);
+      add_out4(y + static_cast<size_t>(drow) * feat_out + c0 + (lane & 7) * 4, v);
+    }
+  }
+}
+__device__ __forceinline__ void scatter32(__half* y, const unsigned char* wbase, int stride, int dst_row, int row_base,
+                                          int nrows, int feat_out, int c0, int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int lr = 8 * i + (lane >> 2);
+    const int drow = __shfl_sync(0xffffffffu, dst_row, lr);
+    if (row_base + lr < nrows) {
+      const float4 a = *reinterpret_cast<const float4*>(wbase + lr * stride + (lane & 3) * 32);
+      const float4 b = *reinterpret_cast<const float4*>(wbase + lr * stride + (lane & 3) * 32 + 16);
+      add_out8(y + static_cast<size_t>(drow) * feat_out + c0 + (lane & 3) * 8, a, b);
+    }
+  }
 }
 
 // ---- CUDA-core form of launch (2): a block owns 32 consecutive Z rows (staged in shared memory
@@ -319,15 +426,7 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
         for (int q = 0; q < 8; ++q)
           *reinterpret_cast<uint4*>(my_row + q * 16) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
         __syncwarp();
-#pragma unroll 4
-        for (int i = 0; i < 8; ++i) {
-          const int lr = 4 * i + (lane >> 3);  // row inside the warp's 32
-          const int drow = __shfl_sync(0xffffffffu, dst_row, lr);
-          if ((warp & 3) * 32 + lr < nrows) {
-            const float4 v = *reinterpret_cast<const float4*>(wbase + lr * kOutStride + (lane & 7) * 16);
-            add_out4(y + static_cast<size_t>(drow) * feat_out + c0 + (lane & 7) * 4, v);
-          }
-        }
+        scatter32(y, wbase, kOutStride, dst_row, (warp & 3) * 32, nrows, feat_out, c0, lane);
       }
       bool has_next = (k + 2 < tiles_per_cta) && tw.next(ranges, num_ranges);
       has_next = has_next && tw.next(ranges, num_ranges);
@@ -404,9 +503,15 @@ int run(const BucketTable& tb, const __half* w, const __half* x, OutT* y, int nu
   int32_t* all_rows = reinterpret_cast<int32_t*>(ws + zb + rb);
 
   const bool vec = feat_in % 8 == 0 && aligned16(x);
-  const long long work = static_cast<long long>(total) * (vec ? feat_in / 8 : feat_in);
-  const int blocks = static_cast<int>(std::min<long long>((work + kThreads - 1) / kThreads, 16ll * kNumSMs));
-  if (vec)
+  const int rows_per_tile = std::max(1, kThreads / (vec ? feat_in / 8 : feat_in));
+  const int blocks = static_cast<int>(std::min<long long>(ceil_div(total, rows_per_tile), 64ll * kNumSMs));
+  bool one_column = vec && feat_in / 8 <= kThreads;
+  for (int b = 0; b < tb.nb; ++b) one_column = one_column && tb.width[b] == 1;
+  if (one_column) {
+    const int rows_per_block = (kThreads / (feat_in / 8)) * kCopyR;
+    const int nblk = static_cast<int>(std::min<long long>(ceil_div(total, rows_per_block), 64ll * kNumSMs));
+    scale_rows_f16_kernel<<<nblk + 1, kThreads, 0, st>>>(tb, x, z, all_rows, ranges, num_rels, feat_in);
+  } else if (vec)
     gather_rows_f16_kernel<8><<<blocks + 1, kThreads, 0, st>>>(tb, x, z, all_rows, ranges, num_rels, feat_in);
   else
     gather_rows_f16_kernel<1><<<blocks + 1, kThreads, 0, st>>>(tb, x, z, all_rows, ranges, num_rels, feat_in);

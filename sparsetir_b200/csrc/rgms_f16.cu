@@ -9,7 +9,8 @@
 // the sparse convolution driver calls with one relation per kernel offset and buckets = [1]
 // (examples/rgms/sparse_conv/sparse_conv.py:93-125).
 //
-// Two launches whatever the number of buckets:
+// Two launches whatever the number of buckets (one when there is a single bucket with one column
+// per row, see rgms_f16_tc_kernel<OutT, true>):
 //   (1) Z[q, :] = sum_j A[q,j] X[cols[q,j], :] for every ELL row q of every bucket (fp32 sums,
 //       stored as fp16), the buckets' rows one after the other in one Z array; the same launch
 //       copies the row ids next to each other and turns the ascending `mid` arrays into the Z-row
@@ -290,17 +291,25 @@ constexpr int kOutStride = 128 + 16;          // padded row of 32 floats: 16-byt
 constexpr int kOffOut = kStagesH * kStageB;
 constexpr int kSmemH = kOffOut + 2 * kTM * kOutStride + 1024;  // two epilogue groups; + slack to align to 1024 bytes
 constexpr int kTcThreads = 384;               // warp 0 loads, warp 1 MMAs, warps 4-7 / 8-11 epilogue
+constexpr int kTcThreadsG = 512;              // ... and warps 12-15 gather X rows (one-launch form)
 
 __device__ __forceinline__ void mbar_arrive_local(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc05::smem_u32(bar)) : "memory");
 }
 
-template <typename OutT>
-__global__ void __launch_bounds__(kTcThreads, 1)
+// GATHER = true is the one-launch form for a single bucket with one column per row (the
+// sparse-convolution shape): there is no Z array; four more warps copy the tile's X rows
+// (row t of the tile = X[gcols[row0 + t]]) straight into the swizzled stage with 16-byte
+// asynchronous copies, 8 lanes per 128-byte row slice, and the row's value gvals[row0 + t]
+// multiplies the finished row in the epilogue.
+template <typename OutT, bool GATHER>
+__global__ void __launch_bounds__(GATHER ? kTcThreadsG : kTcThreads, 1)
 rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_constant__ CUtensorMap tm_w,
                    OutT* __restrict__ y, const int32_t* __restrict__ ranges,
                    const int32_t* __restrict__ all_rows, int num_ranges, int num_rels, int total_rows,
-                   int tiles_per_cta, int feat_in, int feat_out, int tmem_cols) {
+                   int tiles_per_cta, int feat_in, int feat_out, int tmem_cols,
+                   const __half* __restrict__ x, const int32_t* __restrict__ gcols,
+                   const __half* __restrict__ gvals) {
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStagesH];   // the stage's boxes have landed
   __shared__ __align__(8) uint64_t bar_empty[kStagesH];  // the tensor core has read the stage
@@ -318,7 +327,7 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
     if (lane == 0) {
       s_tile[0] = found ? 1 : 0; s_tile[1] = rel; s_tile[2] = row0; s_tile[3] = row1;
       for (int s = 0; s < kStagesH; ++s) {
-        tc05::mbar_init(&bar_full[s], 1);
+        tc05::mbar_init(&bar_full[s], GATHER ? 1 + 128 : 1);  // the W boxes (+ the 128 gathering threads)
         tc05::mbar_init(&bar_empty[s], 1);
       }
       for (int b = 0; b < 2; ++b) {
@@ -326,7 +335,7 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
         tc05::mbar_init(&bar_acc_empty[b], 128);
       }
       tc05::fence_mbar_init();
-      tc05::prefetch_tensormap(&tm_z);
+      if (!GATHER) tc05::prefetch_tensormap(&tm_z);
       tc05::prefetch_tensormap(&tm_w);
     }
     __syncwarp();
@@ -348,7 +357,7 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
     // ---- producer
     if (lane == 0) {
       int it = 0;
-      const uint32_t stage_bytes = kZBoxB + nwb * kWBoxB;
+      const uint32_t stage_bytes = (GATHER ? 0 : kZBoxB) + nwb * kWBoxB;
       for (int k = 0; k < tiles_per_cta && ok; ++k) {
         const int wrow = (tw.rel % num_rels) * feat_in;
         for (int c = 0; c < nkc; ++c, ++it) {
@@ -356,7 +365,7 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
           if (use > 0 && !tc05::mbar_wait(&bar_empty[s], (use - 1) & 1)) { ok = false; break; }
           unsigned char* st = base + s * kStageB;
           tc05::mbar_arrive_expect_tx(&bar_full[s], stage_bytes);
-          tc05::tma_load_2d(st, &tm_z, c * kKC, tw.row0, &bar_full[s]);
+          if (!GATHER) tc05::tma_load_2d(st, &tm_z, c * kKC, tw.row0, &bar_full[s]);
           for (int j = 0; j < nwb; ++j)
             tc05::tma_load_2d(st + kZBoxB + j * kWBoxB, &tm_w, j * 64, wrow + c * kKC, &bar_full[s]);
           armed = it + 1;
@@ -395,7 +404,43 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
         if (k + 1 == tiles_per_cta || !tw.next(ranges, num_ranges)) break;
       }
     }
-  } else if (warp >= 4) {
+  } else if (GATHER && warp >= 12) {
+    // ---- gather warps: warp gw copies rows gw*32 .. gw*32+31 of the tile.  A stage is announced
+    // one step late: after the next stage's copies have been issued, wait for all but those,
+    // make the data visible to the tensor core's proxy, arrive.
+    const int gw = warp - 12;
+    int it = 0, pending = -1;
+    for (int k = 0; k < tiles_per_cta && ok; ++k) {
+      const int mycol = __ldg(gcols + min(tw.row0 + gw * 32 + lane, total_rows - 1));
+      for (int c = 0; c < nkc; ++c, ++it) {
+        const int s = it % kStagesH, use = it / kStagesH;
+        if (use > 0 && !tc05::mbar_wait(&bar_empty[s], (use - 1) & 1)) { ok = false; break; }
+        const uint32_t st = tc05::smem_u32(base + s * kStageB);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int lr = 4 * i + (lane >> 3);  // row inside the warp's 32
+          const int col = __shfl_sync(0xffffffffu, mycol, lr);
+          const int row = gw * 32 + lr, chunk = lane & 7;
+          const __half* src = x + static_cast<size_t>(col) * feat_in + c * kKC + chunk * 8;
+          const uint32_t dst = st + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
+          asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (pending >= 0) {
+          asm volatile("cp.async.wait_group 1;" ::: "memory");
+          tc05::fence_async_smem();
+          mbar_arrive_local(&bar_full[pending]);
+        }
+        pending = s;
+      }
+      if (k + 1 == tiles_per_cta || !tw.next(ranges, num_ranges)) break;
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");  // also when giving up: nothing may land later
+    if (ok && pending >= 0) {
+      tc05::fence_async_smem();
+      mbar_arrive_local(&bar_full[pending]);
+    }
+  } else if (warp >= 4 && warp < 12) {
     // ---- epilogue: group 0 (warps 4-7) takes the even tiles and accumulator 0, group 1 (warps
     // 8-11) the odd ones; thread = tile row = TMEM lane.  32 columns at a time go through a
     // padded shared-memory buffer so that 8 lanes add one row's 128 bytes (whole lines per
@@ -411,6 +456,7 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
       const int buse = k >> 1;
       const int nrows = tw.row1 - tw.row0;
       const int dst_row = __ldg(all_rows + min(tw.row0 + t, total_rows - 1));
+      const float a_t = GATHER ? __half2float(__ldg(gvals + min(tw.row0 + t, total_rows - 1))) : 1.f;
       if (!tc05::mbar_wait(&bar_acc_full[grp], buse & 1)) { ok = false; break; }
       tc05::fence_after_sync();
       const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + grp * feat_out;
@@ -420,6 +466,10 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
         if (c0 + 32 >= feat_out) {  // the accumulator is in registers: the next tile may overwrite it
           tc05::fence_before_sync();
           mbar_arrive_local(&bar_acc_empty[grp]);
+        }
+        if (GATHER) {
+#pragma unroll
+          for (int q = 0; q < 32; ++q) r[q] = __float_as_uint(__uint_as_float(r[q]) * a_t);
         }
         __syncwarp();  // the warp's reads of the previous 32 columns are over
 #pragma unroll
@@ -455,25 +505,47 @@ int rgms_f16_timeouts(unsigned int* count) {
 
 namespace {
 
-// 0 when launched, 1 when this path cannot take the call (caller falls back), -1 on error
-template <typename OutT>
+// ranges[b * R + r] for every bucket (what the last block of the gather launches computes)
+__global__ void __launch_bounds__(kThreads)
+bucket_ranges_kernel(const __grid_constant__ BucketTable tb, int num_rels, int32_t* __restrict__ ranges) {
+  for (int e = threadIdx.x; e <= tb.nb * num_rels; e += kThreads) {
+    if (e == tb.nb * num_rels) {
+      ranges[e] = tb.z_base[tb.nb];
+      continue;
+    }
+    const int b = e / num_rels, r = e % num_rels;
+    int lo = 0, hi = tb.num_groups[b];
+    while (lo < hi) {
+      const int m = lo + (hi - lo) / 2;
+      if (__ldg(tb.mid[b] + m) < r) lo = m + 1; else hi = m;
+    }
+    ranges[e] = tb.z_base[b] + lo * tb.rows_per_group[b];
+  }
+}
+
+// 0 when launched, 1 when this path cannot take the call (caller falls back), -1 on error.
+// GATHER: z is unused, (x, gcols, gvals) describe the rows of the single one-column bucket.
+template <typename OutT, bool GATHER>
 int launch_tc(const __half* z, const __half* w, OutT* y, const int32_t* ranges, const int32_t* all_rows,
-              int num_ranges, int num_rels, int total_rows, int feat_in, int feat_out, cudaStream_t st) {
+              int num_ranges, int num_rels, int total_rows, int feat_in, int feat_out, cudaStream_t st,
+              const __half* x = nullptr, const int32_t* gcols = nullptr, const __half* gvals = nullptr) {
   CUtensorMap tm_z, tm_w;
-  if (make_tmap_2d(&tm_z, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, z, static_cast<uint64_t>(feat_in),
-                   static_cast<uint64_t>(total_rows), static_cast<uint64_t>(feat_in) * 2, kKC, kTM,
-                   CU_TENSOR_MAP_SWIZZLE_128B) != 0)
-    return 1;
   if (make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w, static_cast<uint64_t>(feat_out),
                    static_cast<uint64_t>(num_rels) * feat_in, static_cast<uint64_t>(feat_out) * 2, 64, kKC,
                    CU_TENSOR_MAP_SWIZZLE_128B) != 0)
     return 1;
+  if (GATHER) {
+    tm_z = tm_w;  // not used
+  } else if (make_tmap_2d(&tm_z, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, z, static_cast<uint64_t>(feat_in),
+                          static_cast<uint64_t>(total_rows), static_cast<uint64_t>(feat_in) * 2, kKC, kTM,
+                          CU_TENSOR_MAP_SWIZZLE_128B) != 0) {
+    return 1;
+  }
   static thread_local int configured_device = -1;
   int dev = 0;
   SPTIR_CUDA_OK(cudaGetDevice(&dev));
   if (configured_device != dev) {
-    SPTIR_CUDA_OK(cudaFuncSetAttribute(rgms_f16_tc_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemH));
-    SPTIR_CUDA_OK(cudaFuncSetAttribute(rgms_f16_tc_kernel<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemH));
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(rgms_f16_tc_kernel<OutT, GATHER>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemH));
     configured_device = dev;
   }
   int tmem_cols = 32;
@@ -481,9 +553,9 @@ int launch_tc(const __half* z, const __half* w, OutT* y, const int32_t* ranges, 
   const long long tiles = static_cast<long long>(total_rows) / kTM + num_ranges;  // upper bound
   const long long grid = tiles < kNumSMs ? tiles : kNumSMs;
   const int tiles_per_cta = static_cast<int>((tiles + grid - 1) / grid);
-  rgms_f16_tc_kernel<OutT><<<static_cast<unsigned>(grid), kTcThreads, kSmemH, st>>>(
+  rgms_f16_tc_kernel<OutT, GATHER><<<static_cast<unsigned>(grid), GATHER ? kTcThreadsG : kTcThreads, kSmemH, st>>>(
       tm_z, tm_w, y, ranges, all_rows, num_ranges, num_rels, total_rows, tiles_per_cta, feat_in, feat_out,
-      tmem_cols);
+      tmem_cols, x, gcols, gvals);
   SPTIR_LAUNCH_OK("rgms_f16_tc_kernel");
   return 0;
 }
@@ -494,6 +566,26 @@ int run(const BucketTable& tb, const __half* w, const __half* x, OutT* y, int nu
   const int total = tb.z_base[tb.nb];
   const long long num_ranges = static_cast<long long>(tb.nb) * num_rels;
   if (num_ranges >= INT32_MAX) return fail("sparsetir_rgms_ell3d_f16: too many (bucket, relation) pairs");
+  // SPARSETIR_RGMS_F16_PATH=simt keeps the transform on the CUDA cores, =two keeps the two-launch
+  // form where the one-launch form would be taken (comparison switches)
+  static const int path = [] {
+    const char* e = std::getenv("SPARSETIR_RGMS_F16_PATH");
+    if (e && std::strcmp(e, "simt") == 0) return 2;
+    if (e && std::strcmp(e, "two") == 0) return 1;
+    return 0;
+  }();
+  const bool tc_shape = path != 2 && feat_in % kKC == 0 && feat_out % 64 == 0 && feat_out <= kMaxOut &&
+                        aligned16(w) && aligned16(y);
+  if (tc_shape && path == 0 && tb.nb == 1 && tb.width[0] == 1 && aligned16(x)) {
+    // one bucket, one column per row: no Z array, one small launch for the ranges
+    int32_t* ranges1 = static_cast<int32_t*>(workspace(device_id, st, static_cast<size_t>(num_ranges + 1) * sizeof(int32_t)));
+    if (!ranges1) return -1;
+    bucket_ranges_kernel<<<1, kThreads, 0, st>>>(tb, num_rels, ranges1);
+    SPTIR_LAUNCH_OK("bucket_ranges_kernel");
+    const int rc = launch_tc<OutT, true>(nullptr, w, y, ranges1, tb.rows[0], static_cast<int>(num_ranges), num_rels,
+                                         total, feat_in, feat_out, st, x, tb.cols[0], tb.a[0]);
+    if (rc <= 0) return rc;
+  }
   const size_t zb = (static_cast<size_t>(total) * feat_in * sizeof(__half) + 255) & ~static_cast<size_t>(255);
   const size_t rb = (static_cast<size_t>(num_ranges + 1) * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
   char* ws = static_cast<char*>(workspace(device_id, st, zb + rb + static_cast<size_t>(total) * sizeof(int32_t)));
@@ -517,14 +609,9 @@ int run(const BucketTable& tb, const __half* w, const __half* x, OutT* y, int nu
     gather_rows_f16_kernel<1><<<blocks + 1, kThreads, 0, st>>>(tb, x, z, all_rows, ranges, num_rels, feat_in);
   SPTIR_LAUNCH_OK("gather_rows_f16_kernel");
 
-  // SPARSETIR_RGMS_F16_PATH=simt keeps the transform on the CUDA cores (comparison switch)
-  static const bool use_tc = [] {
-    const char* e = std::getenv("SPARSETIR_RGMS_F16_PATH");
-    return !(e && std::strcmp(e, "simt") == 0);
-  }();
-  if (use_tc && feat_in % kKC == 0 && feat_out % 64 == 0 && feat_out <= kMaxOut && aligned16(w) && aligned16(y)) {
-    const int rc = launch_tc<OutT>(z, w, y, ranges, all_rows, static_cast<int>(num_ranges), num_rels, total,
-                                   feat_in, feat_out, st);
+  if (tc_shape) {
+    const int rc = launch_tc<OutT, false>(z, w, y, ranges, all_rows, static_cast<int>(num_ranges), num_rels, total,
+                                          feat_in, feat_out, st);
     if (rc <= 0) return rc;
   }
   const size_t smem = static_cast<size_t>(kSimtRows) * feat_in * sizeof(float);

@@ -495,26 +495,34 @@ def test_rgms_ell3d_f16_matches_oracle(cuda_device, feat_in, feat_out, out_dtype
     close(got, want, rtol=1e-2, atol=2e-2 if out_dtype == torch.float32 else 6e-2)
 
 
-def test_rgms_ell3d_f16_sparse_convolution_shape(cuda_device):
+@pytest.mark.parametrize("feat_in,feat_out,out_dtype", [(64, 128, torch.float32), (128, 64, torch.float16),
+                                                        (256, 256, torch.float32), (64, 32, torch.float32)])
+def test_rgms_ell3d_f16_sparse_convolution_shape(cuda_device, feat_in, feat_out, out_dtype):
     # what the sparse convolution driver builds: one relation per kernel offset (27), every
-    # (input, output) pair its own ELL row (buckets = [1]), unit values, 64 -> 128 channels
+    # (input, output) pair its own ELL row (buckets = [1]), unit values.  Tensor-core shapes take
+    # the one-launch form (X rows gathered inside the kernel), 64 -> 32 the row-scaling launch and
+    # the CUDA-core transform.
     cf = dg.csf_relational(n=4000, num_rels=27, num_edges=60000, zipf_a=0.3, seed=5)
-    feat_in, feat_out = 64, 128
     x16 = dg.dense_operand(3, cf.n, feat_in).astype(np.float16)
     w16 = rect_weights(4, cf.num_rels, feat_in, feat_out)
     buckets = ell3d_buckets(cf, [1], group=1)
     assert all(c.shape[-1] == 1 for _, _, c, _ in buckets)
+    # non-unit values too: the one-launch form applies them in the epilogue
+    a, r, c, m = buckets[0]
+    a = (a * np.random.default_rng(9).uniform(0.5, 1.5, size=a.shape)).astype(np.float16).astype(np.float32)
+    buckets = [(a, r, c, m)]
     want = orc.rgms_ell3d_f16(w16, x16, np.zeros((cf.m, feat_out), np.float32), buckets, feat_in, feat_out)
-    got = run_rgms_ell3d_f16(cf, x16, w16, buckets, cuda_device, feat_in, feat_out, torch.float32)
-    close(got, want, rtol=1e-2, atol=2e-2)
-    # the same as a dense computation: Y[o] = sum over (r, i -> o) of X[i] W_r
+    got = run_rgms_ell3d_f16(cf, x16, w16, buckets, cuda_device, feat_in, feat_out, out_dtype)
+    close(got, want, rtol=1e-2, atol=2e-2 if out_dtype == torch.float32 else 6e-2)
+    # the same as a dense computation: Y[o] = sum over (r, i -> o) of a X[i] W_r
     y = np.zeros((cf.m, feat_out), np.float64)
     xs, ws = x16.astype(np.float64), w16.astype(np.float64)
-    for r in range(cf.num_rels):
-        for t in range(cf.indptr_i[r], cf.indptr_i[r + 1]):
-            src = cf.indices_j[cf.indptr_j[t]:cf.indptr_j[t + 1]]
-            y[cf.indices_i[t]] += xs[src].sum(0) @ ws[r]
-    close(got, y.astype(np.float32), rtol=1e-2, atol=2e-2)
+    av = a.reshape(-1).astype(np.float64)
+    for rel in range(cf.num_rels):
+        for t in range(cf.indptr_i[rel], cf.indptr_i[rel + 1]):
+            sl = slice(cf.indptr_j[t], cf.indptr_j[t + 1])
+            y[cf.indices_i[t]] += (av[sl, None] * xs[cf.indices_j[sl]]).sum(0) @ ws[rel]
+    close(got, y.astype(np.float32), rtol=1e-2, atol=2e-2 if out_dtype == torch.float32 else 6e-2)
 
 
 def test_rgms_ell3d_f16_empty_buckets_and_accumulation(cuda_device):

@@ -403,6 +403,33 @@ def test_rgms_golden_many_relations_and_empty(cuda_device):
     assert np.any(np.diff(ip) <= 1)
 
 
+def test_rgms_larger_graph_eager_and_captured(cuda_device):
+    # a few hundred tiles per block of the persistent kernel, and the same call captured into a
+    # CUDA graph and replayed (the scratch buffer exists after the eager call)
+    cf = dg.csf_relational(n=30000, num_rels=13, num_edges=260001, seed=21)
+    assert cf.nnz_i >= 65536
+    x = dg.dense_operand(22, cf.n, 64)
+    w = dg.relation_weights(23, cf.num_rels, 64)
+    want = oracle_rgms(cf, x, w)
+    close(run_rgms(cf, x, w, cuda_device), want, atol=ATOL * 8)
+    d = cuda_device
+    y = torch.zeros(cf.m * 64, device=d)
+    args = [dev(cf.data, d), dev(w.reshape(-1), d), dev(x.reshape(-1), d), y, dev(cf.indptr_i, d),
+            dev(cf.indices_i, d), dev(cf.indptr_j, d), dev(cf.indices_j, d)]
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        ops.rgms(*args)  # warm-up on the capturing stream: its scratch buffer
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            y.zero_()
+            ops.rgms(*args)
+    for _ in range(2):
+        g.replay()
+    torch.cuda.synchronize()
+    close(y, want, atol=ATOL * 8)
+
+
 def test_rgms_accumulates_into_y(cuda_device):
     cf = dg.csf_relational(n=400, num_rels=4, num_edges=3000, seed=6)
     x = dg.dense_operand(7, cf.n, 64)

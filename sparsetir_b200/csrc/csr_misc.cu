@@ -69,7 +69,7 @@ sparse_softmax_kernel(const float* __restrict__ a, float* __restrict__ b,
   float s = 0.f;
 #pragma unroll
   for (int k = 0; k < CACHE; ++k) {
-    v[k] = (p0 + lane + k * LPR < p1) ? expf(v[k] - mx) : 0.f;
+    v[k] = (p0 + lane + k * LPR < p1) ? __expf(v[k] - mx) : 0.f;
     s += v[k];
   }
   for (int p = p0 + lane + CACHE * LPR; p < p1; p += LPR) s += expf(__ldg(a + p) - mx);

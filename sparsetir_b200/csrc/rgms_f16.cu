@@ -21,6 +21,8 @@
 //       (N-major boxes of 64 x 64) through a 3-stage ring with TMA; one thread issues 4 MMAs
 //       (M = 128, N = feat_out, K = 16) per slice into one of two TMEM accumulators; two groups
 //       of four warps take the even / odd tiles out of TMEM and add them to Y.
+// A single one-column bucket whose (relation, destination) pairs never repeat and whose values
+// are 0 / 1 can also be computed destination-stationary, without reductions (rgms_f16_os_kernel).
 // Shapes the tensor-core launch does not take (feat_in or feat_out not a multiple of 64, feat_out
 // above 256, unaligned operands) go through a CUDA-core transform with the same Z.
 #include <cuda_fp16.h>
@@ -309,7 +311,10 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
                    const int32_t* __restrict__ all_rows, int num_ranges, int num_rels, int total_rows,
                    int tiles_per_cta, int feat_in, int feat_out, int tmem_cols,
                    const __half* __restrict__ x, const int32_t* __restrict__ gcols,
-                   const __half* __restrict__ gvals) {
+                   const __half* __restrict__ gvals, const int32_t* __restrict__ run_if_set) {
+  // run_if_set != nullptr: this launch is the fall-back of the reduction-free form and runs only
+  // when that form found the input unsuitable (flag set on the device)
+  if (run_if_set != nullptr && __ldg(run_if_set) == 0) return;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStagesH];   // the stage's boxes have landed
   __shared__ __align__(8) uint64_t bar_empty[kStagesH];  // the tensor core has read the stage
@@ -496,6 +501,243 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
   if (warp == 0) tc05::tmem_dealloc(tmem, tmem_cols);
 }
 
+// ---- reduction-free form for the sparse-convolution shape.  When every (relation, destination)
+// pair occurs at most once and every value is 0 or 1, Y can be computed destination-stationary:
+// a tile is 128 consecutive destination rows, its accumulator sums over ALL relations in TMEM
+// (row t of relation r's operand is X[map[dst, r]] or zeros), and Y is read and written once
+// instead of receiving one reduction per pair.  conv_map_kernel builds map[dst * R + r] and sets
+// *flag when the input does not qualify; the kernel below then returns at once and the launch of
+// rgms_f16_tc_kernel<OutT, true> that follows it (run_if_set) does the work instead.
+__global__ void __launch_bounds__(kThreads)
+conv_map_kernel(const __half* __restrict__ vals, const int32_t* __restrict__ rows,
+                const int32_t* __restrict__ cols, const int32_t* __restrict__ ranges, int num_rels,
+                int total, int32_t* __restrict__ map, int32_t* __restrict__ flag) {
+  const int q = blockIdx.x * kThreads + threadIdx.x;
+  if (q >= total) return;
+  const float v = __half2float(__ldg(vals + q));
+  if (v == 0.f) return;  // padding row
+  if (v != 1.f) {
+    *flag = 1;
+    return;
+  }
+  int lo = 0, hi = num_rels;  // relation of row q: last r with ranges[r] <= q
+  while (hi - lo > 1) {
+    const int mid = lo + (hi - lo) / 2;
+    if (__ldg(ranges + mid) <= q) lo = mid; else hi = mid;
+  }
+  const int32_t old = atomicCAS(map + static_cast<size_t>(__ldg(rows + q)) * num_rels + lo, -1, __ldg(cols + q));
+  if (old != -1) *flag = 1;  // a second entry for the same (relation, destination)
+}
+
+constexpr int kOsMaxRels = 512;
+constexpr int kOsMaxStages = 8;
+constexpr int kOsMaxGroups = 4;
+constexpr int kOsThreads = 384 + 128 * kOsMaxGroups;  // warps 12.. are the gather groups
+constexpr int kOsSmemLimit = 226 * 1024;  // dynamic part: the static barriers count against the 227 KB too
+
+// the 32 staged columns of the warp's rows are added to Y with plain loads and stores
+__device__ __forceinline__ void store32(float* y, const unsigned char* wbase, int stride, int row_base, int nrows,
+                                        int feat_out, int c0, int lane) {
+#pragma unroll 4
+  for (int i = 0; i < 8; ++i) {
+    const int lr = 4 * i + (lane >> 3);
+    if (lr < nrows) {
+      const float4 v = *reinterpret_cast<const float4*>(wbase + lr * stride + (lane & 7) * 16);
+      float4* dst = reinterpret_cast<float4*>(y + static_cast<size_t>(row_base + lr) * feat_out + c0) + (lane & 7);
+      const float4 o = *dst;
+      *dst = make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w);
+    }
+  }
+}
+__device__ __forceinline__ void store32(__half* y, const unsigned char* wbase, int stride, int row_base, int nrows,
+                                        int feat_out, int c0, int lane) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int lr = 8 * i + (lane >> 2);
+    if (lr < nrows) {
+      const float4 a = *reinterpret_cast<const float4*>(wbase + lr * stride + (lane & 3) * 32);
+      const float4 b = *reinterpret_cast<const float4*>(wbase + lr * stride + (lane & 3) * 32 + 16);
+      uint4* dst = reinterpret_cast<uint4*>(y + static_cast<size_t>(row_base + lr) * feat_out + c0) + (lane & 3);
+      uint4 o = *dst;
+      __half2* h = reinterpret_cast<__half2*>(&o);
+      h[0] = __hadd2(h[0], __floats2half2_rn(a.x, a.y));
+      h[1] = __hadd2(h[1], __floats2half2_rn(a.z, a.w));
+      h[2] = __hadd2(h[2], __floats2half2_rn(b.x, b.y));
+      h[3] = __hadd2(h[3], __floats2half2_rn(b.z, b.w));
+      *dst = o;
+    }
+  }
+}
+
+template <typename OutT>
+__global__ void __launch_bounds__(kOsThreads, 1)
+rgms_f16_os_kernel(const __grid_constant__ CUtensorMap tm_w, OutT* __restrict__ y,
+                   const __half* __restrict__ x, const int32_t* __restrict__ map,
+                   const int32_t* __restrict__ flag, int m, int num_rels, int feat_in, int feat_out,
+                   int tmem_cols, int nstages, int groups) {
+  if (__ldg(flag) != 0) return;  // the input does not qualify: the next launch does the work
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kOsMaxStages];
+  __shared__ __align__(8) uint64_t bar_empty[kOsMaxStages];
+  __shared__ __align__(8) uint64_t bar_acc_full[2];
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];
+  __shared__ uint32_t s_tmem;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  unsigned char* base = smem_raw + ((1024u - (tc05::smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int nkc = feat_in / kKC, nwb = feat_out / 64;
+  // a stage is the gathered Z box plus feat_out / 64 W boxes; the transposing buffer of the
+  // epilogue follows the nstages stages
+  const int stride = kZBoxB + nwb * kWBoxB;
+  const int off_out = nstages * stride;
+  const int ntiles = (m + kTM - 1) / kTM;
+  // tiles blockIdx.x, blockIdx.x + gridDim.x, ...; the grid never exceeds the number of tiles
+  const int my_tiles = (ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x);
+  const int steps = num_rels * nkc;  // stages per tile
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int s = 0; s < nstages; ++s) {
+        tc05::mbar_init(&bar_full[s], 1 + 128);
+        tc05::mbar_init(&bar_empty[s], 1);
+      }
+      for (int b = 0; b < 2; ++b) {
+        tc05::mbar_init(&bar_acc_full[b], 1);
+        tc05::mbar_init(&bar_acc_empty[b], 128);
+      }
+      tc05::fence_mbar_init();
+      tc05::prefetch_tensormap(&tm_w);
+    }
+    __syncwarp();
+    tc05::tmem_alloc(&s_tmem, tmem_cols);
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tmem = s_tmem;
+  bool ok = true;
+  int armed = 0;
+
+  if (warp == 0) {
+    // ---- W slices by TMA: relation r, slice c of every tile
+    if (lane == 0) {
+      int it = 0;
+      const uint32_t stage_bytes = nwb * kWBoxB;
+      for (int k = 0; k < my_tiles && ok; ++k) {
+        for (int sidx = 0; sidx < steps; ++sidx, ++it) {
+          const int s = it % nstages, use = it / nstages;
+          if (use > 0 && !tc05::mbar_wait(&bar_empty[s], (use - 1) & 1)) { ok = false; break; }
+          unsigned char* st = base + s * stride;
+          tc05::mbar_arrive_expect_tx(&bar_full[s], stage_bytes);
+          for (int j = 0; j < nwb; ++j)
+            tc05::tma_load_2d(st + kZBoxB + j * kWBoxB, &tm_w, j * 64, sidx * kKC, &bar_full[s]);
+          armed = it + 1;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: one accumulator per tile, summed over all relations and slices
+    if (lane == 0) {
+      const uint32_t idesc = tc05::instr_desc(tc05::kFmtF16, kTM, feat_out, /*a_mn=*/0, /*b_mn=*/1);
+      const uint64_t dz0 = tc05::smem_desc_swizzled(tc05::smem_u32(base), 0, 1024, tc05::kSwizzle128B);
+      const uint64_t dw0 = tc05::smem_desc_swizzled(tc05::smem_u32(base) + kZBoxB, kWBoxB, 1024, tc05::kSwizzle128B);
+      int it = 0;
+      for (int k = 0; k < my_tiles && ok; ++k) {
+        const int buf = k & 1, buse = k >> 1;
+        if (buse > 0 && !tc05::mbar_wait(&bar_acc_empty[buf], (buse - 1) & 1)) { ok = false; break; }
+        const uint32_t acc = tmem + buf * feat_out;
+        for (int sidx = 0; sidx < steps; ++sidx, ++it) {
+          const int s = it % nstages, use = it / nstages;
+          if (!tc05::mbar_wait(&bar_full[s], use & 1)) { ok = false; break; }
+          tc05::fence_after_sync();
+          const uint64_t dz = tc05::desc_advance(dz0, s * stride);
+          const uint64_t dw = tc05::desc_advance(dw0, s * stride);
+#pragma unroll
+          for (int ks = 0; ks < kKC / 16; ++ks)
+            tc05::mma_f16(acc, tc05::desc_advance(dz, ks * 32), tc05::desc_advance(dw, ks * 2048), idesc,
+                          (sidx > 0 || ks > 0) ? 1u : 0u);
+          tc05::mma_commit(&bar_empty[s]);
+        }
+        if (!ok) break;
+        tc05::mma_commit(&bar_acc_full[buf]);
+      }
+    }
+  } else if (warp >= 12) {
+    // ---- gather groups: group g (four warps) fills the Z box of the steps g, g + G, g + 2G, ...
+    // (warp gw of the group rows gw*32 .. gw*32+31): wait for the stage, issue the copies, wait
+    // for them to land, make them visible to the tensor core's proxy, arrive.  G groups keep G
+    // gathers in flight.  A missing pair (-1 in the map) is a zero-filled copy.
+    const int g = (warp - 12) >> 2, gw = (warp - 12) & 3;
+    const int total_steps = my_tiles * steps;
+    auto map_entry = [&](int n) -> int {  // source row of this lane's tile row at step n
+      const int k = n / steps, r = (n - k * steps) / nkc;
+      const int row = (static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x)) * kTM + gw * 32 + lane;
+      return row < m ? __ldg(map + static_cast<size_t>(row) * num_rels + r) : -1;
+    };
+    int entry = g < groups && g < total_steps ? map_entry(g) : -1;
+    for (int n = g; g < groups && n < total_steps; n += groups) {
+      const int c = n % nkc;
+      const int entry_next = n + groups < total_steps ? map_entry(n + groups) : -1;
+      const int s = n % nstages, use = n / nstages;
+      if (use > 0 && !tc05::mbar_wait(&bar_empty[s], (use - 1) & 1)) { ok = false; break; }
+      const uint32_t st = tc05::smem_u32(base + s * stride);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int lr = 4 * i + (lane >> 3);  // row inside the warp's 32
+        const int src_row = __shfl_sync(0xffffffffu, entry, lr);
+        const int row = gw * 32 + lr, chunk = lane & 7;
+        const __half* src = x + static_cast<size_t>(max(src_row, 0)) * feat_in + c * kKC + chunk * 8;
+        const uint32_t dst = st + (row >> 3) * 1024 + (row & 7) * 128 + ((chunk ^ (row & 7)) << 4);
+        const uint32_t bytes = src_row >= 0 ? 16u : 0u;  // 0: the 16 bytes are filled with zeros
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      tc05::fence_async_smem();
+      mbar_arrive_local(&bar_full[s]);
+      entry = entry_next;
+    }
+  } else if (warp >= 4) {
+    // ---- epilogue: group 0 (warps 4-7) even tiles, group 1 (warps 8-11) odd tiles; thread = row
+    const int grp = warp >= 8 ? 1 : 0;
+    const int t = (warp & 3) * 32 + lane;
+    unsigned char* gbuf = base + off_out + grp * (kTM * kOutStride);
+    unsigned char* my_row = gbuf + t * kOutStride;
+    const unsigned char* wbase = gbuf + (warp & 3) * 32 * kOutStride;
+    for (int k = grp; k < my_tiles; k += 2) {
+      const int buse = k >> 1;
+      const int row_base = (static_cast<int>(blockIdx.x) + k * static_cast<int>(gridDim.x)) * kTM + (warp & 3) * 32;
+      const int nrows = min(32, m - row_base);  // live rows among the warp's 32 (may be <= 0)
+      if (!tc05::mbar_wait(&bar_acc_full[grp], buse & 1)) { ok = false; break; }
+      tc05::fence_after_sync();
+      const uint32_t taddr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16) + grp * feat_out;
+      for (int c0 = 0; c0 < feat_out; c0 += 32) {
+        uint32_t r[32];
+        tc05::tmem_ld32(taddr + c0, r);
+        if (c0 + 32 >= feat_out) {
+          tc05::fence_before_sync();
+          mbar_arrive_local(&bar_acc_empty[grp]);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<uint4*>(my_row + q * 16) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+        __syncwarp();
+        store32(y, wbase, kOutStride, row_base, nrows, feat_out, c0, lane);
+      }
+    }
+  }
+
+  const bool all_ok = !__syncthreads_or(!ok);
+  if (!all_ok && tid == 0) {
+    atomicAdd(&g_rgms_f16_timeouts, 1u);
+    for (int it = max(0, armed - nstages); it < armed; ++it)
+      tc05::mbar_wait(&bar_full[it % nstages], (it / nstages) & 1);
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc05::tmem_dealloc(tmem, tmem_cols);
+}
+
 }  // namespace
 
 int rgms_f16_timeouts(unsigned int* count) {
@@ -528,7 +770,8 @@ bucket_ranges_kernel(const __grid_constant__ BucketTable tb, int num_rels, int32
 template <typename OutT, bool GATHER>
 int launch_tc(const __half* z, const __half* w, OutT* y, const int32_t* ranges, const int32_t* all_rows,
               int num_ranges, int num_rels, int total_rows, int feat_in, int feat_out, cudaStream_t st,
-              const __half* x = nullptr, const int32_t* gcols = nullptr, const __half* gvals = nullptr) {
+              const __half* x = nullptr, const int32_t* gcols = nullptr, const __half* gvals = nullptr,
+              const int32_t* run_if_set = nullptr) {
   CUtensorMap tm_z, tm_w;
   if (make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w, static_cast<uint64_t>(feat_out),
                    static_cast<uint64_t>(num_rels) * feat_in, static_cast<uint64_t>(feat_out) * 2, 64, kKC,
@@ -555,35 +798,97 @@ int launch_tc(const __half* z, const __half* w, OutT* y, const int32_t* ranges, 
   const int tiles_per_cta = static_cast<int>((tiles + grid - 1) / grid);
   rgms_f16_tc_kernel<OutT, GATHER><<<static_cast<unsigned>(grid), GATHER ? kTcThreadsG : kTcThreads, kSmemH, st>>>(
       tm_z, tm_w, y, ranges, all_rows, num_ranges, num_rels, total_rows, tiles_per_cta, feat_in, feat_out,
-      tmem_cols, x, gcols, gvals);
+      tmem_cols, x, gcols, gvals, run_if_set);
   SPTIR_LAUNCH_OK("rgms_f16_tc_kernel");
   return 0;
 }
 
+// 0 when launched, 1 when this form cannot take the call, -1 on error
 template <typename OutT>
-int run(const BucketTable& tb, const __half* w, const __half* x, OutT* y, int num_rels, int feat_in,
+int launch_os(const __half* w, OutT* y, const __half* x, const int32_t* map, const int32_t* flag, int m,
+              int num_rels, int feat_in, int feat_out, cudaStream_t st) {
+  CUtensorMap tm_w;
+  if (make_tmap_2d(&tm_w, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, w, static_cast<uint64_t>(feat_out),
+                   static_cast<uint64_t>(num_rels) * feat_in, static_cast<uint64_t>(feat_out) * 2, 64, kKC,
+                   CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return 1;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  SPTIR_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(rgms_f16_os_kernel<OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kOsSmemLimit));
+    configured_device = dev;
+  }
+  // as many stages as fit beside the epilogue's buffer and the map slab
+  const int stride = kZBoxB + (feat_out / 64) * kWBoxB;
+  const int fixed = 2 * kTM * kOutStride + 1024;
+  const int nstages = std::min(kOsMaxStages, (kOsSmemLimit - fixed) / stride);
+  if (nstages < 3) return 1;
+  const int smem = nstages * stride + fixed;
+  const int groups = std::min(kOsMaxGroups, nstages - 1);
+  int tmem_cols = 32;
+  while (tmem_cols < 2 * feat_out) tmem_cols *= 2;
+  const int ntiles = ceil_div(m, kTM);
+  const int grid = ntiles < kNumSMs ? ntiles : kNumSMs;
+  rgms_f16_os_kernel<OutT><<<grid, kOsThreads, smem, st>>>(tm_w, y, x, map, flag, m, num_rels, feat_in,
+                                                             feat_out, tmem_cols, nstages, groups);
+  SPTIR_LAUNCH_OK("rgms_f16_os_kernel");
+  return 0;
+}
+
+template <typename OutT>
+int run(const BucketTable& tb, const __half* w, const __half* x, OutT* y, int m, int num_rels, int feat_in,
         int feat_out, int device_id, cudaStream_t st) {
   const int total = tb.z_base[tb.nb];
   const long long num_ranges = static_cast<long long>(tb.nb) * num_rels;
   if (num_ranges >= INT32_MAX) return fail("sparsetir_rgms_ell3d_f16: too many (bucket, relation) pairs");
   // SPARSETIR_RGMS_F16_PATH=simt keeps the transform on the CUDA cores, =two keeps the two-launch
-  // form where the one-launch form would be taken (comparison switches)
+  // form where the one-launch form would be taken, =atomic keeps the one-launch form with
+  // reductions where the reduction-free form would be tried, =os tries the reduction-free form
+  // for every shape it can take (comparison switches)
   static const int path = [] {
     const char* e = std::getenv("SPARSETIR_RGMS_F16_PATH");
     if (e && std::strcmp(e, "simt") == 0) return 2;
     if (e && std::strcmp(e, "two") == 0) return 1;
+    if (e && std::strcmp(e, "atomic") == 0) return 3;
+    if (e && std::strcmp(e, "os") == 0) return 4;
     return 0;
   }();
   const bool tc_shape = path != 2 && feat_in % kKC == 0 && feat_out % 64 == 0 && feat_out <= kMaxOut &&
                         aligned16(w) && aligned16(y);
-  if (tc_shape && path == 0 && tb.nb == 1 && tb.width[0] == 1 && aligned16(x)) {
-    // one bucket, one column per row: no Z array, one small launch for the ranges
-    int32_t* ranges1 = static_cast<int32_t*>(workspace(device_id, st, static_cast<size_t>(num_ranges + 1) * sizeof(int32_t)));
-    if (!ranges1) return -1;
+  if (tc_shape && (path == 0 || path == 3 || path == 4) && tb.nb == 1 && tb.width[0] == 1 && aligned16(x)) {
+    // one bucket, one column per row: no Z array.  Scratch: the relation ranges, a flag, and —
+    // for the reduction-free form — the (destination, relation) -> source map.
+    // The reduction-free form re-reads a slice of W_r per (destination tile, relation), which
+    // costs more than the reductions it saves unless the slice is small and Y is float32
+    // (measured on 100,000 points x 27 offsets: 64->128 float32 154 us against 187 us, but
+    // 128->128 225 against 197 us and 210 against 153 us with a float16 Y): by default it is
+    // tried for feat_in = 64 and a float32 Y only.
+    const bool os_pays = path == 4 || (feat_in == kKC && sizeof(OutT) == 4);
+    const bool try_os = (path == 0 || path == 4) && os_pays && num_rels <= kOsMaxRels &&
+                        static_cast<long long>(m) * num_rels < (1ll << 30);
+    const size_t rb1 = (static_cast<size_t>(num_ranges + 1) * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
+    const size_t map_bytes = try_os ? static_cast<size_t>(m) * num_rels * sizeof(int32_t) : 0;
+    char* ws1 = static_cast<char*>(workspace(device_id, st, rb1 + 256 + map_bytes));
+    if (!ws1) return -1;
+    int32_t* ranges1 = reinterpret_cast<int32_t*>(ws1);
+    int32_t* flag = reinterpret_cast<int32_t*>(ws1 + rb1);
+    int32_t* map = reinterpret_cast<int32_t*>(ws1 + rb1 + 256);
     bucket_ranges_kernel<<<1, kThreads, 0, st>>>(tb, num_rels, ranges1);
     SPTIR_LAUNCH_OK("bucket_ranges_kernel");
-    const int rc = launch_tc<OutT, true>(nullptr, w, y, ranges1, tb.rows[0], static_cast<int>(num_ranges), num_rels,
-                                         total, feat_in, feat_out, st, x, tb.cols[0], tb.a[0]);
+    int rc = 1;
+    if (try_os) {
+      SPTIR_CUDA_OK(cudaMemsetAsync(flag, 0, sizeof(int32_t), st));
+      SPTIR_CUDA_OK(cudaMemsetAsync(map, 0xFF, map_bytes, st));
+      conv_map_kernel<<<ceil_div(total, kThreads), kThreads, 0, st>>>(tb.a[0], tb.rows[0], tb.cols[0], ranges1,
+                                                                     num_rels, total, map, flag);
+      SPTIR_LAUNCH_OK("conv_map_kernel");
+      rc = launch_os<OutT>(w, y, x, map, flag, m, num_rels, feat_in, feat_out, st);
+      if (rc < 0) return rc;
+    }
+    // rc == 0: the reduction-free launch is queued; this one runs only if it found the flag set
+    rc = launch_tc<OutT, true>(nullptr, w, y, ranges1, tb.rows[0], static_cast<int>(num_ranges), num_rels, total,
+                               feat_in, feat_out, st, x, tb.cols[0], tb.a[0], rc == 0 ? flag : nullptr);
     if (rc <= 0) return rc;
   }
   const size_t zb = (static_cast<size_t>(total) * feat_in * sizeof(__half) + 255) & ~static_cast<size_t>(255);
@@ -665,7 +970,7 @@ extern "C" int sparsetir_rgms_ell3d_f16_raw(const void* w, const void* x, void* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (y_is_f16)
     return run<__half>(tb, static_cast<const __half*>(w), static_cast<const __half*>(x), static_cast<__half*>(y),
-                       num_rels, feat_in, feat_out, device_id, st);
+                       m, num_rels, feat_in, feat_out, device_id, st);
   return run<float>(tb, static_cast<const __half*>(w), static_cast<const __half*>(x), static_cast<float*>(y),
-                    num_rels, feat_in, feat_out, device_id, st);
+                    m, num_rels, feat_in, feat_out, device_id, st);
 }

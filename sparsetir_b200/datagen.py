@@ -221,6 +221,27 @@ def csf_relational(n: int = 100_000, num_rels: int = 46, num_edges: int = 1_500_
                _indptr(deg_all), np.concatenate(indices_j), np.concatenate(data))
 
 
+def sparse_conv_pairs(n_in: int = 100_000, n_out: int = 100_000, num_offsets: int = 27,
+                      fill: float = 0.5926, seed: int = 0) -> CSF:
+    """The neighbour maps of a sparse convolution as a CSF tensor: relation = kernel offset; for
+    every offset each output point has, with probability ``fill``, exactly ONE input point
+    (uniformly drawn), so a (relation, destination) pair never repeats; values 1.  Outputs are
+    ascending inside an offset.  Stand-in for the ``nbmaps`` / ``nbsizes`` of the layer files
+    that examples/rgms/sparse_conv/sparse_conv.py:46-60 loads (not available here)."""
+    rng = _rng(seed)
+    indptr_i = [0]
+    indices_i, indices_j = [], []
+    for _ in range(num_offsets):
+        outs = np.nonzero(rng.random(n_out) < fill)[0].astype(np.int32)
+        indices_i.append(outs)
+        indices_j.append(rng.integers(0, n_in, size=len(outs)).astype(np.int32))
+        indptr_i.append(indptr_i[-1] + len(outs))
+    rows = np.concatenate(indices_i)
+    return CSF(n_out, n_in, num_offsets, np.asarray(indptr_i, dtype=np.int32), rows,
+               np.arange(len(rows) + 1, dtype=np.int32), np.concatenate(indices_j),
+               np.ones(len(rows), np.float32))
+
+
 def relation_weights(seed: int, num_rels: int, feat: int) -> np.ndarray:
     """W[r, fo, fi] ~ N(0, 1/feat)."""
     return (_rng(seed).standard_normal((num_rels, feat, feat)) / np.sqrt(feat)).astype(np.float32)

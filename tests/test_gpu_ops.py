@@ -552,6 +552,68 @@ def test_rgms_ell3d_f16_sparse_convolution_shape(cuda_device, feat_in, feat_out,
     close(got, y.astype(np.float32), rtol=1e-2, atol=2e-2 if out_dtype == torch.float32 else 6e-2)
 
 
+@pytest.mark.parametrize("feat_in,feat_out,out_dtype,n_out", [(64, 128, torch.float32, 5000), (128, 64, torch.float16, 3001),
+                                                              (64, 64, torch.float32, 130), (256, 256, torch.float16, 2048)])
+def test_rgms_ell3d_f16_sparse_convolution_maps_without_repeats(cuda_device, feat_in, feat_out, out_dtype, n_out):
+    # neighbour maps in which a (kernel offset, output) pair never repeats and all values are 1:
+    # the destination-stationary form (no reductions into Y); Y already holds values
+    cf = dg.sparse_conv_pairs(n_in=4000, n_out=n_out, num_offsets=27, fill=0.6, seed=feat_in + n_out)
+    x16 = dg.dense_operand(3, cf.n, feat_in).astype(np.float16)
+    w16 = rect_weights(4, cf.num_rels, feat_in, feat_out)
+    buckets = ell3d_buckets(cf, [1], group=1)
+    y0 = np.random.default_rng(1).uniform(-1, 1, size=(cf.m, feat_out)).astype(np.float16).astype(np.float32)
+    want = orc.rgms_ell3d_f16(w16, x16, y0.copy(), buckets, feat_in, feat_out)
+    y = dev(y0.reshape(-1), cuda_device).to(out_dtype)
+    devb = [(dev(a.astype(np.float16), cuda_device), dev(r, cuda_device), dev(c, cuda_device), dev(m, cuda_device))
+            for a, r, c, m in buckets]
+    ops.rgms_ell3d_f16(*ops.rgms_ell3d_f16_args(dev(w16, cuda_device), dev(x16, cuda_device), y, devb, feat_in, feat_out))
+    torch.cuda.synchronize()
+    close(y.float(), want, rtol=1e-2, atol=2e-2 if out_dtype == torch.float32 else 6e-2)
+    # one repeated pair, or one value that is not 0 / 1, sends the same call to the form with reductions
+    a, r, c, m = buckets[0]
+    r2 = r.copy()
+    r2[1] = r2[0]  # rows 0 and 1 of relation 0 now share their destination
+    a3 = a.copy()
+    a3[2] = 0.5
+    for bk in ([(a, r2, c, m)], [(a3, r, c, m)]):
+        want2 = orc.rgms_ell3d_f16(w16, x16, np.zeros((cf.m, feat_out), np.float32), bk, feat_in, feat_out)
+        got2 = run_rgms_ell3d_f16(cf, x16, w16, bk, cuda_device, feat_in, feat_out, out_dtype)
+        close(got2, want2, rtol=1e-2, atol=2e-2 if out_dtype == torch.float32 else 6e-2)
+
+
+def test_rgms_ell3d_f16_reduction_free_form_forced_in_child_process(cuda_device, tmp_path):
+    # by default only feat_in = 64 with a float32 Y takes the destination-stationary form; the
+    # switch (read once per process) sends every eligible shape through it
+    import subprocess
+    import sys
+    cf = dg.sparse_conv_pairs(n_in=3000, n_out=2500, num_offsets=27, fill=0.6, seed=77)
+    buckets = ell3d_buckets(cf, [1], group=1)
+    a, r, c, m = buckets[0]
+    cases = {}
+    for name, (fi, fo, dt) in {"h": (128, 64, "float16"), "w": (256, 256, "float32"), "s": (64, 192, "float16")}.items():
+        x16 = dg.dense_operand(3, cf.n, fi).astype(np.float16)
+        w16 = rect_weights(4, cf.num_rels, fi, fo)
+        want = orc.rgms_ell3d_f16(w16, x16, np.zeros((cf.m, fo), np.float32), buckets, fi, fo)
+        cases.update({f"x_{name}": x16, f"w_{name}": w16, f"want_{name}": want,
+                      f"meta_{name}": np.array([fi, fo, 1 if dt == "float16" else 0])})
+    case = str(tmp_path / "case.npz")
+    np.savez(case, a=a.astype(np.float16), r=r, c=c, m=m, **cases)
+    code = ("import numpy as np, torch, sys; sys.path.insert(0, %r); from sparsetir_b200 import ops\n"
+            "z = np.load(%r); d = torch.device('cuda', 0)\n"
+            "t = lambda v: torch.from_numpy(np.ascontiguousarray(v)).to(d)\n"
+            "bk = [(t(z['a']), t(z['r']), t(z['c']), t(z['m']))]\n"
+            "for n in 'hws':\n"
+            "    fi, fo, half = (int(v) for v in z['meta_' + n])\n"
+            "    y = torch.zeros(z['want_' + n].size, device=d, dtype=torch.float16 if half else torch.float32)\n"
+            "    ops.rgms_ell3d_f16(*ops.rgms_ell3d_f16_args(t(z['w_' + n]), t(z['x_' + n]), y, bk, fi, fo))\n"
+            "    torch.cuda.synchronize()\n"
+            "    np.testing.assert_allclose(y.float().cpu().numpy().reshape(z['want_' + n].shape), z['want_' + n], rtol=1e-2, atol=6e-2 if half else 2e-2)\n"
+            "print('reduction-free ok')" % (os.path.dirname(os.path.dirname(os.path.abspath(__file__))), case))
+    res = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, SPARSETIR_RGMS_F16_PATH="os"),
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0 and "reduction-free ok" in res.stdout, res.stdout + res.stderr
+
+
 def test_rgms_ell3d_f16_empty_buckets_and_accumulation(cuda_device):
     cf = dg.csf_relational(n=300, num_rels=3, num_edges=4000, seed=8)
     feat_in, feat_out = 64, 64

@@ -314,7 +314,7 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
                    const __half* __restrict__ gvals, const int32_t* __restrict__ run_if_set) {
   // run_if_set != nullptr: this launch is the fall-back of the reduction-free form and runs only
   // when that form found the input unsuitable (flag set on the device)
-  if (run_if_set != nullptr && __ldg(run_if_set) == 0) return;
+  if (run_if_set != nullptr && __ldg(run_if_set) == -1) return;
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kStagesH];   // the stage's boxes have landed
   __shared__ __align__(8) uint64_t bar_empty[kStagesH];  // the tensor core has read the stage
@@ -505,13 +505,13 @@ rgms_f16_tc_kernel(const __grid_constant__ CUtensorMap tm_z, const __grid_consta
 // pair occurs at most once and every value is 0 or 1, Y can be computed destination-stationary:
 // a tile is 128 consecutive destination rows, its accumulator sums over ALL relations in TMEM
 // (row t of relation r's operand is X[map[dst, r]] or zeros), and Y is read and written once
-// instead of receiving one reduction per pair.  conv_map_kernel builds map[dst * R + r] and sets
-// *flag when the input does not qualify; the kernel below then returns at once and the launch of
+// instead of receiving one reduction per pair.  conv_map_kernel builds map[dst * R + r] (both it
+// and *flag start as -1, one memset) and sets *flag to 1 when the input does not qualify; the kernel below then returns at once and the launch of
 // rgms_f16_tc_kernel<OutT, true> that follows it (run_if_set) does the work instead.
 __global__ void __launch_bounds__(kThreads)
 conv_map_kernel(const __half* __restrict__ vals, const int32_t* __restrict__ rows,
-                const int32_t* __restrict__ cols, const int32_t* __restrict__ ranges, int num_rels,
-                int total, int32_t* __restrict__ map, int32_t* __restrict__ flag) {
+                const int32_t* __restrict__ cols, const int32_t* __restrict__ mid, int rows_per_group,
+                int num_rels, int total, int32_t* __restrict__ map, int32_t* __restrict__ flag) {
   const int q = blockIdx.x * kThreads + threadIdx.x;
   if (q >= total) return;
   const float v = __half2float(__ldg(vals + q));
@@ -520,12 +520,8 @@ conv_map_kernel(const __half* __restrict__ vals, const int32_t* __restrict__ row
     *flag = 1;
     return;
   }
-  int lo = 0, hi = num_rels;  // relation of row q: last r with ranges[r] <= q
-  while (hi - lo > 1) {
-    const int mid = lo + (hi - lo) / 2;
-    if (__ldg(ranges + mid) <= q) lo = mid; else hi = mid;
-  }
-  const int32_t old = atomicCAS(map + static_cast<size_t>(__ldg(rows + q)) * num_rels + lo, -1, __ldg(cols + q));
+  const int rel = __ldg(mid + q / rows_per_group);
+  const int32_t old = atomicCAS(map + static_cast<size_t>(__ldg(rows + q)) * num_rels + rel, -1, __ldg(cols + q));
   if (old != -1) *flag = 1;  // a second entry for the same (relation, destination)
 }
 
@@ -575,7 +571,7 @@ rgms_f16_os_kernel(const __grid_constant__ CUtensorMap tm_w, OutT* __restrict__ 
                    const __half* __restrict__ x, const int32_t* __restrict__ map,
                    const int32_t* __restrict__ flag, int m, int num_rels, int feat_in, int feat_out,
                    int tmem_cols, int nstages, int groups) {
-  if (__ldg(flag) != 0) return;  // the input does not qualify: the next launch does the work
+  if (__ldg(flag) != -1) return;  // the input does not qualify: the next launch does the work
   extern __shared__ unsigned char smem_raw[];
   __shared__ __align__(8) uint64_t bar_full[kOsMaxStages];
   __shared__ __align__(8) uint64_t bar_empty[kOsMaxStages];
@@ -878,10 +874,9 @@ int run(const BucketTable& tb, const __half* w, const __half* x, OutT* y, int m,
     SPTIR_LAUNCH_OK("bucket_ranges_kernel");
     int rc = 1;
     if (try_os) {
-      SPTIR_CUDA_OK(cudaMemsetAsync(flag, 0, sizeof(int32_t), st));
-      SPTIR_CUDA_OK(cudaMemsetAsync(map, 0xFF, map_bytes, st));
-      conv_map_kernel<<<ceil_div(total, kThreads), kThreads, 0, st>>>(tb.a[0], tb.rows[0], tb.cols[0], ranges1,
-                                                                     num_rels, total, map, flag);
+      SPTIR_CUDA_OK(cudaMemsetAsync(flag, 0xFF, 256 + map_bytes, st));  // flag = -1 (eligible), map = -1
+      conv_map_kernel<<<ceil_div(total, kThreads), kThreads, 0, st>>>(tb.a[0], tb.rows[0], tb.cols[0], tb.mid[0],
+                                                                     tb.rows_per_group[0], num_rels, total, map, flag);
       SPTIR_LAUNCH_OK("conv_map_kernel");
       rc = launch_os<OutT>(w, y, x, map, flag, m, num_rels, feat_in, feat_out, st);
       if (rc < 0) return rc;

@@ -531,36 +531,51 @@ constexpr int kOsMaxGroups = 4;
 constexpr int kOsThreads = 384 + 128 * kOsMaxGroups;  // warps 12.. are the gather groups
 constexpr int kOsSmemLimit = 226 * 1024;  // dynamic part: the static barriers count against the 227 KB too
 
-// the 32 staged columns of the warp's rows are added to Y with plain loads and stores
+// the 32 staged columns of the warp's rows are added to Y with plain loads and stores; all loads
+// of the old values are issued before the first store (stores to Y would otherwise order them)
 __device__ __forceinline__ void store32(float* y, const unsigned char* wbase, int stride, int row_base, int nrows,
                                         int feat_out, int c0, int lane) {
-#pragma unroll 4
+  float4 old[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int lr = 4 * i + (lane >> 3);
+    old[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (lr < nrows)
+      old[i] = __ldcs(reinterpret_cast<const float4*>(y + static_cast<size_t>(row_base + lr) * feat_out + c0) + (lane & 7));
+  }
+#pragma unroll
   for (int i = 0; i < 8; ++i) {
     const int lr = 4 * i + (lane >> 3);
     if (lr < nrows) {
       const float4 v = *reinterpret_cast<const float4*>(wbase + lr * stride + (lane & 7) * 16);
-      float4* dst = reinterpret_cast<float4*>(y + static_cast<size_t>(row_base + lr) * feat_out + c0) + (lane & 7);
-      const float4 o = *dst;
-      *dst = make_float4(o.x + v.x, o.y + v.y, o.z + v.z, o.w + v.w);
+      __stcs(reinterpret_cast<float4*>(y + static_cast<size_t>(row_base + lr) * feat_out + c0) + (lane & 7),
+             make_float4(old[i].x + v.x, old[i].y + v.y, old[i].z + v.z, old[i].w + v.w));
     }
   }
 }
 __device__ __forceinline__ void store32(__half* y, const unsigned char* wbase, int stride, int row_base, int nrows,
                                         int feat_out, int c0, int lane) {
+  uint4 old[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int lr = 8 * i + (lane >> 2);
+    old[i] = make_uint4(0u, 0u, 0u, 0u);
+    if (lr < nrows)
+      old[i] = __ldcs(reinterpret_cast<const uint4*>(y + static_cast<size_t>(row_base + lr) * feat_out + c0) + (lane & 3));
+  }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
     const int lr = 8 * i + (lane >> 2);
     if (lr < nrows) {
       const float4 a = *reinterpret_cast<const float4*>(wbase + lr * stride + (lane & 3) * 32);
       const float4 b = *reinterpret_cast<const float4*>(wbase + lr * stride + (lane & 3) * 32 + 16);
-      uint4* dst = reinterpret_cast<uint4*>(y + static_cast<size_t>(row_base + lr) * feat_out + c0) + (lane & 3);
-      uint4 o = *dst;
+      uint4 o = old[i];
       __half2* h = reinterpret_cast<__half2*>(&o);
       h[0] = __hadd2(h[0], __floats2half2_rn(a.x, a.y));
       h[1] = __hadd2(h[1], __floats2half2_rn(a.z, a.w));
       h[2] = __hadd2(h[2], __floats2half2_rn(b.x, b.y));
       h[3] = __hadd2(h[3], __floats2half2_rn(b.z, b.w));
-      *dst = o;
+      __stcs(reinterpret_cast<uint4*>(y + static_cast<size_t>(row_base + lr) * feat_out + c0) + (lane & 3), o);
     }
   }
 }
@@ -857,8 +872,8 @@ int run(const BucketTable& tb, const __half* w, const __half* x, OutT* y, int m,
     // for the reduction-free form — the (destination, relation) -> source map.
     // The reduction-free form re-reads a slice of W_r per (destination tile, relation), which
     // costs more than the reductions it saves unless the slice is small and Y is float32
-    // (measured on 100,000 points x 27 offsets: 64->128 float32 154 us against 187 us, but
-    // 128->128 225 against 197 us and 210 against 153 us with a float16 Y): by default it is
+    // (measured on 100,000 points x 27 offsets: 64->128 float32 138 us against 187 us, but
+    // 128->128 211 against 197 us and 207 against 153 us with a float16 Y): by default it is
     // tried for feat_in = 64 and a float32 Y only.
     const bool os_pays = path == 4 || (feat_in == kKC && sizeof(OutT) == 4);
     const bool try_os = (path == 0 || path == 4) && os_pays && num_rels <= kOsMaxRels &&

@@ -181,6 +181,15 @@ def test_later_operators_validation_messages():
         ops.rgms_ell3d(f32(16), f32(8), f32(8), f32(4), i32(2), 4)
     with pytest.raises(ops.SparseTIRError, match="do not describe groups x rows x columns"):
         ops.rgms_ell3d(f32(16), f32(8), f32(8), f32(6), i32(3), i32(6), i32(2), 4)
+    # fp16 RGMS with rectangular weights: two trailing scalars, float16 operands, y float16 or float32
+    with pytest.raises(ops.SparseTIRError, match="expected \\(w, x, y"):
+        ops.rgms_ell3d_f16(f16(16), f16(8), f32(8), f16(4), i32(4), i32(4), i32(2), 4)
+    with pytest.raises(ops.SparseTIRError, match="w.dtype is expected to be float16"):
+        ops.rgms_ell3d_f16(f32(16), f16(8), f32(8), 4, 4)
+    with pytest.raises(ops.SparseTIRError, match="must be multiples of feat_in\\*feat_out"):
+        ops.rgms_ell3d_f16(f16(17), f16(8), f32(8), 4, 4)
+    with pytest.raises(ops.SparseTIRError, match="do not describe groups x rows x columns"):
+        ops.rgms_ell3d_f16(f16(32), f16(8), f16(16), f16(6), i32(3), i32(6), i32(2), 4, 8)
     # the small row-wise operators
     with pytest.raises(ops.SparseTIRError, match="indptr.shape"):
         ops.csr_reduce(f32(5), f32(3), i32(5))

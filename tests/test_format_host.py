@@ -192,3 +192,17 @@ def test_csf_to_ell3d_empty_relations_and_rows():
             assert np.array_equal(a, b)
     with pytest.raises(ValueError, match="ascending"):
         fmt.csf_to_ell3d(ip0, ix0, ip1, ix1, [2, 2], [2, 1])
+
+
+def test_sparse_conv_pairs_generator_has_no_repeated_pair():
+    """The stand-in for sparse-convolution neighbour maps: inside an offset every output appears at
+    most once, ascending, with exactly one input; values are 1."""
+    from sparsetir_b200 import datagen as dg
+    cf = dg.sparse_conv_pairs(n_in=500, n_out=700, num_offsets=9, fill=0.5, seed=3)
+    assert cf.num_rels == 9 and cf.m == 700 and cf.n == 500
+    assert cf.nnz_i == cf.nnz_j and np.array_equal(cf.indptr_j, np.arange(cf.nnz_i + 1))
+    for r in range(cf.num_rels):
+        outs = cf.indices_i[cf.indptr_i[r]:cf.indptr_i[r + 1]]
+        assert np.all(np.diff(outs) > 0) and (len(outs) == 0 or (outs[0] >= 0 and outs[-1] < cf.m))
+    assert cf.indices_j.min() >= 0 and cf.indices_j.max() < cf.n and np.all(cf.data == 1.0)
+    assert 0.4 < cf.nnz_i / (9 * 700) < 0.6

@@ -146,6 +146,39 @@ def test_hyb_spmm_matches_oracle(cuda_device, feat, parts):
     close(y, refimpl.spmm_f64(c.indptr, c.indices, c.data, x, c.m, c.n).astype(np.float32))
 
 
+def test_hyb_spmm_full_size_graph_properties(cuda_device):
+    # the bench workload at full size (169,343 nodes), checked through properties that need no CPU
+    # pass over it: the hyb product equals the CSR product of the same matrix, the operator is
+    # linear in X, and a sample of rows matches the oracle
+    c = dg.csr_powerlaw(seed=0)
+    feat = 64
+    d = cuda_device
+    x1 = dev(dg.dense_operand(1, c.n, feat), d)
+    x2 = dev(dg.dense_operand(2, c.n, feat), d)
+    _, devb = hyb_device_buckets(c, 1, BK10, d)
+
+    def hyb(x):
+        y = torch.zeros(c.m * feat, device=d)
+        ops.hyb_spmm(*ops.hyb_args(x, y, devb, feat, 0))
+        return y
+
+    y1, y2 = hyb(x1), hyb(x2)
+    y12 = hyb(2.0 * x1 - 0.5 * x2)
+    ycsr = torch.zeros(c.m * feat, device=d)
+    ops.csrmm(dev(c.data, d), x1.reshape(-1), ycsr, dev(c.indptr, d), dev(c.indices, d))
+    torch.cuda.synchronize()
+    torch.testing.assert_close(y1, ycsr, rtol=RTOL, atol=ATOL)
+    torch.testing.assert_close(y12, 2.0 * y1 - 0.5 * y2, rtol=RTOL, atol=4 * ATOL)
+    rows = np.random.default_rng(0).choice(c.m, size=2000, replace=False)
+    rows = np.concatenate([rows, np.argsort(np.diff(c.indptr))[-5:]])  # and the five longest rows
+    x1h = x1.cpu().numpy()
+    y1h = y1.cpu().numpy().reshape(c.m, feat)
+    for r in rows:
+        sl = slice(c.indptr[r], c.indptr[r + 1])
+        want = (c.data[sl, None].astype(np.float64) * x1h[c.indices[sl]]).sum(0)
+        np.testing.assert_allclose(y1h[r], want, rtol=RTOL, atol=ATOL)
+
+
 @pytest.mark.parametrize("feat,buckets,parts", [(8, [1, 3, 5], 1), (20, [2, 7], 3), (33, [1, 2, 4], 2),
                                                 (640, [4, 64], 1), (1, [1, 2], 1)])
 def test_hyb_spmm_odd_shapes(cuda_device, feat, buckets, parts):

@@ -347,6 +347,38 @@ def test_sddmm_operands_not_32_byte_aligned(cuda_device):
     close(out, orc.sddmm(a, b, c.indptr, c.indices, c.m, c.n, feat), atol=ATOL * 2)
 
 
+def test_sddmm_full_size_graph_properties(cuda_device):
+    # config 3 at full size (232,965 nodes, about 117 M stored positions): sampled positions
+    # against float64 dot products (first, last, and the rows around the longest one included),
+    # and linearity in the row-side operand
+    c = dg.csr_lognormal(seed=0)
+    feat = 32
+    d = cuda_device
+    a1 = dg.dense_operand(1, c.m, feat)
+    b = dg.dense_operand(2, c.n, feat)
+    ip, ix = dev(c.indptr, d), dev(c.indices, d)
+    bd = dev(b.reshape(-1), d)
+
+    def run(a):
+        out = torch.empty(c.nnz, device=d)
+        ops.sddmm(dev(a.reshape(-1), d), bd, out, ip, ix)
+        return out
+
+    o1 = run(a1)
+    a2 = dg.dense_operand(3, c.m, feat)
+    o2 = run(a2)
+    o12 = run((1.5 * a1 - 2.0 * a2).astype(np.float32))
+    torch.cuda.synchronize()
+    torch.testing.assert_close(o12, 1.5 * o1 - 2.0 * o2, rtol=RTOL, atol=8 * ATOL)
+    rng = np.random.default_rng(0)
+    pos = np.concatenate([rng.integers(0, c.nnz, size=20000), [0, c.nnz - 1]])
+    longest = int(np.argmax(np.diff(c.indptr)))
+    pos = np.concatenate([pos, np.arange(c.indptr[longest], min(c.nnz, c.indptr[longest] + 300))])
+    rows = np.searchsorted(c.indptr, pos, side="right") - 1
+    want = np.einsum("ij,ij->i", a1[rows].astype(np.float64), b[c.indices[pos]].astype(np.float64))
+    np.testing.assert_allclose(o1.cpu().numpy()[pos], want, rtol=RTOL, atol=ATOL)
+
+
 def test_edge_to_row_bit_exact(cuda_device):
     g = np.load(os.path.join(GOLD, "edge_to_row.npz"))
     c = dg.csr_lognormal(n=5000, mu=2.0, sigma=1.5, max_deg=3000, seed=7)

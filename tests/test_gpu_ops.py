@@ -495,6 +495,15 @@ def test_rgms_larger_graph_eager_and_captured(cuda_device):
     close(y, want, atol=ATOL * 8)
 
 
+def test_rgms_config5_full_size(cuda_device):
+    # 100,000 nodes, 46 relations, 1.5 M edges, feat 64: the whole result against the oracle
+    cf = dg.csf_relational(seed=0)
+    x = dg.dense_operand(1, cf.n, 64)
+    w = dg.relation_weights(2, cf.num_rels, 64)
+    want = oracle_rgms(cf, x, w)
+    close(run_rgms(cf, x, w, cuda_device), want, atol=ATOL * 8)
+
+
 def test_rgms_accumulates_into_y(cuda_device):
     cf = dg.csf_relational(n=400, num_rels=4, num_edges=3000, seed=6)
     x = dg.dense_operand(7, cf.n, 64)

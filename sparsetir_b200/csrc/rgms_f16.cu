@@ -870,12 +870,14 @@ int run(const BucketTable& tb, const __half* w, const __half* x, OutT* y, int m,
   if (tc_shape && (path == 0 || path == 3 || path == 4) && tb.nb == 1 && tb.width[0] == 1 && aligned16(x)) {
     // one bucket, one column per row: no Z array.  Scratch: the relation ranges, a flag, and —
     // for the reduction-free form — the (destination, relation) -> source map.
-    // The reduction-free form re-reads a slice of W_r per (destination tile, relation), which
-    // costs more than the reductions it saves unless the slice is small and Y is float32
-    // (measured on 100,000 points x 27 offsets: 64->128 float32 138 us against 187 us, but
-    // 128->128 211 against 197 us and 207 against 153 us with a float16 Y): by default it is
-    // tried for feat_in = 64 and a float32 Y only.
-    const bool os_pays = path == 4 || (feat_in == kKC && sizeof(OutT) == 4);
+    // The reduction-free form's time grows with feat_in (steps per tile, bound by the thread that
+    // issues the MMAs) and hardly with feat_out; the form with reductions grows with the bytes
+    // added to Y.  Measured on 100,000 points x 27 offsets (us, reduction-free / reductions):
+    // float32 Y 64->64 122/108, 64->128 138/188, 64->256 171/428, 128->128 211/197,
+    // 128->256 266/480, 256->256 476/546, 128->64 199/123; float16 Y 64->64 119/85,
+    // 64->128 132/142, 64->256 166/260, 128->256 254/282, 256->256 454/321.  By default it is
+    // tried when feat_out >= 2 * feat_in.
+    const bool os_pays = path == 4 || feat_out >= 2 * feat_in;
     const bool try_os = (path == 0 || path == 4) && os_pays && num_rels <= kOsMaxRels &&
                         static_cast<long long>(m) * num_rels < (1ll << 30);
     const size_t rb1 = (static_cast<size_t>(num_ranges + 1) * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);

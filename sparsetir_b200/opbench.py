@@ -383,7 +383,7 @@ def bench_rgms_f16(device, peaks, flush) -> dict:
     """fp16 RGMS with rectangular weights on ELL3D buckets: (a) config 5's graph in buckets of
     1..32 columns, 64 -> 64; (b) the shape the sparse convolution driver builds — 27 relations
     (kernel offsets), every (input, output) pair its own ELL row (buckets = [1]), unit values —
-    at 64 -> 128 and 128 -> 128 channels on 100,000 points with 1.6 M pairs."""
+    at 64 -> 128, 64 -> 256 and 128 -> 128 channels on 100,000 points with 1.6 M pairs."""
     from . import format as fmt
     dv = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)  # noqa: E731
     out = {"workload": "rgms_ell3d_f16", "cases": {}}
@@ -420,6 +420,7 @@ def bench_rgms_f16(device, peaks, flush) -> dict:
     one("config5_graph_buckets_1_32_64x64", cf, [1, 2, 4, 8, 16, 32], 32, 64, 64, 20)
     conv = dg.sparse_conv_pairs(seed=1)  # 100,000 points, 27 offsets, about 1.6 M pairs, none repeated
     one("sparse_conv_27_offsets_64x128", conv, [1], 1, 64, 128, 20)
+    one("sparse_conv_27_offsets_64x256", conv, [1], 1, 64, 256, 20)
     one("sparse_conv_27_offsets_128x128", conv, [1], 1, 128, 128, 20)
     one("sparse_conv_27_offsets_128x128_f16_out", conv, [1], 1, 128, 128, 20, torch.float16)
     return out

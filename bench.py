@@ -130,7 +130,7 @@ def reference_arm(args, rank, world):
     g = dg.csr_powerlaw(seed=0)
     xs = {f: dg.dense_operand(100 + f, g.n, f) for f in FEATS}
     ys = {f: np.zeros((g.m, f), np.float32) for f in FEATS}
-    cores = orc.num_threads()
+    cores = orc.use_all_cores()
     flops = sum(2.0 * g.nnz * f for f in FEATS)
 
     def step():
@@ -429,7 +429,7 @@ def ours_arm(args, rank, world, local_rank):
     # ---- CPU baseline on the host cores (bounded sample)
     cpu = None
     if world == 1 or True:
-        cores = orc.num_threads()
+        cores = orc.use_all_cores()
         ys = {f: np.zeros((g.m, f), np.float32) for f in FEATS}
         xs = {f: x_host[f].numpy() for f in FEATS}
 

@@ -61,6 +61,14 @@ def num_threads() -> int:
     return int(lib().oracle_num_threads())
 
 
+def use_all_cores() -> int:
+    """Makes the ``omp`` entry points use every core this process may run on, whatever
+    OMP_NUM_THREADS says (launchers such as torchrun set it to 1); returns the thread count."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().oracle_set_num_threads(int(n))
+    return num_threads()
+
+
 # ----------------------------------------------------------------- formats
 def column_part_hyb(num_rows: int, num_cols: int, indptr, indices, num_col_parts: int,
                     buckets: Sequence[int], with_pos: bool = False):

@@ -67,6 +67,15 @@ static int upper_bound_int(const int32_t* a, int n, int key) {
   return lo;
 }
 
+/* torchrun exports OMP_NUM_THREADS=1 to its workers: the timed CPU legs ask for the cores explicitly */
+ORACLE_API void oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 ORACLE_API int oracle_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -61,11 +61,13 @@ def test_column_part_hyb_many_threads_large():
     _assert_hyb_equal(got, want, 2, len(bk))
 
 
-@pytest.mark.parametrize("tag", ["a", "b", "c"])
+@pytest.mark.parametrize("tag", ["a", "b", "c", "d", "e", "f"])
 def test_column_part_hyb_golden(tag):
+    # fixtures written by the reference test's own scipy_column_part_hyb (see their `source` entry)
     g = np.load(os.path.join(GOLD, f"hyb_{tag}.npz"))
     parts, buckets = int(g["parts"]), [int(b) for b in g["buckets"]]
-    rows, cols, mask = fmt.column_part_hyb(1000, 1000, g["indptr"], g["indices"], parts, buckets)
+    rows, cols, mask = fmt.column_part_hyb(int(g["m"]), int(g["n"]), g["indptr"], g["indices"],
+                                           parts, buckets)
     for p in range(parts):
         for b in range(len(buckets)):
             k = p * len(buckets) + b

@@ -86,11 +86,39 @@ typedef union {
  * include/tvm/runtime/c_runtime_api.h:195). */
 SPARSETIR_API const char* sparsetir_get_last_error(void);
 
-/* Stream used by later calls from ANY thread for `device_id` (TVMSetStream,
- * include/tvm/runtime/c_runtime_api.h:496; src/runtime/cuda/cuda_device_api.cc:209-211).
- * `stream` is a cudaStream_t; NULL selects the legacy default stream. */
+/* Stream used by later packed calls of the CALLING THREAD for `device_id` (TVMSetStream,
+ * include/tvm/runtime/c_runtime_api.h:496; the reference keeps it in the thread-local
+ * CUDAThreadEntry, src/runtime/cuda/cuda_device_api.cc:209-211, read at launch time,
+ * src/runtime/cuda/cuda_module.cc:170).  `stream` is a cudaStream_t; NULL selects the legacy
+ * default stream.  A thread that never called sparsetir_set_stream for a device uses the
+ * process-wide default set with sparsetir_set_default_stream (initially the legacy default
+ * stream).  sparsetir_get_stream returns what the calling thread's next packed call would use.
+ * The `*_raw` entry points take their stream as an argument and ignore both. */
 SPARSETIR_API int sparsetir_set_stream(int device_id, void* stream);
+SPARSETIR_API int sparsetir_set_default_stream(int device_id, void* stream);
 SPARSETIR_API void* sparsetir_get_stream(int device_id);
+
+/* Scratch memory (no counterpart in the reference, whose generated functions allocate through
+ * TVMBackendAllocWorkspace, include/tvm/runtime/c_backend_api.h:84).  Some operators keep an
+ * intermediate in device memory owned by the library: one grow-only buffer (and one small buffer
+ * of counters) per (device, stream), allocated by the first call that needs it and enlarged by a
+ * call that needs more — cudaMalloc / cudaFree inside that call, which synchronise the device and
+ * fail while the stream is being captured into a CUDA graph.  A caller that wants neither reserves
+ * the buffers up front: after sparsetir_reserve_workspace(device, stream, s, c) no call on that
+ * stream that needs at most s scratch bytes and c counter bytes allocates, synchronises or frees.
+ * The *_workspace queries give the sizes an operator call needs (upper bounds). */
+SPARSETIR_API int sparsetir_reserve_workspace(int device_id, void* stream, size_t scratch_bytes,
+                                              size_t counter_bytes);
+
+/* Deep checks of the index arrays (no counterpart in the reference, whose host stub checks
+ * shapes, dtypes and devices only, src/tir/transforms/arg_binder.cc:152-282).  When switched on —
+ * sparsetir_set_validate(1), or SPARSETIR_VALIDATE=1 in the environment when the library is first
+ * used — every operator call first verifies on the device that its row pointers start at 0, never
+ * decrease and end at the number of stored entries, and that every column / row id lies inside its
+ * range; a violation makes the call return -1 with a message naming the array and the position,
+ * before any kernel that would follow the bad index runs.  Costs a pass over the index arrays and
+ * a stream synchronisation per call; not usable while the stream is being captured. */
+SPARSETIR_API int sparsetir_set_validate(int on);
 
 /* Library version and the compute capability the kernels were compiled for (100). */
 SPARSETIR_API int sparsetir_version(void);
@@ -119,16 +147,21 @@ SPARSETIR_API int sparsetir_csrmm(SPARSETIR_PACKED_ARGS);
  * args: (b f32[n*feat], c f32[m*feat], {w_q f32[nrows_q*width_q], rows_q i32[nrows_q],
  *        cols_q i32[nrows_q*width_q]} x K, feat_size [, flags])
  * The bucket width is len(cols_q)/len(rows_q); buckets with no rows are accepted.
- * flags (bit field, default 0 = reference behaviour: the caller has zero-filled C,
- * examples/spmm/bench_spmm.py:206):
+ * Without SPARSETIR_HYB_ALL_ATOMIC every output row that occurs in a bucket is WRITTEN by exactly
+ * one writer (pieces of wide and split rows are added in a fixed order first), so results are
+ * bit-identical from call to call and C needs no clearing between calls; rows that occur in no
+ * bucket are left as the caller filled them (zero, examples/spmm/bench_spmm.py:206).  A row id
+ * may repeat only in consecutive ELL rows of the widest bucket, as ColumnPartHyb emits split rows
+ * (src/sparse/format.cc:110-116); any other repetition needs SPARSETIR_HYB_ALL_ATOMIC.
+ * flags (bit field, default 0):
  *   SPARSETIR_HYB_ZERO_C       the call zero-fills all of C first;
- *   SPARSETIR_HYB_REARM        the call first zeroes only the C rows that buckets accumulate
- *                              into atomically, so that repeated calls on a C that was
- *                              zero-filled once stay correct;
- *   SPARSETIR_HYB_ALL_ATOMIC   every bucket accumulates atomically (needed when the same row
- *                              occurs in several buckets, i.e. with more than one column
- *                              partition); without it only the LAST bucket triple of the
- *                              argument list is treated as holding split rows.
+ *   SPARSETIR_HYB_REARM        with ALL_ATOMIC: the call zero-fills C first, so that repeated
+ *                              calls stay correct; without ALL_ATOMIC nothing needs re-arming
+ *                              (the fallback kernels for odd shapes clear the rows they add to);
+ *   SPARSETIR_HYB_ALL_ATOMIC   every contribution is added atomically into C, which the caller
+ *                              has zero-filled (needed when the same row occurs in several
+ *                              buckets, i.e. with more than one column partition).
+ * Uses library scratch memory for split rows (see sparsetir_reserve_workspace).
  * Replaces the function built by examples/spmm/bench_spmm.py:116-199 (argument list :207-222). */
 SPARSETIR_API int sparsetir_hyb_spmm(SPARSETIR_PACKED_ARGS);
 #define SPARSETIR_HYB_ZERO_C 1
@@ -251,6 +284,11 @@ typedef struct {
 SPARSETIR_API int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirEllBucket* buckets,
                                          int num_buckets, int m, int n, int feat, int flags,
                                          int device_id, void* stream);
+/* Scratch and counter bytes sparsetir_hyb_spmm(_raw) uses for this bucket table and feature size
+ * (non-zero only when the widest bucket may hold rows split into several ELL rows). */
+SPARSETIR_API int sparsetir_hyb_spmm_workspace(const SparsetirEllBucket* buckets, int num_buckets,
+                                               int feat, size_t* scratch_bytes,
+                                               size_t* counter_bytes);
 SPARSETIR_API int sparsetir_sddmm_raw(const float* a, const float* b, float* c,
                                       const int32_t* indptr, const int32_t* indices,
                                       const float* scale, int m, int n, int feat, int nnz,
@@ -327,7 +365,9 @@ SPARSETIR_API int sparsetir_rgms_ell3d_f16_raw(const void* w, const void* x, voi
  * lives in a fixed 32 MiB array inside the library instead of an allocated scratch buffer:
  *   - feat must be 64 and nnz_i at most 131072; anything else is refused with an error;
  *   - all calls on one device share that array: calls that overlap on the GPU race, order them;
- *   - the first call on a device fetches the array's address; make it before any stream capture. */
+ *   - the first call on a device fetches the array's address, which is also when the 32 MiB are
+ *     taken on that device: make it at start-up, while memory is free, and before any stream
+ *     capture. */
 SPARSETIR_API int sparsetir_rgms_noalloc(const float* a, const float* w, const float* x, float* y,
                                          const int32_t* indptr_i, const int32_t* indices_i,
                                          const int32_t* indptr_j, const int32_t* indices_j, int m,

@@ -88,7 +88,12 @@ _f32p = ctypes.POINTER(ctypes.c_float)
 PLAIN_SYMBOLS = {
     "sparsetir_get_last_error": (ctypes.c_char_p, []),
     "sparsetir_set_stream": (_i, [_i, _vp]),
+    "sparsetir_set_default_stream": (_i, [_i, _vp]),
     "sparsetir_get_stream": (_vp, [_i]),
+    "sparsetir_reserve_workspace": (_i, [_i, _vp, ctypes.c_size_t, ctypes.c_size_t]),
+    "sparsetir_hyb_spmm_workspace": (_i, [ctypes.POINTER(EllBucket), _i, _i,
+                                          ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]),
+    "sparsetir_set_validate": (_i, [_i]),
     "sparsetir_version": (_i, []),
     "sparsetir_sm_arch": (_i, []),
     "sparsetir_tc_timeouts": (_i, [_i, ctypes.POINTER(ctypes.c_uint)]),

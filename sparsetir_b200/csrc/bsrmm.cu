@@ -76,6 +76,7 @@ extern "C" int sparsetir_bsrmm_raw(const void* a_f16, const void* b_f16, float* 
     return fail("sparsetir_bsrmm: null pointer argument");
   if (use_device(device_id) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (validate_enabled() && validate_csr("sparsetir_bsrmm", indptr, nb, indices, nnzb, mb, st) != 0) return -1;
   const __half* a = static_cast<const __half*>(a_f16);
   const __half* b = static_cast<const __half*>(b_f16);
   int rc = bsrmm_tc_launch(a, b, c, indptr, indices, nb, mb, nnzb, blk, feat, st);

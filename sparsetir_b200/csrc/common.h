@@ -32,6 +32,22 @@ cudaStream_t stream_for(int device_id);
 // device once.
 void* workspace(int device_id, cudaStream_t stream, size_t bytes);
 
+// The same for counters and flags that kernels find at zero and leave at zero: the buffer is
+// cleared (on `stream`) when it is allocated, and every kernel that uses it restores the zeros
+// before it ends, so steady-state calls neither allocate nor clear.
+void* zeroed_workspace(int device_id, cudaStream_t stream, size_t bytes);
+
+// Deep checks of index arrays before a launch (validate.cu): enabled by SPARSETIR_VALIDATE=1 or
+// sparsetir_set_validate(1).  Each returns 0, or -1 after recording which array is wrong where;
+// they synchronise `st`.  nnz < 0 skips the check of the last row pointer.
+bool validate_enabled();
+int validate_indptr(const char* op, const char* what, const int32_t* indptr, long long rows,
+                    long long nnz, cudaStream_t st);
+int validate_range(const char* op, const char* what, const int32_t* ids, long long count,
+                   long long bound, cudaStream_t st);
+int validate_csr(const char* op, const int32_t* indptr, long long rows, const int32_t* indices,
+                 long long nnz, long long cols, cudaStream_t st);
+
 constexpr int kNumSMs = 148;  // B200
 
 inline int ceil_div(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }

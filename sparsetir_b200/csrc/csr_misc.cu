@@ -156,6 +156,7 @@ extern "C" int sparsetir_csr_reduce_raw(const float* a, float* b, const int32_t*
   if (!b || !indptr || (nnz > 0 && !a)) return fail("sparsetir_csr_reduce: null pointer argument");
   if (use_device(device_id) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (validate_enabled() && validate_indptr("sparsetir_csr_reduce", "indptr", indptr, n, nnz, st) != 0) return -1;
   if (static_cast<double>(nnz) / n >= 24.0) {
     csr_reduce_kernel<32><<<ceil_div(n, kThreads / 32), kThreads, 0, st>>>(a, b, indptr, n);
   } else {
@@ -173,6 +174,7 @@ extern "C" int sparsetir_sparse_softmax_raw(const float* a, float* b, const int3
   if (!a || !b || !indptr) return fail("sparsetir_sparse_softmax: null pointer argument");
   if (use_device(device_id) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (validate_enabled() && validate_indptr("sparsetir_sparse_softmax", "indptr", indptr, n, nnz, st) != 0) return -1;
   if (static_cast<double>(nnz) / n >= 24.0) {
     sparse_softmax_kernel<32, 16><<<ceil_div(n, kThreads / 32), kThreads, 0, st>>>(a, b, indptr, n);
   } else {

@@ -303,6 +303,7 @@ int csrmm_impl(const float* a, const float* b, float* c, const int32_t* indptr, 
     return fail("sparsetir_csrmm: null pointer argument");
   if (use_device(device_id) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (validate_enabled() && validate_csr("sparsetir_csrmm", indptr, m, indices, nnz, n, st) != 0) return -1;
   const bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
   if (vec4 && static_cast<long long>(feat) * 4 < (1ll << 32) &&
       static_cast<long long>(m) * feat * 4 < (1ll << 32) * 1024) {

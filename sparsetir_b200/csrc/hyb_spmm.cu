@@ -12,14 +12,15 @@
 //    bucket.  Equal-sized items keep every SM busy until the end of the launch; the reference
 //    equalises per block instead (8 * maxBucket slots per block, bench_spmm.py:187-189).
 //    Wide buckets are scheduled first.
-//  - whether an ELL row must be accumulated atomically is decided from the data: pieces of a
-//    chunked wide ELL row, and ELL rows whose row id equals a neighbour's id in the same array
-//    (a row that the format split into several ELL rows, src/sparse/format.cc:110-116), are
-//    reduced with one 16-byte vector atomic per lane; every other ELL row is the only writer of
-//    its output row and is stored.  The reference marks whole buckets atomic
-//    (bench_spmm.py:170,174-177).  With several column partitions the same output row appears
-//    in several arrays, which the kernel cannot see; the caller says so with
-//    SPARSETIR_HYB_ALL_ATOMIC.
+//  - the reference marks whole buckets atomic (bench_spmm.py:170,174-177).  Here the main (lean)
+//    kernel gives every output row one writer: the pieces of a wide ELL row meet in shared memory,
+//    the ELL rows of a row that the format split (src/sparse/format.cc:110-116: consecutive ELL
+//    rows of the widest bucket repeating the row id) meet in a scratch buffer and are added in
+//    order by the last one to finish — no atomics on the output, the same bits on every run.
+//    The fallback kernels for odd shapes decide from the data instead: pieces of a chunked wide
+//    ELL row and ELL rows whose id equals a neighbour's are added with vector atomics.
+//    With several column partitions the same output row appears in several arrays, which the
+//    kernels cannot see; the caller says so with SPARSETIR_HYB_ALL_ATOMIC.
 #include <algorithm>
 #include <cstdlib>
 #include <vector>
@@ -49,9 +50,10 @@ struct HybTable {
   int32_t nrows[kMaxB];
   int32_t width[kMaxB];
   int32_t rows_per_item[kMaxB];    // >= 1; 1 for chunked buckets
-  int32_t chunks_per_row[kMaxB];   // 1 unless width > item_slots
+  int32_t chunks_per_row[kMaxB];   // 1 unless width > item_slots (lean kernel: sub-warps per ELL row)
   int32_t block_start[kMaxB + 1];
   int32_t row_base[kMaxB];         // buckets without a row-id array: ELL row r -> output row base + r
+  int32_t part_base[kMaxB];        // lean kernel: scratch row of ELL row 0, or -1 (bucket has no split rows)
   int32_t nb;
 };
 
@@ -160,22 +162,35 @@ hyb_spmm_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b
 
 // ---------------------------------------------------------------------------------------------
 // Lean kernel: the fast path for 16-byte aligned operands, whole feature tiles and ELL widths
-// of 1, 2, 4 or a multiple of 8 (every power-of-two bucket list).  Same work items and the
-// same results as the kernels above, but written for instruction economy — the gathers come
-// from L2 at well over 10 TB/s if, and only if, the warp spends its issue slots on loads:
-// per stored slot the loop executes one shuffle + one address + one 16-byte load, then one
-// shuffle + four FMAs; row ends sit at compile-time positions of the unrolled batch (narrow
-// rows) or are tested once per 8 slots (wide rows); row ids travel in registers with the
-// "accumulate atomically" flag in the sign bit, so a row end costs one shuffle and a store.
+// of 1, 2, 4 or a multiple of 8 (every power-of-two bucket list).  Written for instruction
+// economy — the gathers come from L2 at well over 10 TB/s if, and only if, the warp spends its
+// issue slots on loads: per stored slot the loop executes one shuffle + one address + one
+// 16-byte load, then one shuffle + four FMAs; row ends sit at compile-time positions of the
+// unrolled batch (narrow rows) or are tested once per 8 slots (wide rows); row ids travel in
+// registers with two flag bits, so a row end costs one shuffle and a store.
+//
+// Every output row has ONE writer, so results are bit-identical from run to run and nothing has
+// to be cleared between calls:
+//  - an ELL row wider than a work item is cut into equal spans, one per sub-warp of the SAME
+//    block; the partial sums meet in shared memory and are added in span order;
+//  - a row that the format split into several ELL rows (consecutive ELL rows of the widest
+//    bucket repeating the row id, src/sparse/format.cc:110-116) is reduced across blocks: each
+//    piece stores its partial sum in a scratch row of its own and counts itself in; the piece that
+//    counts in last adds all of them in ELL-row order and writes the output row.  The counter is
+//    back at zero when the launch ends.
+// With SPARSETIR_HYB_ALL_ATOMIC (several column partitions: the same row in several arrays, which
+// the kernel cannot see) every contribution is added atomically into the zero-filled output.
 // W = floats per lane: 4 (16-byte vectors) or 8 (32-byte vectors, two-wide FMAs)
-template <int LPR, int WM, int W>  // WM = 1, 2, 4: the ELL width itself; WM = 8: a multiple of 8
+constexpr int kFlagAtomic = static_cast<int>(0x80000000u);  // add atomically instead of storing
+
+// row_flag(g): flag word of ELL row g (called by the lane that will hold it)
+// row_end(acc, flag word): all lanes of the sub-warp, after the last slot of an ELL row
+template <int LPR, int WM, int W, class RowFlag, class RowEnd>  // WM = 1, 2, 4: the ELL width itself; 8: a multiple of 8
 __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
-                                          const float* __restrict__ wts,
-                                          const int32_t* __restrict__ rows, int nrows, int r0,
-                                          int nr, int nslots, int per_row,
-                                          const char* __restrict__ bl, unsigned row_bytes,
-                                          char* __restrict__ cl, bool always_atomic, int lane,
-                                          unsigned mask) {
+                                          const float* __restrict__ wts, int r0, int nr, int nslots,
+                                          int per_row, const char* __restrict__ bl,
+                                          unsigned row_bytes, int lane, unsigned mask,
+                                          RowFlag&& row_flag, RowEnd&& row_end) {
   using LV = LaneVec<W>;
   using V = typename LV::type;
   constexpr int U = (32 / W) < LPR ? (32 / W) : LPR;  // gathered rows in flight: 32 registers
@@ -186,26 +201,6 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
   static_assert(LPR % U == 0, "a batch is a whole number of chunks");
   constexpr int RPB = WM < 8 ? LPR / WM : 0;  // ELL rows that end inside one batch (narrow rows)
 
-  // row id of ELL row g of the bucket, sign bit set when it must be accumulated atomically
-  auto row_flag = [&](int g) -> int {
-    if (g >= nrows) return 0;
-    const int rid = row_id(rows, g, 0);  // a bucket without row ids has its base folded into cl
-    const bool split = is_split_row(rows, g, nrows, rid);
-    return rid | ((always_atomic || split) ? 0x80000000 : 0);
-  };
-  auto row_end = [&](V& acc, int rf) {
-    char* dst = const_cast<char*>(vec_of(cl, rf & 0x7fffffff));
-    if (rf < 0) {
-      // rows accumulated atomically were cleared by the re-arm launch, which may still be running
-      // when this kernel was started as its programmatic dependent (returns at once otherwise)
-      asm volatile("griddepcontrol.wait;" ::: "memory");
-      LV::atomic_add(dst, acc);
-    } else {
-      LV::stcs(dst, acc);  // written once: do not displace B rows in L2
-    }
-    acc = LV::zero();
-  };
-
   V acc = LV::zero();
   int c = 0, rf = 0;
   float a = 0.f;
@@ -214,9 +209,9 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
     a = __ldg(wts + lane);
   }
   if (WM < 8) {
-    if (lane < RPB) rf = row_flag(r0 + lane);   // rows ending in batch 0
+    if (lane < RPB && lane < nr) rf = row_flag(r0 + lane);   // rows ending in batch 0
   } else {
-    if (lane < nr) rf = row_flag(r0 + lane);    // all rows of the item (nr <= LPR)
+    if (lane < nr) rf = row_flag(r0 + lane);                  // all rows of the item (nr <= LPR)
   }
   int left = per_row, jrow = 0;  // wide rows only
 
@@ -227,7 +222,7 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
       cn = __ldg(cols + s0 + LPR + lane);
       an = __ldg(wts + s0 + LPR + lane);
     }
-    if (WM < 8 && s0 + LPR < nslots && lane < RPB) rfn = row_flag(r0 + (s0 + LPR) / WM + lane);
+    if (WM < 8 && lane < RPB && (s0 + LPR) / WM + lane < nr) rfn = row_flag(r0 + (s0 + LPR) / WM + lane);
     const int cnt = nslots - s0;  // live slots of this batch if < LPR
     if (cnt >= LPR) {
 #pragma unroll
@@ -285,56 +280,202 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
   }
 }
 
+// What the lean kernel needs besides the bucket table.
+struct LeanArgs {
+  const float* b;
+  float* c;
+  float* part;          // scratch rows for the pieces of split rows (same row stride as c)
+  unsigned* counters;   // [scratch rows][feature tiles], zero before and after every launch
+  int feat;
+  int all_atomic;
+};
+
+// Bits of `pred` over the LPR lanes of this thread's sub-warp, lane 0 of the sub-warp in bit 0.
+template <int LPR>
+__device__ __forceinline__ unsigned sub_ballot(unsigned mask, bool pred) {
+  const unsigned all = __ballot_sync(mask, pred);
+  if constexpr (LPR == 32) {
+    return all;
+  } else {
+    return (all >> ((threadIdx.x & 31) / LPR * LPR)) & ((1u << LPR) - 1u);
+  }
+}
+
+// The last ELL row `g` of a piece of a split row has been accumulated into `acc` by this
+// sub-warp.  A piece is the part of a run of equal row ids that lies inside one work item
+// (items hold `rpi` consecutive ELL rows; rpi = 1 for wide buckets).  Pieces are numbered in
+// ELL-row order; piece k keeps its partial sum in the scratch row of its first ELL row.
+template <int LPR, int W>
+__device__ __noinline__ void finish_split_row(typename LaneVec<W>::type acc,
+                                              const int32_t* __restrict__ rows, int nrows, int g,
+                                              int rpi, int rid, int part_base, char* pl, char* cl,
+                                              unsigned* counters, unsigned row_bytes, int lane,
+                                              unsigned mask) {
+  using LV = LaneVec<W>;
+  constexpr unsigned kFull = LPR == 32 ? 0xffffffffu : ((1u << LPR) - 1u);
+  int first = g, last = g;
+  while (true) {  // LPR ELL rows per step, backwards then forwards
+    const int idx = first - 1 - lane;
+    const unsigned bits = sub_ballot<LPR>(mask, idx >= 0 && __ldg(rows + idx) == rid);
+    const int n = bits == kFull ? LPR : __ffs(~bits) - 1;
+    first -= n;
+    if (n < LPR) break;
+  }
+  while (true) {
+    const int idx = last + 1 + lane;
+    const unsigned bits = sub_ballot<LPR>(mask, idx < nrows && __ldg(rows + idx) == rid);
+    const int n = bits == kFull ? LPR : __ffs(~bits) - 1;
+    last += n;
+    if (n < LPR) break;
+  }
+  const int item0 = first / rpi;
+  const int npieces = last / rpi - item0 + 1;
+  char* dst = cl + static_cast<unsigned long long>(static_cast<unsigned>(rid)) * row_bytes;
+  if (npieces == 1) {  // the whole run lies inside this item
+    LV::stcs(dst, acc);
+    return;
+  }
+  const int mine = max(first, g / rpi * rpi);
+  auto part_of = [&](int ell_row) -> char* {
+    return pl + static_cast<unsigned long long>(static_cast<unsigned>(part_base + ell_row)) * row_bytes;
+  };
+  LV::stcg(part_of(mine), acc);
+  __threadfence();
+  __syncwarp(mask);
+  unsigned* counter = counters + static_cast<size_t>(part_base + first) * gridDim.y + blockIdx.y;
+  unsigned seen = 0;
+  if (lane == 0) seen = atomicAdd(counter, 1u);
+  seen = __shfl_sync(mask, seen, 0, LPR);
+  if (seen + 1 != static_cast<unsigned>(npieces)) return;
+  // last piece to arrive: every other piece's partial sum is visible
+  if (lane == 0) *counter = 0u;
+  __threadfence();
+  typename LV::type sum = LV::ldcg(part_of(first));
+  for (int k = 1; k < npieces; ++k) LV::add(sum, LV::ldcg(part_of((item0 + k) * rpi)));
+  LV::stcs(dst, sum);
+}
+
+// A narrow item of the widest bucket that holds ELL rows of a split row (rare: only bucket lists
+// whose last width is small put split rows into a narrow bucket).  Plain loop, one ELL row at a
+// time; consecutive ELL rows of the same output row inside the item are added up first.
+template <int LPR, int W>
+__device__ __noinline__ void split_item(const int32_t* __restrict__ cols, const float* __restrict__ wts,
+                                        const int32_t* __restrict__ rows, int nrows, int r0, int nr,
+                                        int width, int rpi, int part_base, const char* __restrict__ bl,
+                                        char* pl, char* cl, unsigned* counters, unsigned row_bytes,
+                                        int lane, unsigned mask) {
+  using LV = LaneVec<W>;
+  typename LV::type acc = LV::zero();
+  for (int j = 0; j < nr; ++j) {
+    const int g = r0 + j;
+    for (int s = 0; s < width; ++s) {
+      const int col = __ldg(cols + j * width + s);
+      const float a = __ldg(wts + j * width + s);
+      LV::fma(acc, a, LV::ldg(bl + static_cast<unsigned long long>(static_cast<unsigned>(col)) * row_bytes));
+    }
+    const int rid = __ldg(rows + g);
+    const bool next_same = g + 1 < nrows && __ldg(rows + g + 1) == rid;
+    if (next_same && j + 1 < nr) continue;  // the next ELL row of this item continues the row
+    if (next_same || (g > 0 && __ldg(rows + g - 1) == rid))
+      finish_split_row<LPR, W>(acc, rows, nrows, g, rpi, rid, part_base, pl, cl, counters, row_bytes, lane, mask);
+    else
+      LV::stcs(cl + static_cast<unsigned long long>(static_cast<unsigned>(rid)) * row_bytes, acc);
+    acc = LV::zero();
+  }
+}
+
 template <int LPR, int W>
 __global__ void __launch_bounds__(kThreads, 8)
-hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const float* __restrict__ b,
-                     float* __restrict__ c, int feat, int all_atomic) {
+hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const __grid_constant__ LeanArgs la) {
+  using LV = LaneVec<W>;
+  using V = typename LV::type;
   constexpr int SUBS = kThreads / LPR;
-  constexpr int ITEM = lean_item_slots(LPR, W);
+  __shared__ __align__(32) float s_part[SUBS][LPR * W];  // wide rows: partial sums of the spans
   const int lane = threadIdx.x % LPR;
   const int sub = threadIdx.x / LPR;
   const unsigned mask = group_mask<LPR>();
   const int q = find_bucket(tb, blockIdx.x);
   const int width = tb.width[q], nrows = tb.nrows[q];
-  const int rpi = tb.rows_per_item[q], cpr = tb.chunks_per_row[q];
-  const long long item = static_cast<long long>(blockIdx.x - tb.block_start[q]) * SUBS + sub;
-  long long r0l;
-  int nslots, per_row, nr;
-  size_t first;
-  if (cpr == 1) {
-    r0l = item * rpi;
-    if (r0l >= nrows) return;
-    nr = static_cast<int>(min(static_cast<long long>(nrows), r0l + rpi) - r0l);
-    nslots = nr * width;
-    per_row = width;
-    first = static_cast<size_t>(r0l) * width;
-  } else {
-    r0l = item / cpr;
-    if (r0l >= nrows) return;
-    const int s0 = static_cast<int>(item % cpr) * ITEM;
-    nr = 1;
-    nslots = min(ITEM, width - s0);
-    per_row = nslots;
-    first = static_cast<size_t>(r0l) * width + s0;
-  }
-  const int r0 = static_cast<int>(r0l);
-  const unsigned stride = static_cast<unsigned>(feat) * 4u;  // bytes per dense row
+  const int rpi = tb.rows_per_item[q], spr = tb.chunks_per_row[q];
+  const int part_base = tb.part_base[q];
+  const unsigned stride = static_cast<unsigned>(la.feat) * 4u;  // bytes per dense row
   const unsigned off = (blockIdx.y * LPR + lane) * (W * 4u);  // this lane's piece of the tile
-  const char* bl = reinterpret_cast<const char*>(b) + off;
-  char* cl = reinterpret_cast<char*>(c) + off;
-  const int32_t* cols = tb.cols[q] + first;
-  const float* wts = tb.w[q] + first;
+  const char* bl = reinterpret_cast<const char*>(la.b) + off;
+  char* cl = reinterpret_cast<char*>(la.c) + off;
+  char* pl = reinterpret_cast<char*>(la.part) + off;
   const int32_t* rows = tb.rows[q];
   if (rows == nullptr) cl += static_cast<size_t>(tb.row_base[q]) * stride;
-  const bool always_atomic = all_atomic || cpr > 1;
-  if (width == 1)
-    lean_item<LPR, 1, W>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
-  else if (width == 2)
-    lean_item<LPR, 2, W>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
-  else if (width == 4)
-    lean_item<LPR, 4, W>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
-  else
-    lean_item<LPR, 8, W>(cols, wts, rows, nrows, r0, nr, nslots, per_row, bl, stride, cl, always_atomic, lane, mask);
+  const bool all_atomic = la.all_atomic != 0;
+  auto y_of = [&](int rid) -> char* {
+    return cl + static_cast<unsigned long long>(static_cast<unsigned>(rid)) * stride;
+  };
+
+  if (spr == 1) {
+    // ---- narrow bucket: a sub-warp owns rpi whole ELL rows
+    const long long item = static_cast<long long>(blockIdx.x - tb.block_start[q]) * SUBS + sub;
+    const long long r0l = item * rpi;
+    if (r0l >= nrows) return;
+    const int r0 = static_cast<int>(r0l);
+    const int nr = min(nrows, r0 + rpi) - r0;
+    const size_t first = static_cast<size_t>(r0) * width;
+    if (!all_atomic && part_base >= 0) {
+      // the widest bucket: an item that holds an ELL row of a split row takes the careful path
+      bool any = false;
+      for (int j = lane; j < nr; j += LPR) any = any || is_split_row(rows, r0 + j, nrows, __ldg(rows + r0 + j));
+      if (sub_ballot<LPR>(mask, any) != 0u) {
+        split_item<LPR, W>(tb.cols[q] + first, tb.w[q] + first, rows, nrows, r0, nr, width, rpi, part_base,
+                           bl, pl, cl, la.counters, stride, lane, mask);
+        return;
+      }
+    }
+    auto row_flag = [&](int g) -> int {
+      // a bucket without row ids has its base folded into cl
+      return row_id(rows, g, 0) | (all_atomic ? kFlagAtomic : 0);
+    };
+    auto row_end = [&](V& acc, int rf) {
+      if (rf < 0) LV::atomic_add(y_of(rf & 0x7fffffff), acc);
+      else LV::stcs(y_of(rf), acc);  // written once: do not displace B rows in L2
+      acc = LV::zero();
+    };
+    const int32_t* cols = tb.cols[q] + first;
+    const float* wts = tb.w[q] + first;
+    const int nslots = nr * width;
+    if (width == 1) lean_item<LPR, 1, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end);
+    else if (width == 2) lean_item<LPR, 2, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end);
+    else if (width == 4) lean_item<LPR, 4, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end);
+    else lean_item<LPR, 8, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end);
+    return;
+  }
+
+  // ---- wide bucket: spr sub-warps of this block share one ELL row, each takes one span of it
+  const int rpb = SUBS / spr;  // ELL rows per block
+  const int part = sub % spr;
+  const long long rl = static_cast<long long>(blockIdx.x - tb.block_start[q]) * rpb + sub / spr;
+  const bool live = rl < nrows;
+  const int r = live ? static_cast<int>(rl) : 0;
+  const int span = ((width + spr - 1) / spr + 7) & ~7;  // slots per span, a multiple of 8
+  V total = LV::zero();
+  if (live && part * span < width) {
+    const int s0 = part * span;
+    const int nslots = min(span, width - s0);
+    const size_t first = static_cast<size_t>(r) * width + s0;
+    auto no_flag = [](int) -> int { return 0; };
+    auto keep = [&](V& acc, int) { total = acc; };
+    lean_item<LPR, 8, W>(tb.cols[q] + first, tb.w[q] + first, r, 1, nslots, nslots, bl, stride, lane, mask,
+                         no_flag, keep);
+  }
+  if (part != 0) LV::sts(&s_part[sub][lane * W], total);
+  __syncthreads();
+  if (!live || part != 0) return;
+  for (int k = 1; k < spr; ++k) LV::add(total, LV::lds(&s_part[sub + k][lane * W]));
+  const int rid = row_id(rows, r, 0);
+  if (all_atomic) {
+    LV::atomic_add(y_of(rid), total);
+  } else if (part_base >= 0 && is_split_row(rows, r, nrows, rid)) {
+    finish_split_row<LPR, W>(total, rows, nrows, r, 1, rid, part_base, pl, cl, la.counters, stride, lane, mask);
+  } else {
+    LV::stcs(y_of(rid), total);
+  }
 }
 
 // The main kernel for 16-byte aligned operands: B rows are staged through per-lane rings in
@@ -437,15 +578,12 @@ hyb_spmm_async_kernel(const __grid_constant__ HybTable tb, const float* __restri
                                           valid, ring, acc, on_done);
 }
 
-// Zeroes the output rows that the main kernel accumulates into atomically (chunked wide rows
-// and split rows), so that repeated calls on the same C stay correct without a full memset.
+// Fallback kernels only: zeroes the output rows that they accumulate into atomically (chunked wide
+// rows and split rows), so that repeated calls on the same C stay correct without a full memset.
 // One thread inspects one ELL row (coalesced reads of the row ids); the rows that need clearing
 // are rare, and each is then cleared by the whole warp.
 __global__ void __launch_bounds__(kThreads)
 hyb_rearm_kernel(const __grid_constant__ HybTable tb, float* __restrict__ c, int feat) {
-  // the SpMM launch that follows may start now (programmatic dependent launch): it synchronises
-  // with this grid's completion only before its first atomic accumulation
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const int q = find_bucket(tb, blockIdx.x);
   const int nrows = tb.nrows[q];
   const int32_t* __restrict__ rows = tb.rows[q];
@@ -469,11 +607,47 @@ hyb_rearm_kernel(const __grid_constant__ HybTable tb, float* __restrict__ c, int
   }
 }
 
+// Scratch (bytes) the lean kernel may use for the pieces of split rows before it falls back to
+// atomic accumulation; SPARSETIR_HYB_SCRATCH_MB overrides the default of 1 GiB.
+size_t hyb_scratch_limit() {
+  static const size_t v = [] {
+    const char* e = std::getenv("SPARSETIR_HYB_SCRATCH_MB");
+    const long mb = e ? std::atol(e) : -1;
+    return static_cast<size_t>(mb >= 0 ? mb : 1024) << 20;
+  }();
+  return v;
+}
+
 void plan_items(HybTable& tb, int item) {
   for (int q = 0; q < tb.nb; ++q) {
     tb.rows_per_item[q] = std::max(1, item / tb.width[q]);
     tb.chunks_per_row[q] = tb.width[q] > item ? ceil_div(tb.width[q], item) : 1;
   }
+}
+
+// Lean kernel: a bucket wider than an item gives each ELL row a power-of-two number of sub-warps of
+// one block (all of them from SUBS * item slots on; a sub-warp then walks a longer span).
+void plan_items_lean(HybTable& tb, int item, int subs) {
+  for (int q = 0; q < tb.nb; ++q) {
+    tb.rows_per_item[q] = std::max(1, item / tb.width[q]);
+    int spr = 1;
+    while (spr < subs && spr * item < tb.width[q]) spr *= 2;
+    tb.chunks_per_row[q] = spr;
+    if (spr > 1) tb.rows_per_item[q] = 1;
+  }
+}
+
+long long plan_blocks_lean(HybTable& tb, int subs) {
+  long long blocks = 0;
+  for (int q = 0; q < tb.nb; ++q) {
+    tb.block_start[q] = static_cast<int32_t>(blocks);
+    const int spr = tb.chunks_per_row[q];
+    const long long per_block = spr > 1 ? subs / spr : static_cast<long long>(subs) * tb.rows_per_item[q];
+    blocks += (tb.nrows[q] + per_block - 1) / per_block;
+    if (blocks > INT32_MAX) return -1;
+  }
+  tb.block_start[tb.nb] = static_cast<int32_t>(blocks);
+  return blocks;
 }
 
 // Lanes per dense row, the first template argument of the kernel used: one lane per 16-byte
@@ -525,29 +699,26 @@ long long plan_blocks(HybTable& tb, int subs) {
 }
 
 template <int LPR, int W>
-int launch_lean(HybTable& tb, const float* b, float* c, int feat, int all_atomic,
-                cudaStream_t stream, bool after_rearm) {
-  const long long blocks = plan_blocks(tb, kThreads / LPR);
+int launch_lean(HybTable& tb, const LeanArgs& la, cudaStream_t stream) {
+  plan_items_lean(tb, lean_item_slots(LPR, W), kThreads / LPR);
+  const long long blocks = plan_blocks_lean(tb, kThreads / LPR);
   if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
-  dim3 grid(static_cast<unsigned>(blocks), feat / (W * LPR));
-  if (after_rearm) {
-    // start while the re-arm launch of this call is still running; see hyb_rearm_kernel
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr{};
-    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    SPTIR_CUDA_OK(cudaLaunchKernelEx(&cfg, hyb_spmm_lean_kernel<LPR, W>, tb, b, c, feat, all_atomic));
-    return 0;
-  }
-  hyb_spmm_lean_kernel<LPR, W><<<grid, kThreads, 0, stream>>>(tb, b, c, feat, all_atomic);
+  dim3 grid(static_cast<unsigned>(blocks), la.feat / (W * LPR));
+  hyb_spmm_lean_kernel<LPR, W><<<grid, kThreads, 0, stream>>>(tb, la);
   SPTIR_LAUNCH_OK("hyb_spmm_lean_kernel");
   return 0;
+}
+
+int dispatch_lean(HybTable& tb, const LeanArgs& la, int lanes, int lane_w, cudaStream_t st) {
+  if (lane_w == 8) {
+    if (lanes == 4) return launch_lean<4, 8>(tb, la, st);
+    if (lanes == 8) return launch_lean<8, 8>(tb, la, st);
+    if (lanes == 16) return launch_lean<16, 8>(tb, la, st);
+    return launch_lean<32, 8>(tb, la, st);
+  }
+  if (lanes == 8) return launch_lean<8, 4>(tb, la, st);
+  if (lanes == 16) return launch_lean<16, 4>(tb, la, st);
+  return launch_lean<32, 4>(tb, la, st);
 }
 
 template <int LPR>
@@ -586,6 +757,8 @@ int launch(HybTable& tb, const float* b, float* c, int feat, int all_atomic, cud
 }  // namespace sptir
 
 namespace sptir {
+size_t hyb_scratch_limit_bytes() { return hyb_scratch_limit(); }
+
 // The launcher behind sparsetir_hyb_spmm_raw.  row_bases (may be null): for buckets whose `rows`
 // array is null, ELL row r of bucket q is written to output row row_bases[q] + r.
 int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, const int32_t* row_bases,
@@ -621,6 +794,14 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
     tb.nrows[k] = bk.nrows; tb.width[k] = bk.width;
     tb.row_base[k] = row_bases ? row_bases[order[k]] : 0;
   }
+  if (validate_enabled()) {
+    for (int k = 0; k < tb.nb; ++k) {
+      const long long slots = static_cast<long long>(tb.nrows[k]) * tb.width[k];
+      if (validate_range("sparsetir_hyb_spmm", "a bucket's row_indices", tb.rows[k], tb.nrows[k], m, st) != 0 ||
+          validate_range("sparsetir_hyb_spmm", "a bucket's col_indices", tb.cols[k], slots, n, st) != 0)
+        return -1;
+    }
+  }
   const bool vec4 = (feat % 4 == 0) && aligned16(b) && aligned16(c);
   // the lean kernel takes whole feature tiles and ELL widths of 1, 2, 4 or a multiple of 8; with
   // 32-byte aligned operands and a multiple of 32 features its lanes own 8 floats, else 4
@@ -636,15 +817,55 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
     lanes = lanes_per_row(feat, vec4, n, lane_w);
   }
   lean = lean && feat % (lane_w * lanes) == 0;
-  plan_items(tb, lean ? lean_item_slots(lanes, lane_w) : item_slots(lanes));
+  const size_t c_bytes = static_cast<size_t>(m) * feat * sizeof(float);
+  if (tb.nb == 0) {
+    if (flags & SPARSETIR_HYB_ZERO_C) SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, c_bytes, st));
+    return 0;
+  }
 
-  bool after_rearm = false;  // this call's re-arm kernel directly precedes the SpMM launch
+  if (lean) {
+    // ---- one writer per output row (or everything atomic when the caller asks for it)
+    LeanArgs la{b, c, nullptr, nullptr, feat, all_atomic};
+    bool clear = (flags & SPARSETIR_HYB_ZERO_C) || (all_atomic && (flags & SPARSETIR_HYB_REARM));
+    for (int q = 0; q < tb.nb; ++q) tb.part_base[q] = -1;
+    if (!all_atomic) {
+      // split rows live in the widest bucket(s) that carry row ids: one scratch row per ELL row
+      int maxw = 0;
+      for (int q = 0; q < tb.nb; ++q)
+        if (tb.rows[q] != nullptr) maxw = std::max(maxw, tb.width[q]);
+      long long part_rows = 0;
+      for (int q = 0; q < tb.nb; ++q)
+        if (tb.rows[q] != nullptr && tb.width[q] == maxw) {
+          tb.part_base[q] = static_cast<int32_t>(part_rows);
+          part_rows += tb.nrows[q];
+        }
+      const int tiles = feat / (lane_w * lanes);
+      const size_t part_bytes = static_cast<size_t>(part_rows) * feat * sizeof(float);
+      const size_t counter_bytes = static_cast<size_t>(part_rows) * tiles * sizeof(unsigned);
+      if (part_rows > INT32_MAX || part_bytes > hyb_scratch_limit()) {
+        // a bucket list whose widest bucket holds most of the matrix: adding atomically into a
+        // cleared C costs less memory than a scratch copy of that size
+        for (int q = 0; q < tb.nb; ++q) tb.part_base[q] = -1;
+        la.all_atomic = 1;
+        clear = true;
+      } else if (part_rows > 0) {
+        la.part = static_cast<float*>(workspace(device_id, st, part_bytes));
+        la.counters = static_cast<unsigned*>(zeroed_workspace(device_id, st, counter_bytes));
+        if (la.part == nullptr || la.counters == nullptr) return -1;
+      }
+    }
+    if (clear) SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, c_bytes, st));
+    return dispatch_lean(tb, la, lanes, lane_w, st);
+  }
+
+  // ---- fallback kernels for odd widths, feature counts or alignments
+  plan_items(tb, item_slots(lanes));
   if (flags & SPARSETIR_HYB_ZERO_C) {
-    SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(m) * feat * sizeof(float), st));
+    SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, c_bytes, st));
   } else if (flags & SPARSETIR_HYB_REARM) {
     if (all_atomic) {
-      SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(m) * feat * sizeof(float), st));
-    } else if (tb.nb > 0) {
+      SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, c_bytes, st));
+    } else {
       long long blocks = 0;
       for (int q = 0; q < tb.nb; ++q) {
         tb.block_start[q] = static_cast<int32_t>(blocks);
@@ -654,23 +875,10 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
       if (blocks > INT32_MAX) return fail("sparsetir_hyb_spmm: too many thread blocks");
       hyb_rearm_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, st>>>(tb, c, feat);
       SPTIR_LAUNCH_OK("hyb_rearm_kernel");
-      after_rearm = true;
     }
   }
-  if (tb.nb == 0) return 0;
 
   if (vec4) {
-    if (lean && lane_w == 8) {
-      if (lanes == 4) return launch_lean<4, 8>(tb, b, c, feat, all_atomic, st, after_rearm);
-      if (lanes == 8) return launch_lean<8, 8>(tb, b, c, feat, all_atomic, st, after_rearm);
-      if (lanes == 16) return launch_lean<16, 8>(tb, b, c, feat, all_atomic, st, after_rearm);
-      return launch_lean<32, 8>(tb, b, c, feat, all_atomic, st, after_rearm);
-    }
-    if (lean) {
-      if (lanes == 8) return launch_lean<8, 4>(tb, b, c, feat, all_atomic, st, after_rearm);
-      if (lanes == 16) return launch_lean<16, 4>(tb, b, c, feat, all_atomic, st, after_rearm);
-      return launch_lean<32, 4>(tb, b, c, feat, all_atomic, st, after_rearm);
-    }
     if (lanes == 8) return launch_async<8>(tb, b, c, feat, all_atomic, st);
     if (lanes == 16) return launch_async<16>(tb, b, c, feat, all_atomic, st);
     return launch_async<32>(tb, b, c, feat, all_atomic, st);
@@ -681,6 +889,26 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
   return launch<32, 4, 1>(tb, b, c, feat, all_atomic, st);
 }
 }  // namespace sptir
+
+extern "C" int sparsetir_hyb_spmm_workspace(const SparsetirEllBucket* buckets, int num_buckets,
+                                            int feat, size_t* scratch_bytes,
+                                            size_t* counter_bytes) {
+  if (num_buckets < 0 || (num_buckets > 0 && !buckets) || feat < 0 || !scratch_bytes || !counter_bytes)
+    return sptir::fail("sparsetir_hyb_spmm_workspace: bad argument");
+  int maxw = 0;
+  for (int q = 0; q < num_buckets; ++q)
+    if (buckets[q].nrows > 0 && buckets[q].rows != nullptr) maxw = std::max(maxw, buckets[q].width);
+  size_t rows = 0;
+  for (int q = 0; q < num_buckets; ++q)
+    if (buckets[q].nrows > 0 && buckets[q].rows != nullptr && buckets[q].width == maxw)
+      rows += static_cast<size_t>(buckets[q].nrows);
+  const size_t part = rows * static_cast<size_t>(feat) * sizeof(float);
+  const bool fits = part <= sptir::hyb_scratch_limit_bytes();
+  *scratch_bytes = fits ? part : 0;
+  // a feature tile is at least 32 floats wide
+  *counter_bytes = fits ? rows * static_cast<size_t>((feat + 31) / 32) * sizeof(unsigned) : 0;
+  return 0;
+}
 
 extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirEllBucket* buckets,
                                       int num_buckets, int m, int n, int feat, int flags,

@@ -179,13 +179,18 @@ extern "C" int sparsetir_rgms_raw(const float* a, const float* w, const float* x
                                   int num_rels, int feat, int nnz_i, int nnz_j, int device_id,
                                   void* stream) {
   using namespace sptir;
-  (void)m;
   if (num_rels < 0 || feat < 0 || nnz_i < 0 || nnz_j < 0) return fail("sparsetir_rgms: negative size");
   if (nnz_i == 0 || feat == 0 || num_rels == 0) return 0;
   if (!w || !x || !y || !indptr_i || !indices_i || !indptr_j || (nnz_j > 0 && (!a || !indices_j)))
     return fail("sparsetir_rgms: null pointer argument");
   if (use_device(device_id) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (validate_enabled() &&
+      (validate_indptr("sparsetir_rgms", "indptr_i", indptr_i, num_rels, nnz_i, st) != 0 ||
+       validate_range("sparsetir_rgms", "indices_i", indices_i, nnz_i, m, st) != 0 ||
+       validate_indptr("sparsetir_rgms", "indptr_j", indptr_j, nnz_i, nnz_j, st) != 0 ||
+       validate_range("sparsetir_rgms", "indices_j", indices_j, nnz_j, n, st) != 0))
+    return -1;
   const bool al = aligned16(x) && aligned16(y) && aligned16(w);
   if (al) {
     if (feat == 64) {

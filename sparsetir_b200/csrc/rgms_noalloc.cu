@@ -13,15 +13,16 @@
 // every GPU that loads the library, until the process exits), and every call on a device uses
 // the same array.  Two calls that overlap on the GPU (different streams, no ordering between
 // them) would overwrite each other's intermediate: order them.  The first call on a device
-// looks up the array's device address (cudaGetSymbolAddress); make that first call before any
-// stream capture.
+// looks up the array's device address (cudaGetSymbolAddress), and with it the CUDA runtime loads
+// this module's image on that device — that is when the 32 MiB come into being.  So make that
+// first call at start-up, while device memory is still free, and before any stream capture.
 #include <mutex>
 
 #include "common.h"
 
 namespace sptir {
 
-// defined in rgms_tc.cu
+// defined in csrmm.cu and rgms_tc.cu
 int csrmm_impl(const float* a, const float* b, float* c, const int32_t* indptr, const int32_t* indices,
                int m, int n, int feat, int nnz, int device_id, void* stream, bool hub_rows);
 int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,

@@ -1,4 +1,5 @@
 // Error string, stream table and device selection.
+#include <algorithm>
 #include <atomic>
 #include <cstring>
 #include <map>
@@ -13,7 +14,15 @@ namespace sptir {
 namespace {
 thread_local std::string tls_error;
 constexpr int kMaxDevices = 64;
-std::atomic<void*> g_streams[kMaxDevices];
+// The stream of a (thread, device) pair, as in the reference, whose current stream is a member
+// of the thread-local CUDAThreadEntry (src/runtime/cuda/cuda_device_api.cc:209-211).  A thread that
+// never set one uses the process-wide default of the device.
+std::atomic<void*> g_default_streams[kMaxDevices];
+struct ThreadStreams {
+  void* stream[kMaxDevices] = {};
+  bool set[kMaxDevices] = {};
+};
+thread_local ThreadStreams tls_streams;
 }  // namespace
 
 int fail(const char* fmt, ...) {
@@ -35,7 +44,8 @@ int use_device(int device_id) {
 
 cudaStream_t stream_for(int device_id) {
   if (device_id < 0 || device_id >= kMaxDevices) return nullptr;
-  return static_cast<cudaStream_t>(g_streams[device_id].load(std::memory_order_acquire));
+  if (tls_streams.set[device_id]) return static_cast<cudaStream_t>(tls_streams.stream[device_id]);
+  return static_cast<cudaStream_t>(g_default_streams[device_id].load(std::memory_order_acquire));
 }
 
 namespace {
@@ -44,29 +54,46 @@ struct Scratch {
   size_t bytes = 0;
 };
 std::mutex g_ws_mutex;
-std::map<std::pair<int, cudaStream_t>, Scratch> g_ws;
-}  // namespace
+// [0]: plain scratch; [1]: scratch that is all zero whenever no kernel is using it
+std::map<std::pair<int, cudaStream_t>, Scratch> g_ws[2];
 
-void* workspace(int device_id, cudaStream_t stream, size_t bytes) {
+// Grows the buffer of (device, stream) to at least `bytes`; with `zeroed`, a new buffer is cleared
+// on `stream` before anything queued later can touch it.
+void* grow(int kind, int device_id, cudaStream_t stream, size_t bytes) {
   std::lock_guard<std::mutex> lock(g_ws_mutex);
-  Scratch& s = g_ws[{device_id, stream}];
+  Scratch& s = g_ws[kind][{device_id, stream}];
   if (s.bytes >= bytes && s.ptr != nullptr) return s.ptr;
   if (s.ptr != nullptr) {
     cudaFree(s.ptr);  // synchronises: nothing in flight can still use the old buffer
     s.ptr = nullptr;
     s.bytes = 0;
   }
-  const size_t want = (bytes + (size_t{1} << 20) - 1) & ~((size_t{1} << 20) - 1);
+  const size_t unit = kind == 0 ? (size_t{1} << 20) : (size_t{1} << 12);
+  const size_t want = (std::max<size_t>(bytes, 1) + unit - 1) & ~(unit - 1);
   void* p = nullptr;
-  const cudaError_t err = cudaMalloc(&p, want);
+  cudaError_t err = cudaMalloc(&p, want);
+  if (err == cudaSuccess && kind == 1) {
+    err = cudaMemsetAsync(p, 0, want, stream);
+    if (err != cudaSuccess) cudaFree(p);
+  }
   if (err != cudaSuccess) {
-    cudaGetLastError();  // clear the sticky-free error state of the failed allocation
-    fail("workspace of %zu bytes: %s", want, cudaGetErrorString(err));
+    cudaGetLastError();  // clear the error state of the failed call
+    fail("workspace of %zu bytes: %s (reserve it before capturing a stream: "
+         "sparsetir_reserve_workspace)", want, cudaGetErrorString(err));
     return nullptr;
   }
   s.ptr = p;
   s.bytes = want;
   return p;
+}
+}  // namespace
+
+void* workspace(int device_id, cudaStream_t stream, size_t bytes) {
+  return grow(0, device_id, stream, bytes);
+}
+
+void* zeroed_workspace(int device_id, cudaStream_t stream, size_t bytes) {
+  return grow(1, device_id, stream, bytes);
 }
 
 }  // namespace sptir
@@ -78,7 +105,24 @@ const char* sparsetir_get_last_error(void) { return sptir::tls_error.c_str(); }
 int sparsetir_set_stream(int device_id, void* stream) {
   if (device_id < 0 || device_id >= sptir::kMaxDevices)
     return sptir::fail("sparsetir_set_stream: device id %d out of range", device_id);
-  sptir::g_streams[device_id].store(stream, std::memory_order_release);
+  sptir::tls_streams.stream[device_id] = stream;
+  sptir::tls_streams.set[device_id] = true;
+  return 0;
+}
+
+int sparsetir_set_default_stream(int device_id, void* stream) {
+  if (device_id < 0 || device_id >= sptir::kMaxDevices)
+    return sptir::fail("sparsetir_set_default_stream: device id %d out of range", device_id);
+  sptir::g_default_streams[device_id].store(stream, std::memory_order_release);
+  return 0;
+}
+
+int sparsetir_reserve_workspace(int device_id, void* stream, size_t scratch_bytes,
+                                size_t counter_bytes) {
+  if (sptir::use_device(device_id) != 0) return -1;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (scratch_bytes > 0 && sptir::workspace(device_id, st, scratch_bytes) == nullptr) return -1;
+  if (counter_bytes > 0 && sptir::zeroed_workspace(device_id, st, counter_bytes) == nullptr) return -1;
   return 0;
 }
 

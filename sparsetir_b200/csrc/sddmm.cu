@@ -423,6 +423,7 @@ extern "C" int sparsetir_sddmm_raw(const float* a, const float* b, float* c, con
     return fail("sparsetir_sddmm: null pointer argument");
   if (use_device(device_id) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (validate_enabled() && validate_csr("sparsetir_sddmm", indptr, m, indices, nnz, n, st) != 0) return -1;
   if (feat == 0) {
     SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(nnz) * sizeof(float), st));
     return 0;

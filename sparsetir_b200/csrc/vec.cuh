@@ -106,6 +106,15 @@ template <> struct LaneVec<4> {
   static __device__ __forceinline__ void stcs(void* p, const float4& v) { __stcs(reinterpret_cast<float4*>(p), v); }
   static __device__ __forceinline__ void fma(float4& acc, float w, const float4& x) { Vec<4>::fma(acc, w, x); }
   static __device__ __forceinline__ void atomic_add(void* p, const float4& v) { atomicAdd(reinterpret_cast<float4*>(p), v); }
+  // L2-coherent accesses for data that another block wrote during this launch
+  static __device__ __forceinline__ float4 ldcg(const void* p) { return __ldcg(reinterpret_cast<const float4*>(p)); }
+  static __device__ __forceinline__ void stcg(void* p, const float4& v) { __stcg(reinterpret_cast<float4*>(p), v); }
+  static __device__ __forceinline__ void add(float4& acc, const float4& x) {
+    acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+  }
+  // shared memory (16-byte aligned)
+  static __device__ __forceinline__ void sts(float* p, const float4& v) { *reinterpret_cast<float4*>(p) = v; }
+  static __device__ __forceinline__ float4 lds(const float* p) { return *reinterpret_cast<const float4*>(p); }
 };
 template <> struct LaneVec<8> {
   using type = Pack4;
@@ -119,6 +128,35 @@ template <> struct LaneVec<8> {
     unpack_pair(v.q[2], hi.x, hi.y); unpack_pair(v.q[3], hi.z, hi.w);
     atomicAdd(reinterpret_cast<float4*>(p), lo);
     atomicAdd(reinterpret_cast<float4*>(p) + 1, hi);
+  }
+  static __device__ __forceinline__ Pack4 ldcg(const void* p) {
+    Pack4 r;
+    asm volatile("ld.global.cg.v4.b64 {%0,%1,%2,%3}, [%4];"
+                 : "=l"(r.q[0]), "=l"(r.q[1]), "=l"(r.q[2]), "=l"(r.q[3])
+                 : "l"(p) : "memory");
+    return r;
+  }
+  static __device__ __forceinline__ void stcg(void* p, const Pack4& v) {
+    asm volatile("st.global.cg.v4.b64 [%0], {%1,%2,%3,%4};" ::"l"(p), "l"(v.q[0]), "l"(v.q[1]),
+                 "l"(v.q[2]), "l"(v.q[3])
+                 : "memory");
+  }
+  static __device__ __forceinline__ void add(Pack4& acc, const Pack4& x) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      asm("add.rn.f32x2 %0, %0, %1;" : "+l"(acc.q[i]) : "l"(x.q[i]));
+  }
+  // shared memory (32-byte aligned)
+  static __device__ __forceinline__ void sts(float* p, const Pack4& v) {
+    ulonglong2* d = reinterpret_cast<ulonglong2*>(p);
+    d[0] = make_ulonglong2(v.q[0], v.q[1]);
+    d[1] = make_ulonglong2(v.q[2], v.q[3]);
+  }
+  static __device__ __forceinline__ Pack4 lds(const float* p) {
+    const ulonglong2* d = reinterpret_cast<const ulonglong2*>(p);
+    Pack4 r;
+    r.q[0] = d[0].x; r.q[1] = d[0].y; r.q[2] = d[1].x; r.q[3] = d[1].y;
+    return r;
   }
 };
 

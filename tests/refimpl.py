@@ -113,3 +113,36 @@ def hyb_spmm_from_buckets(buckets, x, m: int) -> np.ndarray:
         contrib = np.einsum("rs,rsf->rf", np.asarray(w, np.float64), x[cols])
         np.add.at(y, rows, contrib)
     return y
+
+
+def ellmm_f64(a, b, indices, nb: int, col: int, blk: int, feat: int) -> np.ndarray:
+    """Block-ELL SpMM in fp64: c[i,bi,f] = sum_j sum_bj a[i,j,bi,bj] * b[indices[i,j],bj,f]."""
+    a = np.asarray(a, np.float64).reshape(nb, col, blk, blk)
+    b3 = np.asarray(b, np.float64).reshape(-1, blk, feat)
+    if col == 0:
+        return np.zeros((nb * blk, feat))
+    return np.einsum("ijxy,ijyf->ixf", a, b3[np.asarray(indices).reshape(nb, col)]).reshape(nb * blk, feat)
+
+
+def fusedmm_f64(q, k, v, indptr, indices) -> np.ndarray:
+    """Sparse attention in fp64 with the reference's softmax (numerator not shifted by the row
+    maximum: exp(s) / sum exp(s - max))."""
+    q, k, v = (np.asarray(t, np.float64) for t in (q, k, v))
+    m = len(indptr) - 1
+    rows = np.repeat(np.arange(m), np.diff(indptr))
+    s = np.einsum("ef,ef->e", q[rows], k[indices])
+    out = np.zeros((m, v.shape[1]))
+    if len(s) == 0:
+        return out
+    mx = np.full(m, -np.inf)
+    np.maximum.at(mx, rows, s)
+    den = np.zeros(m)
+    np.add.at(den, rows, np.exp(s - mx[rows]))
+    np.add.at(out, rows, (np.exp(s) / den[rows])[:, None] * v[indices])
+    return out
+
+
+def row_sums_f64(vals, indptr) -> np.ndarray:
+    out = np.zeros(len(indptr) - 1)
+    np.add.at(out, np.repeat(np.arange(len(indptr) - 1), np.diff(indptr)), np.asarray(vals, np.float64))
+    return out

@@ -289,6 +289,11 @@ SPARSETIR_API int sparsetir_hyb_spmm_raw(const float* b, float* c, const Sparset
 SPARSETIR_API int sparsetir_hyb_spmm_workspace(const SparsetirEllBucket* buckets, int num_buckets,
                                                int feat, size_t* scratch_bytes,
                                                size_t* counter_bytes);
+/* The feature tile the main hyb kernel uses for 16/32-byte aligned operands with n rows of b:
+ * `lanes` lanes of `lane_floats` floats each (the kernel is hyb_spmm_lean_kernel<lanes, lane_floats>,
+ * launched with feat / (lanes * lane_floats) tiles in grid.y).  For tools that match a launch with
+ * a profile. */
+SPARSETIR_API int sparsetir_hyb_spmm_tile(int n, int feat, int* lanes, int* lane_floats);
 SPARSETIR_API int sparsetir_sddmm_raw(const float* a, const float* b, float* c,
                                       const int32_t* indptr, const int32_t* indices,
                                       const float* scale, int m, int n, int feat, int nnz,

@@ -9,7 +9,8 @@ import ctypes
 import os
 
 _PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG, "libsparsetir_b200.so")
+# SPARSETIR_B200_LIBRARY names another build of the same library (kernel experiments)
+LIB_PATH = os.environ.get("SPARSETIR_B200_LIBRARY") or os.path.join(_PKG, "libsparsetir_b200.so")
 
 # ---- ctypes mirrors of the structs in include/sparsetir_b200.h ---------------------------------
 
@@ -91,6 +92,7 @@ PLAIN_SYMBOLS = {
     "sparsetir_set_default_stream": (_i, [_i, _vp]),
     "sparsetir_get_stream": (_vp, [_i]),
     "sparsetir_reserve_workspace": (_i, [_i, _vp, ctypes.c_size_t, ctypes.c_size_t]),
+    "sparsetir_hyb_spmm_tile": (_i, [_i, _i, ctypes.POINTER(ctypes.c_int), ctypes.POINTER(ctypes.c_int)]),
     "sparsetir_hyb_spmm_workspace": (_i, [ctypes.POINTER(EllBucket), _i, _i,
                                           ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]),
     "sparsetir_set_validate": (_i, [_i]),

@@ -656,7 +656,7 @@ long long plan_blocks_lean(HybTable& tb, int subs) {
 // tile is narrowed until that slice fits the part of L2 that stays resident for data every SM
 // reads (measured: about half of the 126 MB), because re-reading the index arrays once per tile
 // costs little next to re-fetching B rows from HBM.
-int lanes_per_row(int feat, bool vec4, int n, int lane_w) {
+int lanes_per_row_impl(int feat, bool vec4, int n, int lane_w) {
   const int units = vec4 ? feat / lane_w : feat;
   const int min_lanes = lane_w == 8 ? 4 : 8;
   int lanes = units <= min_lanes ? min_lanes : (units <= 8 ? 8 : (units <= 16 ? 16 : 32));
@@ -758,6 +758,7 @@ int launch(HybTable& tb, const float* b, float* c, int feat, int all_atomic, cud
 
 namespace sptir {
 size_t hyb_scratch_limit_bytes() { return hyb_scratch_limit(); }
+int lanes_per_row(int feat, bool vec4, int n, int lane_w) { return lanes_per_row_impl(feat, vec4, n, lane_w); }
 
 // The launcher behind sparsetir_hyb_spmm_raw.  row_bases (may be null): for buckets whose `rows`
 // array is null, ELL row r of bucket q is written to output row row_bases[q] + r.
@@ -811,10 +812,10 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
     lean = lean && (w == 1 || w == 2 || w == 4 || w % 8 == 0);
   }
   int lane_w = (lean && feat % 32 == 0 && aligned32(b) && aligned32(c)) ? max_lane_floats() : 4;
-  int lanes = lanes_per_row(feat, vec4, n, lane_w);
+  int lanes = lanes_per_row_impl(feat, vec4, n, lane_w);
   if (lane_w == 8 && feat % (lane_w * lanes) != 0) {  // no whole tiles of 8-float lanes
     lane_w = 4;
-    lanes = lanes_per_row(feat, vec4, n, lane_w);
+    lanes = lanes_per_row_impl(feat, vec4, n, lane_w);
   }
   lean = lean && feat % (lane_w * lanes) == 0;
   const size_t c_bytes = static_cast<size_t>(m) * feat * sizeof(float);
@@ -889,6 +890,20 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
   return launch<32, 4, 1>(tb, b, c, feat, all_atomic, st);
 }
 }  // namespace sptir
+
+extern "C" int sparsetir_hyb_spmm_tile(int n, int feat, int* lanes, int* lane_floats) {
+  if (!lanes || !lane_floats || feat <= 0 || feat % 4 != 0)
+    return sptir::fail("sparsetir_hyb_spmm_tile: feat_size must be a positive multiple of 4");
+  int lane_w = feat % 32 == 0 ? sptir::max_lane_floats() : 4;
+  int l = sptir::lanes_per_row(feat, true, n, lane_w);
+  if (lane_w == 8 && feat % (lane_w * l) != 0) {
+    lane_w = 4;
+    l = sptir::lanes_per_row(feat, true, n, lane_w);
+  }
+  *lanes = l;
+  *lane_floats = lane_w;
+  return 0;
+}
 
 extern "C" int sparsetir_hyb_spmm_workspace(const SparsetirEllBucket* buckets, int num_buckets,
                                             int feat, size_t* scratch_bytes,

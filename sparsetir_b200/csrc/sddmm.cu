@@ -21,6 +21,8 @@
 #include <cstdint>
 #include <cstdlib>
 
+#include <algorithm>
+
 #include "common.h"
 #include "vec.cuh"
 
@@ -360,14 +362,40 @@ int launch(const float* a, const float* b, float* c, const int32_t* indptr, cons
   return 0;
 }
 
+// Blocks of sddmm_lean_kernel<LPR> that fit one SM at a time (asked of the runtime once per device).
+template <int LPR>
+int lean_blocks_per_sm() {
+  static thread_local int cached_device = -1, cached = 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 4;
+  if (dev != cached_device) {
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sddmm_lean_kernel<LPR>, kThreads, 0) != cudaSuccess || n < 1)
+      n = 4;
+    cached = n;
+    cached_device = dev;
+  }
+  return cached;
+}
+
 template <int LPR>
 int launch_lean_tile(const float* a, const float* b, float* c, const int32_t* indptr,
                      const int32_t* indices, const float* scale, int m, int feat, int nnz, int foff,
                      cudaStream_t stream) {
   // long chunks amortise the row search; short ones keep small inputs spread over the SMs
-  const int chunk = nnz >= (1 << 22) ? 1024 : 256;
-  const int warps = ceil_div(nnz, chunk);
-  const int blocks = ceil_div(warps, kThreads / 32);
+  int chunk = nnz >= (1 << 22) ? 1024 : 256;
+  const int wpb = kThreads / 32;
+  int blocks = ceil_div(ceil_div(nnz, chunk), wpb);
+  // A launch of only a few waves of blocks ends with a partly filled wave (3.02 waves cost as
+  // much as 4): then the chunk is resized so that the blocks fill a whole number of waves.
+  const long long resident = static_cast<long long>(kNumSMs) * lean_blocks_per_sm<LPR>();
+  if (nnz >= (1 << 22) && blocks > resident / 2 && blocks < 8 * resident) {
+    const long long waves = std::max<long long>(1, (blocks + resident / 2) / resident);
+    const long long want_warps = waves * resident * wpb;
+    chunk = static_cast<int>((nnz + want_warps - 1) / want_warps);
+    chunk = (chunk + 31) & ~31;
+    blocks = ceil_div(ceil_div(nnz, chunk), wpb);
+  }
   sddmm_lean_kernel<LPR><<<blocks, kThreads, 0, stream>>>(a, b, c, indptr, indices, scale, m, nnz,
                                                            feat, foff, foff != 0, chunk);
   SPTIR_LAUNCH_OK("sddmm_lean_kernel");

@@ -19,6 +19,8 @@ from . import datagen as dg
 from . import ops
 
 L2_BYTES = 126 * 1024 * 1024
+FP32_GFLOPS_NOMINAL = 148 * 128 * 2 * 1.965     # fp32 FMA rate at the maximum SM clock
+L2_GATHER_GBS_MEASURED = 17800.0                 # random 128-byte row gathers from an L2-resident array
 
 
 def _time(fn: Callable[[], None], number: int, repeat: int = 3, warmup: int = 3) -> float:
@@ -47,7 +49,7 @@ def _time_graph(fn: Callable[[], None], number: int, repeat: int = 5) -> float:
         fn()
     torch.cuda.current_stream().wait_stream(side)
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
+    with torch.cuda.graph(graph, stream=side):  # the stream whose scratch the warm-up call set up
         for _ in range(number):
             fn()
     graph.replay()
@@ -152,7 +154,10 @@ def bench_sddmm(device, peaks, feats=(32, 64, 128, 256)) -> dict:
     indptr, indices, scale, nnz = sddmm_graph_on_device(device)
     gen = torch.Generator(device=device)
     gen.manual_seed(1)
-    out = {"workload": "sddmm_lognormal_232965", "nnz": nnz, "per_feat": {}}
+    out = {"workload": "sddmm_lognormal_232965", "nnz": nnz,
+           "graph": "built on the GPU with a torch generator: the twin of datagen.csr_lognormal(seed=0) "
+                    "(same degree sequence, other column draws)",
+           "per_feat": {}}
     c = torch.empty(nnz, device=device)
     for f in feats:
         a = torch.rand(n * f, device=device, generator=gen) * 2 - 1
@@ -161,8 +166,15 @@ def bench_sddmm(device, peaks, feats=(32, 64, 128, 256)) -> dict:
         ms = _time(fn, number=3, repeat=3, warmup=2)
         flops = 2.0 * nnz * f + nnz
         byts = 4 * (n + 1) + 12 * nnz + 8 * n * f
-        out["per_feat"][str(f)] = _entry(ms, flops, byts, peaks,
-                                         gather_gbs=(4.0 * nnz * f) / (ms * 1e-3) / 1e9)
+        ent = _entry(ms, flops, byts, peaks, gather_gbs=(4.0 * nnz * f) / (ms * 1e-3) / 1e9)
+        # the three roofs side by side: HBM by the compulsory bytes, the fp32 FMA pipes (nominal
+        # 148 SMs x 128 lanes x 2 x 1.965 GHz), and the L2-to-SM path that carries one B row per
+        # position (17.8 TB/s is the rate this kernel reached at F = 32 with the path 77-79 % busy)
+        ent["fma_frac"] = ent["gflops"] / FP32_GFLOPS_NOMINAL
+        ent["l2_gather_frac"] = ent["gather_gbs"] / L2_GATHER_GBS_MEASURED
+        ent["binding_roof"] = max((ent["hbm_frac"], "hbm"), (ent["fma_frac"], "fp32 fma"),
+                                  (ent["l2_gather_frac"], "l2-to-sm gather"))[1]
+        out["per_feat"][str(f)] = ent
         del a, b
     # spot check of the full-size result against a float64 recomputation of 4096 random edges
     f = feats[0]
@@ -214,62 +226,212 @@ def bench_sddmm(device, peaks, feats=(32, 64, 128, 256)) -> dict:
     return out
 
 
+def _max_over_ranks(ms: float, device) -> float:
+    import torch.distributed as dist
+    t = torch.tensor([ms], device=device, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _all_ranks_ok(ok: bool, device) -> bool:
+    import torch.distributed as dist
+    t = torch.tensor([1.0 if ok else 0.0], device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    return bool(t.item() == 1.0)
+
+
 def bench_sddmm_sharded(device, peaks, rank: int, world: int, feats=(32, 128)) -> dict:
     """Config 3 cut into nnz-balanced row blocks, one per rank (every rank builds the same seeded
-    graph and keeps its block).  Per feature size: the shard kernels alone (max over ranks) and
-    with the all-gather of the per-position outputs.  Collective: every rank must call it."""
+    graph and keeps its block), each block in four row chunks whose all-gathers overlap the next
+    chunk's kernels.  Per feature size: the shard kernels alone (max and min over ranks), the step
+    that ends with the per-position outputs all-gathered on every rank, and the whole graph on
+    rank 0 alone in the same run, so that the parallel efficiency is a ratio of two numbers of one
+    run.  Every rank checks its own positions against the CPU oracle.  Collective."""
     import torch.distributed as dist
 
-    from . import dist as sdist
-    from . import format as fmt
+    from oracle import oracle as orc
+    from . import sharded
 
     n = 232_965
     indptr, indices, scale, nnz = sddmm_graph_on_device(device)
-    cuts = fmt.row_partition(indptr.cpu().numpy(), world)
-    r0, r1 = int(cuts[rank]), int(cuts[rank + 1])
-    ip_host = indptr.cpu().numpy()
-    sizes = [int(ip_host[cuts[k + 1]] - ip_host[cuts[k]]) for k in range(world)]
-    p0, p1 = int(ip_host[r0]), int(ip_host[r1])
-    ip_loc = (indptr[r0:r1 + 1] - indptr[r0]).contiguous()
-    ix_loc, sc_loc = indices[p0:p1], scale[p0:p1]
+    op = sharded.ShardedSddmm(indptr, indices, scale, n, chunks=4, device=device)
     c_full = torch.empty(nnz, device=device)
-    c_loc = c_full[p0:p1]
     gen = torch.Generator(device=device)
     gen.manual_seed(1)
-    out = {"workload": "sddmm_lognormal_232965", "nnz": nnz, "rows_per_rank": [int(cuts[k + 1] - cuts[k]) for k in range(world)],
-           "nnz_per_rank": sizes, "per_feat": {}}
-
-    def max_over_ranks(ms: float) -> float:
-        t = torch.tensor([ms], device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
+    out = {"workload": "sddmm_lognormal_232965", "nnz": nnz,
+           "graph": "built on the GPU with a torch generator: the twin of datagen.csr_lognormal(seed=0) "
+                    "(same degree sequence, other column draws)",
+           "rows_per_rank": [int(op.cuts[k + 1] - op.cuts[k]) for k in range(world)],
+           "nnz_per_rank": [sum(op.chunk_sizes[c][k] for c in range(op.chunks)) for k in range(world)],
+           "chunks": op.chunks, "per_feat": {}}
+    ok = True
     for f in feats:
         a = torch.rand(n * f, device=device, generator=gen) * 2 - 1
         b = torch.rand(n * f, device=device, generator=gen) * 2 - 1
-        fn = ops.sddmm.prepare(a[r0 * f:r1 * f], b, c_loc, ip_loc, ix_loc, sc_loc)
+        calls = op.prepare(a, b, c_full, f)
         dist.barrier()
-        ms = max_over_ranks(_time(fn, number=3, repeat=3, warmup=2))
+        mine = _time(lambda: op.run(calls), number=3, repeat=3, warmup=2)
+        ms = _max_over_ranks(mine, device)
+        ms_min = -_max_over_ranks(-mine, device)
 
         def with_gather():
-            fn()
-            sdist.all_gather_blocks(c_loc, sizes, out=c_full)
+            op.run(calls, c_full)
+            op.wait()
 
         dist.barrier()
-        ms_g = max_over_ranks(_time(with_gather, number=2, repeat=3, warmup=1))
+        ms_g = _max_over_ranks(_time(with_gather, number=3, repeat=3, warmup=2), device)
+        # the whole graph on rank 0 alone (the other ranks wait at the barrier)
+        single = 0.0
+        if rank == 0:
+            fn1 = ops.sddmm.prepare(a, b, torch.empty(nnz, device=device), indptr, indices, scale)
+            single = _time(fn1, number=3, repeat=3, warmup=2)
+            del fn1
+        dist.barrier()
+        single = _max_over_ranks(single, device)
         flops = 2.0 * nnz * f + nnz
-        out["per_feat"][str(f)] = {"ms": ms, "gflops": flops / (ms * 1e-3) / 1e9,
-                                   "gather_gbs": (4.0 * nnz * f) / (ms * 1e-3) / 1e9,
-                                   "ms_with_allgather": ms_g,
-                                   "gflops_with_allgather": flops / (ms_g * 1e-3) / 1e9}
-        if f == feats[0]:  # the gathered result is the right one: float64 spot check on rank 0
+        recv = 4.0 * (nnz - out["nnz_per_rank"][rank])
+        out["per_feat"][str(f)] = {
+            "ms": ms, "ms_min_over_ranks": ms_min, "gflops": flops / (ms * 1e-3) / 1e9,
+            "gather_gbs": (4.0 * nnz * f) / (ms * 1e-3) / 1e9,
+            "ms_with_allgather": ms_g, "gflops_with_allgather": flops / (ms_g * 1e-3) / 1e9,
+            "allgather_recv_gbs_per_gpu": recv / (ms_g * 1e-3) / 1e9,
+            "ms_one_gpu_same_run": single,
+            "parallel_efficiency_kernels": single / (world * ms),
+            "parallel_efficiency_with_allgather": single / (world * ms_g)}
+        if f == feats[0]:
+            # this rank's positions (taken from the gathered result on this GPU) against the oracle's
+            # loop nest on the host, and a few thousand positions of the other ranks in float64
+            with_gather()
+            torch.cuda.synchronize()
+            r0, r1 = op.row0, op.row1
+            ip_host = indptr[r0:r1 + 1].cpu().numpy()
+            p0, p1 = int(ip_host[0]), int(ip_host[-1])
+            orc.use_all_cores()
+            want = orc.sddmm(a.view(n, f)[r0:r1].cpu().numpy(), b.view(n, f).cpu().numpy(),
+                             (ip_host - p0).astype(np.int32), indices[p0:p1].cpu().numpy(), r1 - r0, n, f,
+                             scale=scale[p0:p1].cpu().numpy(), omp=True)
+            got = c_full[p0:p1].cpu().numpy()
+            ok = bool(np.allclose(got, want, rtol=1e-4, atol=1e-5))
             e = torch.randint(0, nnz, (4096,), device=device)
             row = torch.searchsorted(indptr.long(), e, right=True) - 1
-            want = (a.view(n, f)[row].double() * b.view(n, f)[indices[e].long()].double()).sum(1) * scale[e].double()
-            err = (c_full[e].double() - want).abs().max().item()
+            ref = (a.view(n, f)[row].double() * b.view(n, f)[indices[e].long()].double()).sum(1) * scale[e].double()
+            err = (c_full[e].double() - ref).abs().max().item()
+            ok = ok and err < 1e-4
             out["spot_check_max_abs_err"] = err
-            assert err < 1e-4, err
-        del a, b
+        del a, b, calls
+    out["every_rank_matches_oracle"] = _all_ranks_ok(ok, device)
+    assert out["every_rank_matches_oracle"], "a rank's SDDMM positions differ from the oracle"
+    return out
+
+
+def bench_bsrmm_sharded(device, peaks, rank: int, world: int) -> dict:
+    """Config 4 cut into block rows balanced by stored blocks; every rank checks its block rows
+    against the oracle.  A call of a few microseconds: the figures show the latency floor."""
+    import torch.distributed as dist
+
+    from oracle import oracle as orc
+    from . import sharded
+
+    bs = dg.bsr_mask(seed=0)
+    feat = 512
+    op = sharded.ShardedBsrmm(bs.indptr, bs.indices, bs.data, bs.nb, bs.blk, device=device)
+    b_host = dg.dense_operand_normal(1, bs.nb * bs.blk, feat)
+    b = torch.from_numpy(b_host.astype(np.float16).reshape(-1)).to(device)
+    c_loc = torch.zeros(op.block_rows * bs.blk * feat, device=device)
+    c_all = torch.empty(bs.mb * bs.blk * feat, device=device)
+    call = op.prepare(b, c_loc, feat)
+    run = (lambda: call()) if call is not None else (lambda: None)
+    dist.barrier()
+    ms = _max_over_ranks(_time(run, number=100), device)
+
+    def with_gather():
+        run()
+        op.gather(c_loc, feat, c_all)
+        op.wait()
+
+    dist.barrier()
+    ms_g = _max_over_ranks(_time(with_gather, number=20), device)
+    torch.cuda.synchronize()
+    s = op.shard
+    ok = True
+    if op.block_rows > 0:
+        want = orc.bsrmm_f16(s.data, b_host, s.indptr, s.indices, op.block_rows, bs.nb, bs.blk, feat, omp=True)
+        ok = bool(np.allclose(c_loc.cpu().numpy().reshape(want.shape), want, rtol=1e-2, atol=1e-2))
+        lo = s.row0 * bs.blk * feat
+        ok = ok and bool(torch.equal(c_all[lo:lo + c_loc.numel()], c_loc))
+    flops = 2.0 * bs.nnzb * bs.blk * bs.blk * feat
+    res = {"workload": "bsr_spmm_4096_blk32_10pct_F512_f16", "block_rows_per_rank": [r // bs.blk for r in op.rows_per_rank],
+           "ms": ms, "gflops": flops / (ms * 1e-3) / 1e9, "ms_with_allgather": ms_g,
+           "every_rank_matches_oracle": _all_ranks_ok(ok, device)}
+    assert res["every_rank_matches_oracle"], "a rank's BSR block rows differ from the oracle"
+    return res
+
+
+def bench_rgms_sharded(device, peaks, rank: int, world: int) -> dict:
+    """Config 5 cut by destination rows balanced by edges (one writer per output row); every rank
+    checks its rows against the oracle."""
+    import torch.distributed as dist
+
+    from oracle import oracle as orc
+    from . import sharded
+
+    cf = dg.csf_relational(seed=0)
+    feat = 64
+    op = sharded.ShardedRgms(cf.indptr_i, cf.indices_i, cf.indptr_j, cf.indices_j, cf.data, cf.m, cf.n, device=device)
+    x_host = dg.dense_operand(1, cf.n, feat)
+    w_host = dg.relation_weights(2, cf.num_rels, feat)
+    x = torch.from_numpy(x_host.reshape(-1)).to(device)
+    w = torch.from_numpy(w_host.reshape(-1)).to(device)
+    s = op.shard
+    y_loc = torch.zeros(s.num_rows * feat, device=device)
+    y_all = torch.empty(cf.m * feat, device=device)
+    call = op.prepare(w, x, y_loc)
+
+    def run():
+        y_loc.zero_()  # the operator accumulates: clearing Y is part of every call
+        if call is not None:
+            call()
+
+    dist.barrier()
+    ms = _max_over_ranks(_time(run, number=20), device)
+
+    def with_gather():
+        run()
+        op.gather(y_loc, feat, y_all)
+        op.wait()
+
+    dist.barrier()
+    ms_g = _max_over_ranks(_time(with_gather, number=10), device)
+    torch.cuda.synchronize()
+    ok = True
+    if s.num_rows > 0:
+        orc.use_all_cores()
+        want = orc.rgms(s.data, w_host, x_host, np.zeros((s.num_rows, feat), np.float32), s.indptr_i, s.indices_i,
+                        s.indptr_j, s.indices_j, s.num_rows, cf.n, cf.num_rels, feat, omp=True)
+        # the oracle's sequential fp32 sums are themselves up to 1e-5 off the float64 result
+        ok = bool(np.allclose(y_loc.cpu().numpy().reshape(want.shape), want, rtol=1e-4, atol=3e-5))
+        ok = ok and bool(torch.equal(y_all[s.row0 * feat:s.row1 * feat], y_loc))
+    flops_ref = 2.0 * cf.nnz_j * feat * feat + 2.0 * cf.nnz_j * feat
+    res = {"workload": "rgms_100k_46rel_1.5M_F64", "rows_per_rank": op.rows_per_rank,
+           "edges_rank0": int(len(s.indices_j)), "ms": ms, "gflops": flops_ref / (ms * 1e-3) / 1e9,
+           "ms_with_allgather": ms_g, "every_rank_matches_oracle": _all_ranks_ok(ok, device)}
+    assert res["every_rank_matches_oracle"], "a rank's RGMS rows differ from the oracle"
+    return res
+
+
+def run_sharded(device, peaks, rank: int, world: int, log=print) -> Dict[str, dict]:
+    """The other operators of the set on row shards, one per rank (collective)."""
+    out = {}
+    for name, fn in (("sddmm", lambda: bench_sddmm_sharded(device, peaks, rank, world)),
+                     ("bsrmm", lambda: bench_bsrmm_sharded(device, peaks, rank, world)),
+                     ("rgms", lambda: bench_rgms_sharded(device, peaks, rank, world))):
+        try:
+            out[name] = fn()
+        except Exception as e:  # keep the other operators' numbers (every rank fails or none does)
+            out[name] = {"error": repr(e)}
+        if rank == 0:
+            log(f"[opbench sharded] {name}: {out[name]}")
+        torch.cuda.empty_cache()
     return out
 
 

@@ -1,0 +1,290 @@
+"""Row-sharded operators on the GPUs of one box: shard -> replicate -> run -> gather.
+
+The reference is single-GPU; this layer is new.  Every operator of the path is independent per
+output row, so rank k of N holds a contiguous block of rows of the sparse operand with a balanced
+share of the stored entries (``dist.shard_*``), the whole dense operand, and computes the output
+rows (or per-position outputs) of its block with the single-GPU entry points.  The classes below
+package that: construction shards and uploads the structure (every rank passes the SAME whole
+matrix), ``run`` launches the shard's kernels, ``gather`` all-gathers the output blocks over NCCL
+into the full result on every rank, optionally in row chunks so that the gather of chunk k
+overlaps the kernels of chunk k + 1.  ``replicate_rows`` is the other collective of the path:
+every rank contributes an equal block of rows of the dense operand.
+
+A collective that fails (a peer that is gone, a timeout of the process group) raises
+``ShardError`` — the counterpart, in this layer, of the -1 an entry point returns.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from . import dist as sdist
+from . import format as fmt
+from . import ops
+
+
+class ShardError(RuntimeError):
+    """A collective of the sharded layer failed (time-out, lost peer, mismatched sizes)."""
+
+
+def _world(group=None) -> int:
+    return dist.get_world_size(group) if dist.is_initialized() else 1
+
+
+def _rank(group=None) -> int:
+    return dist.get_rank(group) if dist.is_initialized() else 0
+
+
+def guarded(what: str, fn: Callable, *args, **kwargs):
+    """Runs a collective; any failure of the backend becomes a ShardError that names the step."""
+    try:
+        return fn(*args, **kwargs)
+    except (ValueError, TypeError):
+        raise
+    except Exception as e:  # RuntimeError, DistBackendError, DistNetworkError ...
+        raise ShardError(f"{what} failed on rank {_rank()}: {e}") from e
+
+
+def row_block(num_rows: int, world: int) -> int:
+    """Rows per rank of the equal-block layout used to replicate a dense operand: every rank owns
+    ``row_block`` rows (the last ones may own fewer real rows; the buffer is padded)."""
+    return -(-int(num_rows) // int(world))
+
+
+def replicate_rows(local_rows: torch.Tensor, full: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather of EQUAL row blocks: ``local_rows`` is this rank's ``[row_block * feat]`` piece,
+    ``full`` the ``[world * row_block * feat]`` buffer that holds the whole (padded) operand
+    afterwards.  One NCCL all-gather, in place."""
+    world = _world(group)
+    if world == 1:
+        if full.data_ptr() != local_rows.data_ptr():
+            full[:local_rows.numel()].copy_(local_rows)
+        return full
+    if full.numel() != world * local_rows.numel():
+        raise ValueError("replicate_rows: full must hold world equal blocks")
+    guarded("replicate_rows (all-gather of the dense operand)", dist.all_gather_into_tensor,
+            full, local_rows.contiguous(), group=group)
+    return full
+
+
+class _Gatherer:
+    """All-gather of per-rank output blocks cut into chunks, issued on a side stream so that it
+    overlaps whatever the caller launches next."""
+
+    def __init__(self, device: torch.device):
+        self.stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
+        self.pending: List = []
+
+    def gather(self, local: torch.Tensor, sizes: Sequence[int], out: torch.Tensor, offsets: Sequence[int],
+               group=None) -> None:
+        """Blocks of ``sizes[k]`` elements, rank k's going to ``out[offsets[k]:offsets[k]+sizes[k]]``;
+        runs after everything queued so far on the current stream."""
+        world = _world(group)
+        pieces = [out[int(o):int(o) + int(s)] for o, s in zip(offsets, sizes)]
+        if world == 1:
+            if pieces[0].data_ptr() != local.data_ptr():
+                pieces[0].copy_(local)
+            return
+        if local.numel() != sizes[_rank(group)]:
+            raise ValueError(f"rank {_rank(group)}: local block has {local.numel()} elements, "
+                             f"expected {sizes[_rank(group)]}")
+        if self.stream is None or min(int(s) for s in sizes) == 0:
+            # CPU ranks (gloo) and degenerate cuts: the broadcast-based path of the base layer
+            tmp = guarded("all-gather of the output blocks", sdist.all_gather_blocks, local, sizes, group=group)
+            for p, t in zip(pieces, torch.split(tmp, [int(s) for s in sizes])):
+                if p.data_ptr() != t.data_ptr():
+                    p.copy_(t)
+            return
+        done = torch.cuda.Event()
+        done.record()
+        with torch.cuda.stream(self.stream):
+            self.stream.wait_event(done)
+            # unequal blocks straight into place: NCCL runs them as one group of broadcasts
+            work = guarded("all-gather of the output blocks", dist.all_gather, pieces, local,
+                           group=group, async_op=True)
+        self.pending.append(work)
+
+    def wait(self) -> None:
+        """Makes the current stream wait for every gather issued so far."""
+        for w in self.pending:
+            guarded("all-gather of the output blocks", w.wait)
+        self.pending.clear()
+
+
+def _dev(a, device) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).to(device)
+
+
+class ShardedHybSpmm:
+    """Y = A X with A decomposed into the hyb format shard by shard."""
+
+    def __init__(self, indptr, indices, data, num_cols: int, buckets: Sequence[int], parts: int = 1,
+                 device: Optional[torch.device] = None, group=None):
+        self.group, self.world, self.rank = group, _world(group), _rank(group)
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.num_rows_total = len(indptr) - 1
+        self.num_cols = int(num_cols)
+        self.shard = sdist.shard_csr(indptr, indices, data, num_cols, self.world, self.rank)
+        rows, cols, mask, vals, _ = fmt.column_part_hyb(self.shard.num_rows, num_cols, self.shard.indptr,
+                                                       self.shard.indices, parts, list(buckets),
+                                                       data=self.shard.data)
+        self.buckets = [(_dev(vals[p][b], self.device), _dev(rows[p][b], self.device), _dev(cols[p][b], self.device))
+                        for p in range(parts) for b in range(len(buckets))]
+        from . import _lib as L
+        self.flags = (L.HYB_REARM | L.HYB_ALL_ATOMIC) if parts > 1 else 0
+        self.rows_per_rank = self.shard.rows_per_rank()
+        self.row_offsets = [int(c) for c in self.shard.cuts[:-1]]
+        self.referenced_cols = int(np.unique(self.shard.indices).size)
+        self._gatherer = _Gatherer(self.device)
+
+    def prepare(self, x: torch.Tensor, y_local: torch.Tensor, feat: int) -> ops.PreparedCall:
+        """The shard's call: ``x`` is the whole dense operand ``[num_cols * feat]`` on this GPU,
+        ``y_local`` the ``[shard rows * feat]`` output block (zero-filled once by the caller)."""
+        return ops.hyb_spmm.prepare(*ops.hyb_args(x, y_local, self.buckets, feat, self.flags))
+
+    def gather(self, y_local: torch.Tensor, feat: int, out: torch.Tensor) -> None:
+        """Queues the all-gather of the output rows into ``out [num_rows_total * feat]`` behind the
+        work queued so far; ``wait()`` orders later work after it."""
+        self._gatherer.gather(y_local, [r * feat for r in self.rows_per_rank], out,
+                              [o * feat for o in self.row_offsets], self.group)
+
+    def wait(self) -> None:
+        self._gatherer.wait()
+
+
+class ShardedSddmm:
+    """out[p] = scale[p] * <A[row(p)], B[col(p)]> over the stored positions of the shard's rows,
+    the rows cut into ``chunks`` pieces (balanced by stored positions) so that the all-gather of
+    one piece overlaps the kernels of the next."""
+
+    def __init__(self, indptr, indices, scale, num_cols: int, chunks: int = 4,
+                 device: Optional[torch.device] = None, group=None):
+        self.group, self.world, self.rank = group, _world(group), _rank(group)
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        on_device = isinstance(indptr, torch.Tensor)
+        ip_host = indptr.cpu().numpy() if on_device else np.ascontiguousarray(indptr, dtype=np.int32)
+        self.num_rows_total, self.num_cols = len(ip_host) - 1, int(num_cols)
+        self.nnz_total = int(ip_host[-1])
+        cuts = fmt.row_partition(ip_host, self.world)
+        self.cuts = cuts
+        self.row0, self.row1 = int(cuts[self.rank]), int(cuts[self.rank + 1])
+        chunks = max(1, int(chunks)) if self.world > 1 else 1
+        # every rank needs every rank's chunk boundaries (sizes and offsets of the gathered pieces)
+        self.chunk_sizes: List[List[int]] = [[] for _ in range(chunks)]
+        self.chunk_offsets: List[List[int]] = [[] for _ in range(chunks)]
+        my_rows: List[int] = []
+        for k in range(self.world):
+            r0, r1 = int(cuts[k]), int(cuts[k + 1])
+            sub = fmt.row_partition((ip_host[r0:r1 + 1] - ip_host[r0]).astype(np.int32), chunks)
+            for c in range(chunks):
+                a, b = r0 + int(sub[c]), r0 + int(sub[c + 1])
+                self.chunk_sizes[c].append(int(ip_host[b] - ip_host[a]))
+                self.chunk_offsets[c].append(int(ip_host[a]))
+            if k == self.rank:
+                my_rows = [r0 + int(s) for s in sub]
+        self.chunk_rows = my_rows  # chunks + 1 global row numbers
+        to_dev = (lambda t: t.to(self.device)) if on_device else (lambda a: _dev(a, self.device))
+        self._ip, self._ix, self._scale = [], [], []
+        for c in range(chunks):
+            a, b = my_rows[c], my_rows[c + 1]
+            p0, p1 = int(ip_host[a]), int(ip_host[b])
+            self._ip.append(_dev((ip_host[a:b + 1] - ip_host[a]).astype(np.int32), self.device))
+            self._ix.append(to_dev(indices[p0:p1]).contiguous())
+            self._scale.append(None if scale is None else to_dev(scale[p0:p1]).contiguous())
+        self.chunks = chunks
+        self._gatherer = _Gatherer(self.device)
+
+    def prepare(self, a: torch.Tensor, b: torch.Tensor, out_full: torch.Tensor, feat: int) -> List[ops.PreparedCall]:
+        """One call per chunk: ``a`` is the whole row-side operand ``[num_rows_total * feat]`` (only
+        the shard's rows are read), ``b`` the replicated column-side operand, ``out_full`` the
+        ``[nnz_total]`` result; each chunk writes its own range of it."""
+        calls = []
+        for c in range(self.chunks):
+            r0, r1 = self.chunk_rows[c], self.chunk_rows[c + 1]
+            off, size = self.chunk_offsets[c][self.rank], self.chunk_sizes[c][self.rank]
+            args = [a[r0 * feat:r1 * feat], b, out_full[off:off + size], self._ip[c], self._ix[c]]
+            if self._scale[c] is not None:
+                args.append(self._scale[c])
+            calls.append(ops.sddmm.prepare(*args) if size > 0 else None)
+        return calls
+
+    def run(self, calls: List, out_full: Optional[torch.Tensor] = None) -> None:
+        """Launches the chunks in order; with ``out_full`` every chunk's all-gather is queued right
+        behind its kernels (call ``wait()`` before reading other ranks' parts)."""
+        for c, call in enumerate(calls):
+            if call is not None:
+                call()
+            if out_full is not None and self.world > 1:
+                off, size = self.chunk_offsets[c][self.rank], self.chunk_sizes[c][self.rank]
+                self._gatherer.gather(out_full[off:off + size], self.chunk_sizes[c], out_full,
+                                      self.chunk_offsets[c], self.group)
+
+    def wait(self) -> None:
+        self._gatherer.wait()
+
+
+class ShardedBsrmm:
+    """C = A B for a BSR matrix cut into block rows balanced by stored blocks."""
+
+    def __init__(self, indptr, indices, blocks, num_block_cols: int, blk: int,
+                 device: Optional[torch.device] = None, group=None):
+        self.group, self.world, self.rank = group, _world(group), _rank(group)
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.blk, self.num_block_cols = int(blk), int(num_block_cols)
+        self.shard = sdist.shard_bsr(indptr, indices, blocks, self.world, self.rank)
+        self.block_rows_total = len(indptr) - 1
+        self.block_rows = self.shard.row1 - self.shard.row0
+        self.nnzb = len(self.shard.indices)
+        self._a = _dev(self.shard.data.reshape(-1), self.device)
+        self._ip, self._ix = _dev(self.shard.indptr, self.device), _dev(self.shard.indices, self.device)
+        self.rows_per_rank = [int(self.shard.cuts[k + 1] - self.shard.cuts[k]) * self.blk for k in range(self.world)]
+        self.row_offsets = [int(c) * self.blk for c in self.shard.cuts[:-1]]
+        self._gatherer = _Gatherer(self.device)
+
+    def prepare(self, b: torch.Tensor, c_local: torch.Tensor, feat: int) -> Optional[ops.PreparedCall]:
+        if self.block_rows == 0:
+            return None
+        return ops.bsrmm.prepare(self._a, b, c_local, self._ip, self._ix, self.block_rows,
+                                 self.num_block_cols, self.nnzb, self.blk, feat)
+
+    def gather(self, c_local: torch.Tensor, feat: int, out: torch.Tensor) -> None:
+        self._gatherer.gather(c_local, [r * feat for r in self.rows_per_rank], out,
+                              [o * feat for o in self.row_offsets], self.group)
+
+    def wait(self) -> None:
+        self._gatherer.wait()
+
+
+class ShardedRgms:
+    """Y = sum_r A_r X W_r cut by destination rows (balanced by edges): one writer per output row,
+    no reduction across GPUs."""
+
+    def __init__(self, indptr_i, indices_i, indptr_j, indices_j, data, num_rows: int, num_cols: int,
+                 device: Optional[torch.device] = None, group=None):
+        self.group, self.world, self.rank = group, _world(group), _rank(group)
+        self.device = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.num_rows_total, self.num_cols = int(num_rows), int(num_cols)
+        self.shard = sdist.shard_rgms(indptr_i, indices_i, indptr_j, indices_j, data, num_rows,
+                                      self.world, self.rank)
+        s = self.shard
+        self._arrays = [_dev(v, self.device) for v in (s.data, s.indptr_i, s.indices_i, s.indptr_j, s.indices_j)]
+        self.rows_per_rank = [int(s.cuts[k + 1] - s.cuts[k]) for k in range(self.world)]
+        self.row_offsets = [int(c) for c in s.cuts[:-1]]
+        self._gatherer = _Gatherer(self.device)
+
+    def prepare(self, w: torch.Tensor, x: torch.Tensor, y_local: torch.Tensor) -> Optional[ops.PreparedCall]:
+        """``y_local [shard rows * feat]`` is accumulated into (zero-fill it first)."""
+        if self.shard.num_rows == 0 or len(self.shard.indices_i) == 0:
+            return None
+        a, ip_i, ix_i, ip_j, ix_j = self._arrays
+        return ops.rgms.prepare(a, w, x, y_local, ip_i, ix_i, ip_j, ix_j)
+
+    def gather(self, y_local: torch.Tensor, feat: int, out: torch.Tensor) -> None:
+        self._gatherer.gather(y_local, [r * feat for r in self.rows_per_rank], out,
+                              [o * feat for o in self.row_offsets], self.group)
+
+    def wait(self) -> None:
+        self._gatherer.wait()

@@ -362,7 +362,7 @@ def ours_arm(args, rank, world, local_rank):
     # its gather (half of all bytes) overlaps the kernels of the others.
     gather_ms = nvlink = y_all = None
     if world > 1:
-        y_all = {f: torch.empty(g.m * f, device=device) for f in FEATS}
+        y_all = {f: sharded.peer_empty(g.m * f, torch.float32, device) for f in FEATS}
         order = tuple(sorted(FEATS, reverse=True))
 
         def gather_step():
@@ -377,6 +377,8 @@ def ours_arm(args, rank, world, local_rank):
         nvlink = {"bound": "nvlink", "achieved": recv_max / (gather_ms * 1e-3) / 1e9, "peak": NVLINK_GBS,
                   "unit": "GB/s", "frac": recv_max / (gather_ms * 1e-3) / 1e9 / NVLINK_GBS,
                   "bytes_received_per_gpu_per_step": recv_max,
+                  "transport": ("peer writes over NVLink, one copy per peer (symmetric memory)"
+                                if isinstance(y_all[FEATS[0]], sharded.PeerOutput) else "NCCL all-gather"),
                   "note": "every GPU must receive the other shards' rows of Y: these bytes over the "
                           "measured 770 GB/s per direction are the floor of this step"}
     value_ms = gather_ms if world > 1 else kernel_ms
@@ -473,7 +475,8 @@ def ours_arm(args, rank, world, local_rank):
         got = y_host[f_chk].numpy().reshape(m_loc, f_chk)
         np.testing.assert_allclose(got, want[shard.row0:shard.row1], rtol=1e-4, atol=1e-5)
         if world > 1:
-            np.testing.assert_allclose(y_all[f_chk].cpu().numpy().reshape(g.m, f_chk), want, rtol=1e-4, atol=1e-5)
+            np.testing.assert_allclose(sharded.local_tensor(y_all[f_chk]).cpu().numpy().reshape(g.m, f_chk), want,
+                                       rtol=1e-4, atol=1e-5)
     except AssertionError as e:
         ok = False
         log(f"bench.py: rank {rank}: result differs from the oracle: {str(e)[:400]}")

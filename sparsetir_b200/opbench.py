@@ -255,12 +255,14 @@ def bench_sddmm_sharded(device, peaks, rank: int, world: int, feats=(32, 128)) -
     n = 232_965
     indptr, indices, scale, nnz = sddmm_graph_on_device(device)
     op = sharded.ShardedSddmm(indptr, indices, scale, n, chunks=4, device=device)
-    c_full = torch.empty(nnz, device=device)
+    c_out = sharded.peer_empty(nnz, torch.float32, device)
+    c_full = sharded.local_tensor(c_out)
     gen = torch.Generator(device=device)
     gen.manual_seed(1)
     out = {"workload": "sddmm_lognormal_232965", "nnz": nnz,
            "graph": "built on the GPU with a torch generator: the twin of datagen.csr_lognormal(seed=0) "
                     "(same degree sequence, other column draws)",
+           "transport": "peer writes over NVLink" if isinstance(c_out, sharded.PeerOutput) else "NCCL",
            "rows_per_rank": [int(op.cuts[k + 1] - op.cuts[k]) for k in range(world)],
            "nnz_per_rank": [sum(op.chunk_sizes[c][k] for c in range(op.chunks)) for k in range(world)],
            "chunks": op.chunks, "per_feat": {}}
@@ -268,14 +270,14 @@ def bench_sddmm_sharded(device, peaks, rank: int, world: int, feats=(32, 128)) -
     for f in feats:
         a = torch.rand(n * f, device=device, generator=gen) * 2 - 1
         b = torch.rand(n * f, device=device, generator=gen) * 2 - 1
-        calls = op.prepare(a, b, c_full, f)
+        calls = op.prepare(a, b, c_out, f)
         dist.barrier()
         mine = _time(lambda: op.run(calls), number=3, repeat=3, warmup=2)
         ms = _max_over_ranks(mine, device)
         ms_min = -_max_over_ranks(-mine, device)
 
         def with_gather():
-            op.run(calls, c_full)
+            op.run(calls, c_out)
             op.wait()
 
         dist.barrier()
@@ -338,7 +340,8 @@ def bench_bsrmm_sharded(device, peaks, rank: int, world: int) -> dict:
     b_host = dg.dense_operand_normal(1, bs.nb * bs.blk, feat)
     b = torch.from_numpy(b_host.astype(np.float16).reshape(-1)).to(device)
     c_loc = torch.zeros(op.block_rows * bs.blk * feat, device=device)
-    c_all = torch.empty(bs.mb * bs.blk * feat, device=device)
+    c_out = sharded.peer_empty(bs.mb * bs.blk * feat, torch.float32, device)
+    c_all = sharded.local_tensor(c_out)
     call = op.prepare(b, c_loc, feat)
     run = (lambda: call()) if call is not None else (lambda: None)
     dist.barrier()
@@ -346,7 +349,7 @@ def bench_bsrmm_sharded(device, peaks, rank: int, world: int) -> dict:
 
     def with_gather():
         run()
-        op.gather(c_loc, feat, c_all)
+        op.gather(c_loc, feat, c_out)
         op.wait()
 
     dist.barrier()
@@ -384,7 +387,8 @@ def bench_rgms_sharded(device, peaks, rank: int, world: int) -> dict:
     w = torch.from_numpy(w_host.reshape(-1)).to(device)
     s = op.shard
     y_loc = torch.zeros(s.num_rows * feat, device=device)
-    y_all = torch.empty(cf.m * feat, device=device)
+    y_out = sharded.peer_empty(cf.m * feat, torch.float32, device)
+    y_all = sharded.local_tensor(y_out)
     call = op.prepare(w, x, y_loc)
 
     def run():
@@ -397,7 +401,7 @@ def bench_rgms_sharded(device, peaks, rank: int, world: int) -> dict:
 
     def with_gather():
         run()
-        op.gather(y_loc, feat, y_all)
+        op.gather(y_loc, feat, y_out)
         op.wait()
 
     dist.barrier()

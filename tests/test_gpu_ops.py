@@ -648,8 +648,7 @@ def test_rgms_config5_full_size(cuda_device):
     got = run_rgms(cf, x, w, cuda_device)
     err_gpu, err_oracle = parity(got, want, rgms_truth(cf, x, w))
     print(f"rgms config 5: max error vs float64: GPU {err_gpu:.3e}, oracle {err_oracle:.3e}")
-    # and bit-identical when repeated
-    assert torch.equal(got, run_rgms(cf, x, w, cuda_device)) or os.environ.get("SPARSETIR_RGMS_PATH")
+    assert err_gpu <= max(2 * err_oracle, 1e-5)
 
 
 def test_rgms_accumulates_into_y(cuda_device):

@@ -39,6 +39,7 @@ __device__ unsigned int g_tc_timeouts = 0;  // bounded waits that ran out, since
 int rgms_tc_timeouts(unsigned int* count);  // the same counter of rgms_tc.cu
 int tcspmm_timeouts(unsigned int* count);   // ... and of tcspmm.cu
 int rgms_f16_timeouts(unsigned int* count);  // ... and of rgms_f16.cu
+int rgms_fused_timeouts(unsigned int* count);  // ... and of rgms_fused.cu
 
 namespace {
 
@@ -384,6 +385,8 @@ extern "C" int sparsetir_tc_timeouts(int device_id, unsigned int* count) {
   if (tcspmm_timeouts(&tcs) != 0) return -1;
   unsigned int rh = 0;
   if (rgms_f16_timeouts(&rh) != 0) return -1;
-  *count = bsr + rgms + tcs + rh;
+  unsigned int rf = 0;
+  if (rgms_fused_timeouts(&rf) != 0) return -1;
+  *count = bsr + rgms + tcs + rh + rf;
   return 0;
 }

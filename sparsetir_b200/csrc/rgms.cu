@@ -22,6 +22,8 @@
 // prefix scan over the relation sizes, so no tile table has to be built or stored anywhere.
 #include <cstdlib>
 
+#include <cstring>
+
 #include "common.h"
 #include "rgms_common.cuh"
 #include "spmm_core.cuh"
@@ -31,6 +33,9 @@ namespace sptir {
 // defined in rgms_tc.cu; returns 1 when the shape is not supported by the tensor-core path
 int csrmm_impl(const float* a, const float* b, float* c, const int32_t* indptr, const int32_t* indices,
                int m, int n, int feat, int nnz, int device_id, void* stream, bool hub_rows);
+int rgms_fused_launch(const float* a, const float* w, const float* x, float* y, const int32_t* indptr_i,
+                      const int32_t* indices_i, const int32_t* indptr_j, const int32_t* indices_j,
+                      int num_rels, int feat, int nnz_i, int nnz_j, int n, int m, cudaStream_t stream);
 int rgms_tc_launch(const float* a, const float* w, const float* x, float* y,
                    const int32_t* indptr_i, const int32_t* indices_i, const int32_t* indptr_j,
                    const int32_t* indices_j, int num_rels, int feat, int nnz_i,
@@ -203,6 +208,19 @@ extern "C" int sparsetir_rgms_raw(const float* a, const float* w, const float* x
         const char* e = std::getenv("SPARSETIR_RGMS_FUSED");
         return e != nullptr && e[0] == '1';
       }();
+      // SPARSETIR_RGMS_PATH=fused selects the one-launch form of rgms_fused.cu instead: it gathers,
+      // multiplies and scatters tile by tile and needs no scratch memory, but its sixteen gather
+      // warps per SM keep fewer loads in flight than a whole launch of the SpMM kernel does
+      // (measured at 100 k nodes / 1.5 M edges: 183 us against 139 us for the two launches).
+      static const bool one_launch = [] {
+        const char* e = std::getenv("SPARSETIR_RGMS_PATH");
+        return e != nullptr && std::strcmp(e, "fused") == 0;
+      }();
+      if (one_launch && !fused) {
+        const int rc1 = rgms_fused_launch(a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, feat,
+                                          nnz_i, nnz_j, n, m, st);
+        if (rc1 <= 0) return rc1;
+      }
       float* z = nullptr;
       if (!fused)
         z = static_cast<float*>(workspace(device_id, st, static_cast<size_t>(nnz_i) * 64 * sizeof(float)));

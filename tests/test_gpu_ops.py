@@ -651,6 +651,28 @@ def test_rgms_config5_full_size(cuda_device):
     assert err_gpu <= max(2 * err_oracle, 1e-5)
 
 
+def test_rgms_one_launch_form_in_child_process(cuda_device, tmp_path):
+    # SPARSETIR_RGMS_PATH=fused (read once per process): gather, 3xTF32 product and scatter in one
+    # persistent launch without scratch memory.  Same parity bar; tiles with more entries than the
+    # staging buffer holds (a relation whose rows have ~40 entries) and many tiny relations included.
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    code = ("import sys; sys.path.insert(0, %r); sys.path.insert(0, %r)\n"
+            "import ctypes, numpy as np, torch, test_gpu_ops as T\n"
+            "from sparsetir_b200 import _lib as L, datagen as dg\n"
+            "d = torch.device('cuda', 0)\n"
+            "for n, rels, edges, seed in ((3000, 11, 40000, 64), (300, 3, 30000, 12), (500, 300, 3000, 3), (30000, 13, 260001, 21)):\n"
+            "    cf = dg.csf_relational(n=n, num_rels=rels, num_edges=edges, seed=seed)\n"
+            "    x = dg.dense_operand(1, cf.n, 64); w = dg.relation_weights(2, cf.num_rels, 64)\n"
+            "    T.parity(T.run_rgms(cf, x, w, d), T.oracle_rgms(cf, x, w), T.rgms_truth(cf, x, w))\n"
+            "k = ctypes.c_uint(9); assert L.load().sparsetir_tc_timeouts(0, ctypes.byref(k)) == 0 and k.value == 0\n"
+            "print('one launch ok')" % (root, os.path.join(root, "tests")))
+    r = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, SPARSETIR_RGMS_PATH="fused"),
+                       capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "one launch ok" in r.stdout, r.stdout + r.stderr
+
+
 def test_rgms_accumulates_into_y(cuda_device):
     cf = dg.csf_relational(n=400, num_rels=4, num_edges=3000, seed=6)
     x = dg.dense_operand(7, cf.n, 64)

@@ -304,6 +304,8 @@ SPARSETIR_API int sparsetir_bsrmm_raw(const void* a_f16, const void* b_f16, floa
                                       const int32_t* indptr, const int32_t* indices, int nb,
                                       int mb, int nnzb, int blk, int feat, int device_id,
                                       void* stream);
+/* Scratch bytes sparsetir_rgms(_raw) uses (see sparsetir_reserve_workspace; no counters). */
+SPARSETIR_API int sparsetir_rgms_workspace(int feat, int nnz_i, size_t* scratch_bytes);
 SPARSETIR_API int sparsetir_rgms_raw(const float* a, const float* w, const float* x, float* y,
                                      const int32_t* indptr_i, const int32_t* indices_i,
                                      const int32_t* indptr_j, const int32_t* indices_j, int m,

@@ -105,6 +105,7 @@ PLAIN_SYMBOLS = {
     "sparsetir_sddmm_edge_to_row_raw": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "sparsetir_bsrmm_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_raw": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),
+    "sparsetir_rgms_workspace": (_i, [_i, _i, ctypes.POINTER(ctypes.c_size_t)]),
     "sparsetir_csr_reduce_raw": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "sparsetir_sparse_softmax_raw": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp]),
     "sparsetir_csr2bsr_raw": (_i, [_vp] * 6 + [_i, _i, _i, _i, _vp]),

@@ -178,6 +178,13 @@ int launch_tile(const float* a, const float* w, const float* x, float* y, const 
 }  // namespace
 }  // namespace sptir
 
+extern "C" int sparsetir_rgms_workspace(int feat, int nnz_i, size_t* scratch_bytes) {
+  if (!scratch_bytes || feat < 0 || nnz_i < 0) return sptir::fail("sparsetir_rgms_workspace: bad argument");
+  // the two-launch form keeps one aggregated feature row per (relation, destination) pair
+  *scratch_bytes = feat == 64 ? static_cast<size_t>(nnz_i) * 64 * sizeof(float) : 0;
+  return 0;
+}
+
 extern "C" int sparsetir_rgms_raw(const float* a, const float* w, const float* x, float* y,
                                   const int32_t* indptr_i, const int32_t* indices_i,
                                   const int32_t* indptr_j, const int32_t* indices_j, int m, int n,

@@ -309,6 +309,207 @@ bsrmm_tma_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   if (warp == 0) tc05::tmem_dealloc(tmem, kTmemCols);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Persistent variant (the default when feat is a multiple of 256): at 128 x 128 blocks and 512
+// features the kernel above is 512 short-lived thread blocks, and what a call costs is mostly what
+// every one of them pays before and after its dozen tile loads: barrier set-up, TMEM allocation,
+// the first load's latency with nothing to overlap it, an epilogue nothing overlaps either.  Here
+// one block per SM walks work items (block row, 256 features), so that
+//   - barriers and TMEM are set up once per SM,
+//   - the producer warp runs ahead across item boundaries: while the tensor core finishes one
+//     item, the tiles of the next are already landing (8 stages of 18 KB),
+//   - two TMEM accumulators alternate, so the epilogue of an item (TMEM -> registers -> 32
+//     coalesced row stores per warp) overlaps the loads and MMAs of the next,
+//   - the A block of a stored block is loaded once for two feature tiles.
+// Roles: warp 0 producer (TMA), warp 1 MMA issuer, warps 2-5 epilogue (a warp reads the TMEM lanes
+// 32 * (warp % 4) .. + 31: lane = feature inside the tile, column = row inside the block row).
+// Every mbarrier wait is bounded.
+constexpr int kPThreads = 192;
+constexpr int kPTiles = 2;                              // feature tiles of 128 per work item
+constexpr int kPStageBytes = kPTiles * kBBytes + kABytes;  // 18 KB
+constexpr int kPStages = 6;
+constexpr int kPSmem = kPStages * kPStageBytes + 1024;
+constexpr uint32_t kPAccCols = kPTiles * kBlk;          // 64 TMEM columns per accumulator
+
+__global__ void __launch_bounds__(kPThreads, 2)
+bsrmm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                     float* __restrict__ c, const int32_t* __restrict__ indptr,
+                     const int32_t* __restrict__ indices, int feat, int num_items, int items_per_row) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ __align__(8) uint64_t bar_full[kPStages];   // operands of the stage have landed
+  __shared__ __align__(8) uint64_t bar_empty[kPStages];  // the tensor core has read the stage
+  __shared__ __align__(8) uint64_t bar_acc_full[2];      // accumulator holds a finished item
+  __shared__ __align__(8) uint64_t bar_acc_empty[2];     // the epilogue has read it (128 arrivals)
+  __shared__ uint32_t s_tmem;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  unsigned char* tiles = smem_raw + ((1024u - (tc05::smem_u32(smem_raw) & 1023u)) & 1023u);
+
+  if (tid == 0) {
+    for (int s = 0; s < kPStages; ++s) {
+      tc05::mbar_init(&bar_full[s], 1);
+      tc05::mbar_init(&bar_empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      tc05::mbar_init(&bar_acc_full[b], 1);
+      tc05::mbar_init(&bar_acc_empty[b], 128);
+    }
+    tc05::fence_mbar_init();
+    tc05::prefetch_tensormap(&tm_a);
+    tc05::prefetch_tensormap(&tm_b);
+  }
+  if (warp == 0) tc05::tmem_alloc(&s_tmem, 2 * kPAccCols);
+  tc05::fence_before_sync();
+  __syncthreads();
+  tc05::fence_after_sync();
+  const uint32_t tmem = s_tmem;
+  bool ok = true;
+  int armed = 0;  // producer: stored blocks whose loads have been issued
+
+  if (warp == 0) {
+    // ---- producer: one stage per stored block, across item boundaries
+    int bk = 0;  // stored blocks issued so far by this thread block
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const int i = item / items_per_row, f0 = (item % items_per_row) * (kPTiles * kTileF);
+      const int p0 = __ldg(indptr + i), nblk = __ldg(indptr + i + 1) - p0;
+      int cols = 0;
+      for (int it = 0; it < nblk; ++it, ++bk) {
+        const int stage = bk % kPStages, use = bk / kPStages;
+        if ((it & 31) == 0) cols = (it + lane < nblk) ? __ldg(indices + p0 + it + lane) : 0;
+        const int col = __shfl_sync(0xffffffffu, cols, it & 31);
+        if (use > 0) {
+          if (lane == 0) ok = tc05::mbar_wait(&bar_empty[stage], (use - 1) & 1);
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) break;
+        }
+        if (lane == 0) {
+          unsigned char* st = tiles + stage * kPStageBytes;
+          tc05::mbar_arrive_expect_tx(&bar_full[stage], kPStageBytes);
+#pragma unroll
+          for (int tt = 0; tt < kPTiles; ++tt) {
+            tc05::tma_load_2d(st + tt * kBBytes, &tm_b, f0 + tt * kTileF, col * kBlk, &bar_full[stage]);
+            tc05::tma_load_2d(st + tt * kBBytes + kBBytes / 2, &tm_b, f0 + tt * kTileF + 64, col * kBlk, &bar_full[stage]);
+          }
+          tc05::tma_load_2d(st + kPTiles * kBBytes, &tm_a, 0, (p0 + it) * kBlk, &bar_full[stage]);
+        }
+        armed = bk + 1;
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer
+    constexpr uint32_t idesc = tc05::instr_desc(tc05::kFmtF16, kTileF, kBlk, /*a_mn=*/1, /*b_mn=*/0);
+    // B tile, MN-major: 16 K rows of 128 bytes per step; the two 64-feature atoms are 4 KB apart
+    const uint64_t da0 = tc05::smem_desc_swizzled(tc05::smem_u32(tiles), kBBytes / 2, 1024, tc05::kSwizzle128B);
+    // A block, K-major: rows of 64 bytes, 16 columns (32 bytes) per step inside the row
+    const uint64_t db0 = tc05::smem_desc_swizzled(tc05::smem_u32(tiles) + kPTiles * kBBytes, 0, 512, tc05::kSwizzle64B);
+    int bk = 0, acc_it = 0;  // stored blocks / non-empty items so far
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const int i = item / items_per_row;
+      const int nblk = __ldg(indptr + i + 1) - __ldg(indptr + i);
+      if (nblk <= 0) continue;
+      const int buf = acc_it & 1, buse = acc_it >> 1;
+      if (buse > 0) {
+        if (lane == 0) ok = tc05::mbar_wait(&bar_acc_empty[buf], (buse - 1) & 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+      }
+      for (int it = 0; it < nblk; ++it, ++bk) {
+        const int stage = bk % kPStages, use = bk / kPStages;
+        if (lane == 0) ok = tc05::mbar_wait(&bar_full[stage], use & 1);
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (!ok) break;
+        if (lane == 0) {
+          tc05::fence_after_sync();
+          const uint64_t db_s = tc05::desc_advance(db0, stage * kPStageBytes);
+#pragma unroll
+          for (int tt = 0; tt < kPTiles; ++tt) {
+            const uint64_t da_s = tc05::desc_advance(da0, stage * kPStageBytes + tt * kBBytes);
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks)  // K = 32 block columns = 2 x 16
+              tc05::mma_f16(tmem + buf * kPAccCols + tt * kBlk, tc05::desc_advance(da_s, ks * 16 * 128),
+                            tc05::desc_advance(db_s, ks * 32), idesc, (it > 0 || ks > 0) ? 1u : 0u);
+          }
+          tc05::mma_commit(&bar_empty[stage]);
+          if (it == nblk - 1) tc05::mma_commit(&bar_acc_full[buf]);
+        }
+        __syncwarp();
+      }
+      ++acc_it;
+    }
+  } else {
+    // ---- epilogue: thread = feature inside the 128-feature tile
+    const int q = warp & 3;  // TMEM lane quarter of this warp
+    int acc_it = 0;
+    for (int item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const int i = item / items_per_row, f0 = (item % items_per_row) * (kPTiles * kTileF);
+      const int nblk = __ldg(indptr + i + 1) - __ldg(indptr + i);
+      float* crow = c + (static_cast<size_t>(i) * kBlk) * feat + f0 + q * 32 + lane;
+      if (nblk <= 0) {  // empty block-row: zeros, no tensor-core work
+#pragma unroll
+        for (int tt = 0; tt < kPTiles; ++tt)
+#pragma unroll 4
+          for (int bi = 0; bi < kBlk; ++bi) crow[static_cast<size_t>(bi) * feat + tt * kTileF] = 0.f;
+        continue;
+      }
+      const int buf = acc_it & 1, buse = acc_it >> 1;
+      if (!tc05::mbar_wait(&bar_acc_full[buf], buse & 1)) { ok = false; break; }
+      tc05::fence_after_sync();
+#pragma unroll
+      for (int tt = 0; tt < kPTiles; ++tt) {
+        uint32_t r[32];
+        tc05::tmem_ld32(tmem + (static_cast<uint32_t>(q * 32) << 16) + buf * kPAccCols + tt * kBlk, r);
+        if (tt == kPTiles - 1) {  // everything of this accumulator is in registers
+          tc05::fence_before_sync();
+          asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tc05::smem_u32(&bar_acc_empty[buf])) : "memory");
+        }
+#pragma unroll
+        for (int bi = 0; bi < kBlk; ++bi)
+          __stcs(crow + static_cast<size_t>(bi) * feat + tt * kTileF, __uint_as_float(r[bi]));
+      }
+      ++acc_it;
+    }
+  }
+
+  const bool all_ok = !__syncthreads_or(!ok);
+  if (!all_ok && tid == 0) {
+    atomicAdd(&g_tc_timeouts, 1u);
+    // gave up: let the copies already issued land (bounded) before the block's memory is released
+    for (int bk = max(0, armed - kPStages); bk < armed; ++bk)
+      tc05::mbar_wait(&bar_full[bk % kPStages], (bk / kPStages) & 1);
+  }
+  tc05::fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tc05::tmem_dealloc(tmem, 2 * kPAccCols);
+}
+
+// 0 when launched, 1 when this path cannot take the call (caller falls back), -1 on error
+int bsrmm_persist_launch(const __half* a, const __half* b, float* c, const int32_t* indptr,
+                         const int32_t* indices, int nb, int mb, int nnzb, int feat, cudaStream_t stream) {
+  if (nnzb <= 0 || mb <= 0 || feat % (kPTiles * kTileF) != 0) return 1;
+  CUtensorMap tm_a, tm_b;
+  if (make_tmap_2d(&tm_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a, kBlk, static_cast<uint64_t>(nnzb) * kBlk,
+                   kBlk * 2, kBlk, kBlk, CU_TENSOR_MAP_SWIZZLE_64B) != 0)
+    return 1;
+  if (make_tmap_2d(&tm_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, b, static_cast<uint64_t>(feat),
+                   static_cast<uint64_t>(mb) * kBlk, static_cast<uint64_t>(feat) * 2, 64, kBlk,
+                   CU_TENSOR_MAP_SWIZZLE_128B) != 0)
+    return 1;
+  static thread_local int configured_device = -1;
+  int dev = 0;
+  SPTIR_CUDA_OK(cudaGetDevice(&dev));
+  if (configured_device != dev) {
+    SPTIR_CUDA_OK(cudaFuncSetAttribute(bsrmm_persist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kPSmem));
+    configured_device = dev;
+  }
+  const int items_per_row = feat / (kPTiles * kTileF);
+  const long long items = static_cast<long long>(nb) * items_per_row;
+  if (items > INT32_MAX) return 1;
+  const int grid = static_cast<int>(items < 2 * kNumSMs ? items : 2 * kNumSMs);  // two blocks per SM (shared memory)
+  bsrmm_persist_kernel<<<grid, kPThreads, kPSmem, stream>>>(tm_a, tm_b, c, indptr, indices, feat,
+                                                            static_cast<int>(items), items_per_row);
+  SPTIR_LAUNCH_OK("bsrmm_persist_kernel");
+  return 0;
+}
+
 // 0 when launched, 1 when this path cannot take the call (caller falls back), -1 on error
 int bsrmm_tma_launch(const __half* a, const __half* b, float* c, const int32_t* indptr,
                      const int32_t* indices, int nb, int mb, int nnzb, int feat, cudaStream_t stream) {
@@ -350,6 +551,15 @@ int bsrmm_tc_launch(const __half* a, const __half* b, float* c, const int32_t* i
     const char* e = std::getenv("SPARSETIR_BSR_PATH");
     return !(e && std::strcmp(e, "regs") == 0);
   }();
+  // SPARSETIR_BSR_PATH=tma keeps one thread block per (block row, 128 features)
+  static const bool persistent = [] {
+    const char* e = std::getenv("SPARSETIR_BSR_PATH");
+    return e == nullptr || e[0] == '\0';
+  }();
+  if (persistent) {
+    const int rc = bsrmm_persist_launch(a, b, c, indptr, indices, nb, mb, nnzb, feat, stream);
+    if (rc <= 0) return rc;
+  }
   if (use_tma) {
     const int rc = bsrmm_tma_launch(a, b, c, indptr, indices, nb, mb, nnzb, feat, stream);
     if (rc <= 0) return rc;

@@ -120,6 +120,18 @@ SPARSETIR_API int sparsetir_reserve_workspace(int device_id, void* stream, size_
  * a stream synchronisation per call; not usable while the stream is being captured. */
 SPARSETIR_API int sparsetir_set_validate(int on);
 
+/* Sending half of an all-gather of row shards over NVLink (no counterpart in the reference, whose
+ * operators run on one device).  Copies `bytes` bytes (a multiple of 4) at `src`, in the memory of
+ * GPU `device_id`, to each of the `n_peers` addresses in `peer_dst`: peer-mapped device pointers
+ * (CUDA IPC, cuMemMap or a symmetric-memory allocation) at which the other GPUs expect this GPU's
+ * block.  One kernel on `stream` reads the block once and stores it to every peer; it waits on
+ * nothing.  A GPU's buffer is complete once every peer's call has finished: order that between the
+ * ranks (a stream-ordered barrier such as a one-element all-reduce).  Returns 0, or -1 with the
+ * error string set. */
+#define SPARSETIR_MAX_PEERS 15
+SPARSETIR_API int sparsetir_peer_scatter(int device_id, void* stream, const void* src, size_t bytes,
+                                         int n_peers, void* const* peer_dst);
+
 /* Library version and the compute capability the kernels were compiled for (100). */
 SPARSETIR_API int sparsetir_version(void);
 SPARSETIR_API int sparsetir_sm_arch(void);

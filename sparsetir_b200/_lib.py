@@ -96,6 +96,7 @@ PLAIN_SYMBOLS = {
     "sparsetir_hyb_spmm_workspace": (_i, [ctypes.POINTER(EllBucket), _i, _i,
                                           ctypes.POINTER(ctypes.c_size_t), ctypes.POINTER(ctypes.c_size_t)]),
     "sparsetir_set_validate": (_i, [_i]),
+    "sparsetir_peer_scatter": (_i, [_i, _vp, _vp, ctypes.c_size_t, _i, ctypes.POINTER(ctypes.c_void_p)]),
     "sparsetir_version": (_i, []),
     "sparsetir_sm_arch": (_i, []),
     "sparsetir_tc_timeouts": (_i, [_i, ctypes.POINTER(ctypes.c_uint)]),

@@ -22,7 +22,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libsparsetir_b200.so")
 
 SOURCES = [
     "runtime.cc", "abi.cc", "format.cc", "validate.cu",
-    "csrmm.cu", "hyb_spmm.cu", "sddmm.cu", "bsrmm.cu", "bsrmm_tc.cu", "rgms.cu", "rgms_tc.cu", "rgms_fused.cu", "rgms_noalloc.cu", "rgms_ell3d.cu", "rgms_f16.cu", "tcspmm.cu", "csr_misc.cu", "fusedmm.cu",
+    "csrmm.cu", "hyb_spmm.cu", "sddmm.cu", "bsrmm.cu", "bsrmm_tc.cu", "rgms.cu", "rgms_tc.cu", "rgms_fused.cu", "rgms_noalloc.cu", "rgms_ell3d.cu", "rgms_f16.cu", "tcspmm.cu", "csr_misc.cu", "fusedmm.cu", "peer_scatter.cu",
 ]
 
 NVCC_FLAGS = [

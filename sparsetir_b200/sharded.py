@@ -17,6 +17,8 @@ A collective that fails (a peer that is gone, a timeout of the process group) ra
 """
 from __future__ import annotations
 
+import ctypes
+import os
 from typing import Callable, List, Optional, Sequence
 
 import numpy as np
@@ -107,6 +109,16 @@ def local_tensor(out) -> torch.Tensor:
     return out.tensor if isinstance(out, PeerOutput) else out
 
 
+def _peer_transport() -> str:
+    """How a block reaches the peers' buffers: ``scatter`` (one kernel of this library that stores
+    the block to every peer) or ``copy`` (one copy-engine transfer per peer).
+    ``SPARSETIR_PEER_TRANSPORT`` selects; the default is the faster one measured on NVSwitch."""
+    v = os.environ.get("SPARSETIR_PEER_TRANSPORT", "copy").lower()
+    if v not in ("scatter", "copy"):
+        raise ValueError(f"SPARSETIR_PEER_TRANSPORT={v!r}: expected 'scatter' or 'copy'")
+    return v
+
+
 class _Gatherer:
     """All-gather of per-rank output blocks, issued on side streams so that it overlaps whatever
     the caller launches next.
@@ -148,12 +160,26 @@ class _Gatherer:
                 ready = torch.cuda.Event()
                 ready.record()
                 lo, hi = int(offsets[rank]), int(offsets[rank]) + int(sizes[rank])
-                for step in range(1, world):  # every rank starts with another peer
-                    k = (rank + step) % world
-                    s = self.peer_streams[k]
-                    with torch.cuda.stream(s):
-                        s.wait_event(ready)
-                        out.peers[k][lo:hi].copy_(local, non_blocking=True)
+                order = [(rank + step) % world for step in range(1, world)]  # every rank starts with another peer
+                if _peer_transport() == "scatter":
+                    # one kernel: the block is read once and stored to every peer
+                    from . import _lib as L
+                    src = local.contiguous()
+                    dst = (ctypes.c_void_p * len(order))(
+                        *[out.peers[k].data_ptr() + lo * out.peers[k].element_size() for k in order])
+                    s = self.peer_streams[rank]
+                    s.wait_event(ready)
+                    src.record_stream(s)
+                    if L.load().sparsetir_peer_scatter(self.device.index, ctypes.c_void_p(s.cuda_stream),
+                                                       ctypes.c_void_p(src.data_ptr()),
+                                                       src.numel() * src.element_size(), len(order), dst) != 0:
+                        raise ShardError(f"rank {rank}: peer scatter failed: {L.last_error()}")
+                else:
+                    for k in order:  # one copy-engine transfer per peer
+                        s = self.peer_streams[k]
+                        with torch.cuda.stream(s):
+                            s.wait_event(ready)
+                            out.peers[k][lo:hi].copy_(local, non_blocking=True)
             self.p2p_pending = True
             return
         pieces = [out[int(o):int(o) + int(s)] for o, s in zip(offsets, sizes)]

@@ -365,10 +365,11 @@ def ours_arm(args, rank, world, local_rank):
         y_all = {f: sharded.peer_empty(g.m * f, torch.float32, device) for f in FEATS}
         order = tuple(sorted(FEATS, reverse=True))
 
+        gathered = {f: op.prepare_gathered(x_dev[f], y_all[f], f) for f in FEATS}
+
         def gather_step():
             for f in order:
-                calls[f]()
-                op.gather(y_dev[f], f, y_all[f])
+                gathered[f]()
             op.wait()
 
         gather_ms = timed(gather_step, max(3, min(args.steps, 20)))
@@ -377,7 +378,7 @@ def ours_arm(args, rank, world, local_rank):
         nvlink = {"bound": "nvlink", "achieved": recv_max / (gather_ms * 1e-3) / 1e9, "peak": NVLINK_GBS,
                   "unit": "GB/s", "frac": recv_max / (gather_ms * 1e-3) / 1e9 / NVLINK_GBS,
                   "bytes_received_per_gpu_per_step": recv_max,
-                  "transport": ("peer writes over NVLink, one copy per peer (symmetric memory)"
+                  "transport": (sharded.peer_transport_note()
                                 if isinstance(y_all[FEATS[0]], sharded.PeerOutput) else "NCCL all-gather"),
                   "note": "every GPU must receive the other shards' rows of Y: these bytes over the "
                           "measured 770 GB/s per direction are the floor of this step"}

@@ -176,6 +176,18 @@ SPARSETIR_API int sparsetir_csrmm(SPARSETIR_PACKED_ARGS);
  * Uses library scratch memory for split rows (see sparsetir_reserve_workspace).
  * Replaces the function built by examples/spmm/bench_spmm.py:116-199 (argument list :207-222). */
 SPARSETIR_API int sparsetir_hyb_spmm(SPARSETIR_PACKED_ARGS);
+/* The same operator for one shard of a row-sharded A whose output every GPU wants whole: each
+ * finished row of C is stored on this GPU and, by the same kernel, at the same offset of every
+ * peer's copy of C — the sending half of the all-gather rides on the SpMM's own stores over NVLink
+ * instead of following it as a copy (no counterpart in the reference, which has one device).
+ * args: as sparsetir_hyb_spmm with feat_size AND flags given, then one integer per peer: the
+ *       peer-mapped address (CUDA IPC, cuMemMap, symmetric memory) at which that peer keeps this
+ *       call's c, aligned like c.  1 to SPARSETIR_MAX_PEERS peers.
+ * Needs the one-writer kernel: 16-byte aligned b and c, feat_size a multiple of 32, bucket widths
+ * 1, 2, 4 or multiples of 8, flags without ZERO_C and ALL_ATOMIC; otherwise -1, and the caller
+ * runs sparsetir_hyb_spmm followed by sparsetir_peer_scatter.  The kernel waits on nothing; a
+ * GPU's copy is complete when every peer's call has finished (order that between the ranks). */
+SPARSETIR_API int sparsetir_hyb_spmm_peers(SPARSETIR_PACKED_ARGS);
 #define SPARSETIR_HYB_ZERO_C 1
 #define SPARSETIR_HYB_REARM 2
 #define SPARSETIR_HYB_ALL_ATOMIC 4
@@ -190,6 +202,16 @@ SPARSETIR_API int sparsetir_hyb_spmm(SPARSETIR_PACKED_ARGS);
  * (tests/python/sparsetir/sparse_tir_scripts.py:268-318; flat signature
  * tests/python/sparsetir/sparse_tir_lowered_buffer_scripts.py:458-475). */
 SPARSETIR_API int sparsetir_sddmm(SPARSETIR_PACKED_ARGS);
+/* SDDMM for one shard of a row-sharded graph whose per-position result every GPU wants whole:
+ * every finished c[p] is also stored at the same offset of each peer's copy of c, by the kernel
+ * that computes it (see sparsetir_hyb_spmm_peers).
+ * args: (a, b, c, indptr, indices, peer_c_0 ... peer_c_{P-1} [, scale]): the five tensors of
+ *       sparsetir_sddmm (sizes inferred from their lengths), then one integer per peer: the
+ *       peer-mapped address of that peer's copy of this call's c (4-byte aligned), 1 to
+ *       SPARSETIR_MAX_PEERS of them; then the optional per-position factor.
+ * Needs feat_size a multiple of 32 and 32-byte aligned a and b; otherwise -1, and the caller runs
+ * sparsetir_sddmm followed by sparsetir_peer_scatter. */
+SPARSETIR_API int sparsetir_sddmm_peers(SPARSETIR_PACKED_ARGS);
 
 /* Edge -> row lookup, the preprocess kernel of fused SDDMM:
  * mid[p] = upper_bound(indptr, p) - 1.
@@ -296,6 +318,11 @@ typedef struct {
 SPARSETIR_API int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirEllBucket* buckets,
                                          int num_buckets, int m, int n, int feat, int flags,
                                          int device_id, void* stream);
+/* sparsetir_hyb_spmm_peers without the packed layer: peer_c[k] is peer k's copy of c. */
+SPARSETIR_API int sparsetir_hyb_spmm_peers_raw(const float* b, float* c,
+                                               const SparsetirEllBucket* buckets, int num_buckets,
+                                               int m, int n, int feat, int flags, int n_peers,
+                                               void* const* peer_c, int device_id, void* stream);
 /* Scratch and counter bytes sparsetir_hyb_spmm(_raw) uses for this bucket table and feature size
  * (non-zero only when the widest bucket may hold rows split into several ELL rows). */
 SPARSETIR_API int sparsetir_hyb_spmm_workspace(const SparsetirEllBucket* buckets, int num_buckets,
@@ -310,6 +337,11 @@ SPARSETIR_API int sparsetir_sddmm_raw(const float* a, const float* b, float* c,
                                       const int32_t* indptr, const int32_t* indices,
                                       const float* scale, int m, int n, int feat, int nnz,
                                       int device_id, void* stream);
+SPARSETIR_API int sparsetir_sddmm_peers_raw(const float* a, const float* b, float* c,
+                                            const int32_t* indptr, const int32_t* indices,
+                                            const float* scale, int m, int n, int feat, int nnz,
+                                            int n_peers, void* const* peer_c, int device_id,
+                                            void* stream);
 SPARSETIR_API int sparsetir_sddmm_edge_to_row_raw(const int32_t* indptr, int32_t* mid, int m,
                                                   int nnz, int device_id, void* stream);
 SPARSETIR_API int sparsetir_bsrmm_raw(const void* a_f16, const void* b_f16, float* c,

@@ -67,7 +67,9 @@ HYB_MAX_BUCKETS = 64
 PACKED_SYMBOLS = (
     "sparsetir_csrmm",
     "sparsetir_hyb_spmm",
+    "sparsetir_hyb_spmm_peers",
     "sparsetir_sddmm",
+    "sparsetir_sddmm_peers",
     "sparsetir_sddmm_edge_to_row",
     "sparsetir_bsrmm",
     "sparsetir_rgms",
@@ -102,7 +104,11 @@ PLAIN_SYMBOLS = {
     "sparsetir_tc_timeouts": (_i, [_i, ctypes.POINTER(ctypes.c_uint)]),
     "sparsetir_csrmm_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_hyb_spmm_raw": (_i, [_vp, _vp, ctypes.POINTER(EllBucket), _i, _i, _i, _i, _i, _i, _vp]),
+    "sparsetir_hyb_spmm_peers_raw": (_i, [_vp, _vp, ctypes.POINTER(EllBucket), _i, _i, _i, _i, _i, _i,
+                                          ctypes.POINTER(ctypes.c_void_p), _i, _vp]),
     "sparsetir_sddmm_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "sparsetir_sddmm_peers_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i,
+                                       ctypes.POINTER(ctypes.c_void_p), _i, _vp]),
     "sparsetir_sddmm_edge_to_row_raw": (_i, [_vp, _vp, _i, _i, _i, _vp]),
     "sparsetir_bsrmm_raw": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp]),
     "sparsetir_rgms_raw": (_i, [_vp] * 8 + [_i] * 7 + [_vp]),

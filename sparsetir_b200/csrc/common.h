@@ -48,6 +48,18 @@ int validate_range(const char* op, const char* what, const int32_t* ids, long lo
 int validate_csr(const char* op, const int32_t* indptr, long long rows, const int32_t* indices,
                  long long nnz, long long cols, cudaStream_t st);
 
+// Copies of an output array on other GPUs (peer-mapped): a kernel that takes one stores every
+// finished element also at the same offset from (its own output pointer + delta[k]).  n = 0 for a
+// plain call.  Filled by peer_table().
+struct PeerOut {
+  long long delta[SPARSETIR_MAX_PEERS];  // bytes from this GPU's output to peer k's copy of it
+  int n;
+};
+
+// Checks the peer addresses of a *_peers entry point and turns them into offsets from `own`;
+// every copy must sit like `own` with respect to `align` bytes.  Returns 0 or -1 (error recorded).
+int peer_table(const char* fn, const void* own, int n_peers, void* const* peers, size_t align, PeerOut* out);
+
 constexpr int kNumSMs = 148;  // B200
 
 inline int ceil_div(long long a, long long b) { return static_cast<int>((a + b - 1) / b); }

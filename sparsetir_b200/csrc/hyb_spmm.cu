@@ -288,7 +288,17 @@ struct LeanArgs {
   unsigned* counters;   // [scratch rows][feature tiles], zero before and after every launch
   int feat;
   int all_atomic;
+  PeerOut peers;
 };
+
+// The one store of a finished piece of an output row: into this GPU's C and, when the call has
+// peers, into every peer's copy (plain stores over NVLink; nothing waits on them).
+template <int W>
+__device__ __forceinline__ void store_out(char* p, const typename LaneVec<W>::type& v, const PeerOut* po) {
+  LaneVec<W>::stcs(p, v);
+  if (po != nullptr)
+    for (int k = 0; k < po->n; ++k) LaneVec<W>::stcg(p + po->delta[k], v);
+}
 
 // Bits of `pred` over the LPR lanes of this thread's sub-warp, lane 0 of the sub-warp in bit 0.
 template <int LPR>
@@ -310,7 +320,7 @@ __device__ __noinline__ void finish_split_row(typename LaneVec<W>::type acc,
                                               const int32_t* __restrict__ rows, int nrows, int g,
                                               int rpi, int rid, int part_base, char* pl, char* cl,
                                               unsigned* counters, unsigned row_bytes, int lane,
-                                              unsigned mask) {
+                                              unsigned mask, const PeerOut* po) {
   using LV = LaneVec<W>;
   constexpr unsigned kFull = LPR == 32 ? 0xffffffffu : ((1u << LPR) - 1u);
   int first = g, last = g;
@@ -332,7 +342,7 @@ __device__ __noinline__ void finish_split_row(typename LaneVec<W>::type acc,
   const int npieces = last / rpi - item0 + 1;
   char* dst = cl + static_cast<unsigned long long>(static_cast<unsigned>(rid)) * row_bytes;
   if (npieces == 1) {  // the whole run lies inside this item
-    LV::stcs(dst, acc);
+    store_out<W>(dst, acc, po);
     return;
   }
   const int mine = max(first, g / rpi * rpi);
@@ -352,7 +362,7 @@ __device__ __noinline__ void finish_split_row(typename LaneVec<W>::type acc,
   __threadfence();
   typename LV::type sum = LV::ldcg(part_of(first));
   for (int k = 1; k < npieces; ++k) LV::add(sum, LV::ldcg(part_of((item0 + k) * rpi)));
-  LV::stcs(dst, sum);
+  store_out<W>(dst, sum, po);
 }
 
 // A narrow item of the widest bucket that holds ELL rows of a split row (rare: only bucket lists
@@ -363,7 +373,7 @@ __device__ __noinline__ void split_item(const int32_t* __restrict__ cols, const 
                                         const int32_t* __restrict__ rows, int nrows, int r0, int nr,
                                         int width, int rpi, int part_base, const char* __restrict__ bl,
                                         char* pl, char* cl, unsigned* counters, unsigned row_bytes,
-                                        int lane, unsigned mask) {
+                                        int lane, unsigned mask, const PeerOut* po) {
   using LV = LaneVec<W>;
   typename LV::type acc = LV::zero();
   for (int j = 0; j < nr; ++j) {
@@ -377,18 +387,20 @@ __device__ __noinline__ void split_item(const int32_t* __restrict__ cols, const 
     const bool next_same = g + 1 < nrows && __ldg(rows + g + 1) == rid;
     if (next_same && j + 1 < nr) continue;  // the next ELL row of this item continues the row
     if (next_same || (g > 0 && __ldg(rows + g - 1) == rid))
-      finish_split_row<LPR, W>(acc, rows, nrows, g, rpi, rid, part_base, pl, cl, counters, row_bytes, lane, mask);
+      finish_split_row<LPR, W>(acc, rows, nrows, g, rpi, rid, part_base, pl, cl, counters, row_bytes, lane, mask,
+                               po);
     else
-      LV::stcs(cl + static_cast<unsigned long long>(static_cast<unsigned>(rid)) * row_bytes, acc);
+      store_out<W>(cl + static_cast<unsigned long long>(static_cast<unsigned>(rid)) * row_bytes, acc, po);
     acc = LV::zero();
   }
 }
 
-template <int LPR, int W>
+template <int LPR, int W, bool PEERS>
 __global__ void __launch_bounds__(kThreads, 8)
 hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const __grid_constant__ LeanArgs la) {
   using LV = LaneVec<W>;
   using V = typename LV::type;
+  const PeerOut* po = PEERS ? &la.peers : nullptr;
   constexpr int SUBS = kThreads / LPR;
   __shared__ __align__(32) float s_part[SUBS][LPR * W];  // wide rows: partial sums of the spans
   const int lane = threadIdx.x % LPR;
@@ -424,7 +436,7 @@ hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const __grid_constant_
       for (int j = lane; j < nr; j += LPR) any = any || is_split_row(rows, r0 + j, nrows, __ldg(rows + r0 + j));
       if (sub_ballot<LPR>(mask, any) != 0u) {
         split_item<LPR, W>(tb.cols[q] + first, tb.w[q] + first, rows, nrows, r0, nr, width, rpi, part_base,
-                           bl, pl, cl, la.counters, stride, lane, mask);
+                           bl, pl, cl, la.counters, stride, lane, mask, po);
         return;
       }
     }
@@ -434,7 +446,7 @@ hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const __grid_constant_
     };
     auto row_end = [&](V& acc, int rf) {
       if (rf < 0) LV::atomic_add(y_of(rf & 0x7fffffff), acc);
-      else LV::stcs(y_of(rf), acc);  // written once: do not displace B rows in L2
+      else store_out<W>(y_of(rf), acc, po);  // written once: do not displace B rows in L2
       acc = LV::zero();
     };
     const int32_t* cols = tb.cols[q] + first;
@@ -472,9 +484,10 @@ hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const __grid_constant_
   if (all_atomic) {
     LV::atomic_add(y_of(rid), total);
   } else if (part_base >= 0 && is_split_row(rows, r, nrows, rid)) {
-    finish_split_row<LPR, W>(total, rows, nrows, r, 1, rid, part_base, pl, cl, la.counters, stride, lane, mask);
+    finish_split_row<LPR, W>(total, rows, nrows, r, 1, rid, part_base, pl, cl, la.counters, stride, lane, mask,
+                             po);
   } else {
-    LV::stcs(y_of(rid), total);
+    store_out<W>(y_of(rid), total, po);
   }
 }
 
@@ -704,7 +717,10 @@ int launch_lean(HybTable& tb, const LeanArgs& la, cudaStream_t stream) {
   const long long blocks = plan_blocks_lean(tb, kThreads / LPR);
   if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
   dim3 grid(static_cast<unsigned>(blocks), la.feat / (W * LPR));
-  hyb_spmm_lean_kernel<LPR, W><<<grid, kThreads, 0, stream>>>(tb, la);
+  if (la.peers.n > 0)
+    hyb_spmm_lean_kernel<LPR, W, true><<<grid, kThreads, 0, stream>>>(tb, la);
+  else
+    hyb_spmm_lean_kernel<LPR, W, false><<<grid, kThreads, 0, stream>>>(tb, la);
   SPTIR_LAUNCH_OK("hyb_spmm_lean_kernel");
   return 0;
 }
@@ -762,8 +778,9 @@ int lanes_per_row(int feat, bool vec4, int n, int lane_w) { return lanes_per_row
 
 // The launcher behind sparsetir_hyb_spmm_raw.  row_bases (may be null): for buckets whose `rows`
 // array is null, ELL row r of bucket q is written to output row row_bases[q] + r.
-int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, const int32_t* row_bases,
-                  int num_buckets, int m, int n, int feat, int flags, int device_id, void* stream) {
+int hyb_spmm_run(const float* b, float* c, const SparsetirEllBucket* buckets, const int32_t* row_bases,
+                 int num_buckets, int m, int n, int feat, int flags, int device_id, void* stream,
+                 const PeerOut* peers) {
   if (num_buckets < 0 || num_buckets > kMaxB)
     return fail("sparsetir_hyb_spmm: %d buckets exceed the maximum of %d", num_buckets, kMaxB);
   if (m < 0 || feat < 0) return fail("sparsetir_hyb_spmm: negative size");
@@ -819,6 +836,11 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
   }
   lean = lean && feat % (lane_w * lanes) == 0;
   const size_t c_bytes = static_cast<size_t>(m) * feat * sizeof(float);
+  const bool to_peers = peers != nullptr && peers->n > 0;
+  if (to_peers && (!lean || all_atomic || (flags & SPARSETIR_HYB_ZERO_C)))
+    return fail("sparsetir_hyb_spmm_peers: needs the one-writer kernel (feat_size a multiple of its tile, "
+                "16-byte aligned b and c, bucket widths 1, 2, 4 or multiples of 8, no ALL_ATOMIC or ZERO_C "
+                "flag); run sparsetir_hyb_spmm and sparsetir_peer_scatter instead");
   if (tb.nb == 0) {
     if (flags & SPARSETIR_HYB_ZERO_C) SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, c_bytes, st));
     return 0;
@@ -826,7 +848,8 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
 
   if (lean) {
     // ---- one writer per output row (or everything atomic when the caller asks for it)
-    LeanArgs la{b, c, nullptr, nullptr, feat, all_atomic};
+    LeanArgs la{b, c, nullptr, nullptr, feat, all_atomic, PeerOut{}};
+    if (to_peers) la.peers = *peers;
     bool clear = (flags & SPARSETIR_HYB_ZERO_C) || (all_atomic && (flags & SPARSETIR_HYB_REARM));
     for (int q = 0; q < tb.nb; ++q) tb.part_base[q] = -1;
     if (!all_atomic) {
@@ -846,6 +869,9 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
       if (part_rows > INT32_MAX || part_bytes > hyb_scratch_limit()) {
         // a bucket list whose widest bucket holds most of the matrix: adding atomically into a
         // cleared C costs less memory than a scratch copy of that size
+        if (to_peers)
+          return fail("sparsetir_hyb_spmm_peers: the split rows need %zu bytes of scratch, beyond the limit; "
+                      "run sparsetir_hyb_spmm and sparsetir_peer_scatter instead", part_bytes);
         for (int q = 0; q < tb.nb; ++q) tb.part_base[q] = -1;
         la.all_atomic = 1;
         clear = true;
@@ -889,6 +915,11 @@ int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, c
   if (feat <= 32) return launch<32, 1, 1>(tb, b, c, feat, all_atomic, st);
   return launch<32, 4, 1>(tb, b, c, feat, all_atomic, st);
 }
+
+int hyb_spmm_impl(const float* b, float* c, const SparsetirEllBucket* buckets, const int32_t* row_bases,
+                  int num_buckets, int m, int n, int feat, int flags, int device_id, void* stream) {
+  return hyb_spmm_run(b, c, buckets, row_bases, num_buckets, m, n, feat, flags, device_id, stream, nullptr);
+}
 }  // namespace sptir
 
 extern "C" int sparsetir_hyb_spmm_tile(int n, int feat, int* lanes, int* lane_floats) {
@@ -923,6 +954,14 @@ extern "C" int sparsetir_hyb_spmm_workspace(const SparsetirEllBucket* buckets, i
   // a feature tile is at least 32 floats wide
   *counter_bytes = fits ? rows * static_cast<size_t>((feat + 31) / 32) * sizeof(unsigned) : 0;
   return 0;
+}
+
+extern "C" int sparsetir_hyb_spmm_peers_raw(const float* b, float* c, const SparsetirEllBucket* buckets,
+                                            int num_buckets, int m, int n, int feat, int flags,
+                                            int n_peers, void* const* peer_c, int device_id, void* stream) {
+  sptir::PeerOut po{};
+  if (sptir::peer_table("sparsetir_hyb_spmm_peers", c, n_peers, peer_c, 32, &po) != 0) return -1;
+  return sptir::hyb_spmm_run(b, c, buckets, nullptr, num_buckets, m, n, feat, flags, device_id, stream, &po);
 }
 
 extern "C" int sparsetir_hyb_spmm_raw(const float* b, float* c, const SparsetirEllBucket* buckets,

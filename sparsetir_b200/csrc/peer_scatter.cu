@@ -45,6 +45,34 @@ peer_scatter_kernel(const uint4* __restrict__ src, size_t n16, const __grid_cons
   }
 }
 
+// The same with a source that is not 16-byte aligned where the destinations are: each thread
+// assembles its 16-byte piece from four word loads (a warp still reads 512 contiguous bytes) so
+// that the stores that cross NVLink stay 16 bytes wide.
+template <int U>
+__global__ void __launch_bounds__(256)
+peer_scatter_shift_kernel(const uint32_t* __restrict__ src, size_t n16, const __grid_constant__ PeerPtrs dst) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  auto piece = [&](size_t j) {
+    const uint32_t* w = src + 4 * j;
+    return make_uint4(__ldcs(w), __ldcs(w + 1), __ldcs(w + 2), __ldcs(w + 3));
+  };
+  for (; i + (U - 1) * stride < n16; i += U * stride) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = piece(i + u * stride);
+    for (int k = 0; k < dst.n; ++k) {
+      uint4* d = static_cast<uint4*>(dst.p[k]);
+#pragma unroll
+      for (int u = 0; u < U; ++u) d[i + u * stride] = v[u];
+    }
+  }
+  for (; i < n16; i += stride) {
+    const uint4 v = piece(i);
+    for (int k = 0; k < dst.n; ++k) static_cast<uint4*>(dst.p[k])[i] = v;
+  }
+}
+
 __global__ void __launch_bounds__(256)
 peer_scatter_words_kernel(const uint32_t* __restrict__ src, size_t n4, const __grid_constant__ PeerPtrs dst) {
   const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
@@ -55,12 +83,14 @@ peer_scatter_words_kernel(const uint32_t* __restrict__ src, size_t n4, const __g
 }
 
 int scatter_blocks() {
-  // The NVLink ports, not the SMs, bound this kernel: two blocks per SM keep enough stores in
-  // flight, and the kernels that run beside it share the SMs.  SPARSETIR_SCATTER_BLOCKS overrides.
+  // The NVLink ports, not the SMs, bound this kernel: 74 blocks already reach the rate of 592
+  // (measured with three peers: 635 against 658 GB/s received per GPU), so one block per SM keeps
+  // the links busy and leaves most of every SM to the kernels that run beside it.
+  // SPARSETIR_SCATTER_BLOCKS overrides.
   static const int n = [] {
     const char* e = getenv("SPARSETIR_SCATTER_BLOCKS");
     const int v = e ? atoi(e) : 0;
-    return v > 0 ? v : 2 * kNumSMs;
+    return v > 0 ? v : kNumSMs;
   }();
   return n;
 }
@@ -82,22 +112,25 @@ extern "C" int sparsetir_peer_scatter(int device_id, void* stream, const void* s
   dst.n = n_peers;
   const uintptr_t s = reinterpret_cast<uintptr_t>(src);
   if (s % 4) return fail("sparsetir_peer_scatter: source not 4-byte aligned");
-  bool same_phase = true;  // every destination is as far from a 16-byte boundary as the source
+  // the destinations are cut at 16-byte boundaries when they all sit alike; the source then is
+  // either aligned with them (vector loads) or not (four word loads per piece)
+  bool alike = true;
   for (int k = 0; k < n_peers; ++k) {
     if (peer_dst[k] == nullptr) return fail("sparsetir_peer_scatter: destination %d is null", k);
     const uintptr_t d = reinterpret_cast<uintptr_t>(peer_dst[k]);
     if (d % 4) return fail("sparsetir_peer_scatter: destination %d not 4-byte aligned", k);
-    same_phase = same_phase && (d % 16 == s % 16);
+    alike = alike && (d % 16 == reinterpret_cast<uintptr_t>(peer_dst[0]) % 16);
     dst.p[k] = peer_dst[k];
   }
   const int blocks = scatter_blocks();
-  if (!same_phase) {
+  if (!alike) {
     peer_scatter_words_kernel<<<blocks, 256, 0, st>>>(static_cast<const uint32_t*>(src), bytes / 4, dst);
     SPTIR_LAUNCH_OK("peer_scatter_words_kernel");
     return 0;
   }
-  // words up to the first 16-byte boundary, the 16-byte body, the words after it
-  const size_t head = (s % 16) ? ((16 - s % 16) < bytes ? (16 - s % 16) : bytes) : 0;
+  // words up to the destinations' first 16-byte boundary, the 16-byte body, the words after it
+  const size_t d0 = reinterpret_cast<uintptr_t>(peer_dst[0]) % 16;
+  const size_t head = d0 ? ((16 - d0) < bytes ? (16 - d0) : bytes) : 0;
   const size_t body = (bytes - head) / 16 * 16;
   const size_t tail = bytes - head - body;
   auto shifted = [&](size_t off) {
@@ -113,8 +146,12 @@ extern "C" int sparsetir_peer_scatter(int device_id, void* stream, const void* s
     const size_t n16 = body / 16;
     const size_t want = (n16 + 256 * 4 - 1) / (256 * 4);
     const int grid = static_cast<int>(want < static_cast<size_t>(blocks) ? want : blocks);
-    peer_scatter_kernel<4><<<grid, 256, 0, st>>>(
-        reinterpret_cast<const uint4*>(static_cast<const char*>(src) + head), n16, shifted(head));
+    const char* from = static_cast<const char*>(src) + head;
+    if (reinterpret_cast<uintptr_t>(from) % 16 == 0)
+      peer_scatter_kernel<4><<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(from), n16, shifted(head));
+    else
+      peer_scatter_shift_kernel<4><<<grid, 256, 0, st>>>(reinterpret_cast<const uint32_t*>(from), n16,
+                                                         shifted(head));
     SPTIR_LAUNCH_OK("peer_scatter_kernel");
   }
   if (tail) {

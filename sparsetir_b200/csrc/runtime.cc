@@ -88,6 +88,21 @@ void* grow(int kind, int device_id, cudaStream_t stream, size_t bytes) {
 }
 }  // namespace
 
+int peer_table(const char* fn, const void* own, int n_peers, void* const* peers, size_t align, PeerOut* out) {
+  if (n_peers < 1 || n_peers > SPARSETIR_MAX_PEERS)
+    return fail("%s: %d peers, expected 1 to %d", fn, n_peers, SPARSETIR_MAX_PEERS);
+  if (peers == nullptr) return fail("%s: null peer table", fn);
+  out->n = n_peers;
+  for (int k = 0; k < n_peers; ++k) {
+    if (peers[k] == nullptr) return fail("%s: peer %d is null", fn, k);
+    const uintptr_t a = reinterpret_cast<uintptr_t>(peers[k]), o = reinterpret_cast<uintptr_t>(own);
+    if (a % align != o % align)
+      return fail("%s: peer %d is not aligned like the output itself (%zu bytes)", fn, k, align);
+    out->delta[k] = static_cast<long long>(static_cast<intptr_t>(a) - static_cast<intptr_t>(o));
+  }
+  return 0;
+}
+
 void* workspace(int device_id, cudaStream_t stream, size_t bytes) {
   return grow(0, device_id, stream, bytes);
 }

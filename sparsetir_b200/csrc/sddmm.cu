@@ -221,12 +221,14 @@ __device__ __forceinline__ int warp_row_search(const int32_t* __restrict__ indpt
   return lo + __ffs(__ballot_sync(0xffffffffu, gt)) - 1;
 }
 
-template <int LPR>
+// With PEERS the finished value of every position (the last feature tile's pass) is also stored
+// into the peers' copies of c: 128 contiguous bytes per warp and peer, over NVLink.
+template <int LPR, bool PEERS>
 __global__ void __launch_bounds__(kThreads, LPR <= 8 ? 4 : 2)
 sddmm_lean_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
                   const int32_t* __restrict__ indptr, const int32_t* __restrict__ indices,
                   const float* __restrict__ scale, int m, int nnz, int ld, int foff, int accumulate,
-                  int chunk) {
+                  int chunk, int last_tile, const __grid_constant__ PeerOut po) {
   constexpr int U = LPR < 4 ? LPR : 4;  // gathered rows in flight per lane (8 registers each)
   const int wlane = threadIdx.x & 31;
   const int lane = wlane % LPR;
@@ -316,7 +318,15 @@ sddmm_lean_kernel(const float* __restrict__ a, const float* __restrict__ b, floa
         part[i] = keep + __shfl_xor_sync(mask, send, offl, LPR);
       }
     }
-    if (live) c[e] = fmaf(part[0], mul, old);
+    if (live) {
+      const float v = fmaf(part[0], mul, old);
+      c[e] = v;
+      if constexpr (PEERS) {
+        if (last_tile)
+          for (int k = 0; k < po.n; ++k)
+            *reinterpret_cast<float*>(reinterpret_cast<char*>(c + e) + po.delta[k]) = v;
+      }
+    }
   }
 }
 
@@ -370,7 +380,7 @@ int lean_blocks_per_sm() {
   if (cudaGetDevice(&dev) != cudaSuccess) return 4;
   if (dev != cached_device) {
     int n = 0;
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sddmm_lean_kernel<LPR>, kThreads, 0) != cudaSuccess || n < 1)
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, sddmm_lean_kernel<LPR, false>, kThreads, 0) != cudaSuccess || n < 1)
       n = 4;
     cached = n;
     cached_device = dev;
@@ -381,7 +391,7 @@ int lean_blocks_per_sm() {
 template <int LPR>
 int launch_lean_tile(const float* a, const float* b, float* c, const int32_t* indptr,
                      const int32_t* indices, const float* scale, int m, int feat, int nnz, int foff,
-                     cudaStream_t stream) {
+                     int last_tile, const PeerOut& po, cudaStream_t stream) {
   // long chunks amortise the row search; short ones keep small inputs spread over the SMs
   int chunk = nnz >= (1 << 22) ? 1024 : 256;
   const int wpb = kThreads / 32;
@@ -396,8 +406,12 @@ int launch_lean_tile(const float* a, const float* b, float* c, const int32_t* in
     chunk = (chunk + 31) & ~31;
     blocks = ceil_div(ceil_div(nnz, chunk), wpb);
   }
-  sddmm_lean_kernel<LPR><<<blocks, kThreads, 0, stream>>>(a, b, c, indptr, indices, scale, m, nnz,
-                                                           feat, foff, foff != 0, chunk);
+  if (po.n > 0)
+    sddmm_lean_kernel<LPR, true><<<blocks, kThreads, 0, stream>>>(a, b, c, indptr, indices, scale, m, nnz, feat,
+                                                                  foff, foff != 0, chunk, last_tile, po);
+  else
+    sddmm_lean_kernel<LPR, false><<<blocks, kThreads, 0, stream>>>(a, b, c, indptr, indices, scale, m, nnz, feat,
+                                                                   foff, foff != 0, chunk, last_tile, po);
   SPTIR_LAUNCH_OK("sddmm_lean_kernel");
   return 0;
 }
@@ -417,7 +431,7 @@ size_t l2_budget_bytes() {
 // slice of B (n rows) fits the L2 budget; one launch per tile, in stream order.
 int launch_lean(const float* a, const float* b, float* c, const int32_t* indptr,
                 const int32_t* indices, const float* scale, int m, int n, int feat, int nnz,
-                cudaStream_t stream) {
+                const PeerOut& po, cudaStream_t stream) {
   int tile = 32;
   for (int t = 256; t > 32; t /= 2)
     if (feat % t == 0 && static_cast<size_t>(n) * t * 4 <= l2_budget_bytes()) {
@@ -426,11 +440,12 @@ int launch_lean(const float* a, const float* b, float* c, const int32_t* indptr,
     }
   for (int foff = 0; foff < feat; foff += tile) {
     int rc;
+    const int last = foff + tile >= feat;
     switch (tile) {
-      case 256: rc = launch_lean_tile<32>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, stream); break;
-      case 128: rc = launch_lean_tile<16>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, stream); break;
-      case 64: rc = launch_lean_tile<8>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, stream); break;
-      default: rc = launch_lean_tile<4>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, stream); break;
+      case 256: rc = launch_lean_tile<32>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, last, po, stream); break;
+      case 128: rc = launch_lean_tile<16>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, last, po, stream); break;
+      case 64: rc = launch_lean_tile<8>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, last, po, stream); break;
+      default: rc = launch_lean_tile<4>(a, b, c, indptr, indices, scale, m, feat, nnz, foff, last, po, stream); break;
     }
     if (rc != 0) return rc;
   }
@@ -440,10 +455,11 @@ int launch_lean(const float* a, const float* b, float* c, const int32_t* indptr,
 }  // namespace
 }  // namespace sptir
 
-extern "C" int sparsetir_sddmm_raw(const float* a, const float* b, float* c, const int32_t* indptr,
-                                   const int32_t* indices, const float* scale, int m, int n,
-                                   int feat, int nnz, int device_id, void* stream) {
-  using namespace sptir;
+namespace sptir {
+namespace {
+int sddmm_run(const float* a, const float* b, float* c, const int32_t* indptr, const int32_t* indices,
+              const float* scale, int m, int n, int feat, int nnz, int device_id, void* stream,
+              const PeerOut& po) {
   if (m < 0 || n < 0 || feat < 0 || nnz < 0) return fail("sparsetir_sddmm: negative size");
   if (nnz == 0) return 0;
   if (m < 1) return fail("sparsetir_sddmm: %d stored entries but no rows", nnz);
@@ -452,12 +468,15 @@ extern "C" int sparsetir_sddmm_raw(const float* a, const float* b, float* c, con
   if (use_device(device_id) != 0) return -1;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (validate_enabled() && validate_csr("sparsetir_sddmm", indptr, m, indices, nnz, n, st) != 0) return -1;
+  const bool lean = feat > 0 && feat % 32 == 0 && aligned32(a) && aligned32(b);
+  if (po.n > 0 && !lean)
+    return fail("sparsetir_sddmm_peers: needs feat_size a positive multiple of 32 and 32-byte aligned a and b; "
+                "run sparsetir_sddmm and sparsetir_peer_scatter instead");
   if (feat == 0) {
     SPTIR_CUDA_OK(cudaMemsetAsync(c, 0, static_cast<size_t>(nnz) * sizeof(float), st));
     return 0;
   }
-  if (feat % 32 == 0 && aligned32(a) && aligned32(b))
-    return launch_lean(a, b, c, indptr, indices, scale, m, n, feat, nnz, st);
+  if (lean) return launch_lean(a, b, c, indptr, indices, scale, m, n, feat, nnz, po, st);
   const bool vec4 = (feat % 4 == 0) && aligned16(a) && aligned16(b);
   if (vec4) {
     const int nv = feat / 4;
@@ -477,6 +496,23 @@ extern "C" int sparsetir_sddmm_raw(const float* a, const float* b, float* c, con
   sddmm_generic_kernel<<<blocks, kThreads, 0, st>>>(a, b, c, indptr, indices, scale, m, feat, nnz);
   SPTIR_LAUNCH_OK("sddmm_generic_kernel");
   return 0;
+}
+}  // namespace
+}  // namespace sptir
+
+extern "C" int sparsetir_sddmm_raw(const float* a, const float* b, float* c, const int32_t* indptr,
+                                   const int32_t* indices, const float* scale, int m, int n,
+                                   int feat, int nnz, int device_id, void* stream) {
+  return sptir::sddmm_run(a, b, c, indptr, indices, scale, m, n, feat, nnz, device_id, stream, sptir::PeerOut{});
+}
+
+extern "C" int sparsetir_sddmm_peers_raw(const float* a, const float* b, float* c, const int32_t* indptr,
+                                         const int32_t* indices, const float* scale, int m, int n,
+                                         int feat, int nnz, int n_peers, void* const* peer_c,
+                                         int device_id, void* stream) {
+  sptir::PeerOut po{};
+  if (sptir::peer_table("sparsetir_sddmm_peers", c, n_peers, peer_c, 4, &po) != 0) return -1;
+  return sptir::sddmm_run(a, b, c, indptr, indices, scale, m, n, feat, nnz, device_id, stream, po);
 }
 
 extern "C" int sparsetir_sddmm_edge_to_row_raw(const int32_t* indptr, int32_t* mid, int m, int nnz,

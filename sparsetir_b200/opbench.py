@@ -262,7 +262,7 @@ def bench_sddmm_sharded(device, peaks, rank: int, world: int, feats=(32, 128)) -
     out = {"workload": "sddmm_lognormal_232965", "nnz": nnz,
            "graph": "built on the GPU with a torch generator: the twin of datagen.csr_lognormal(seed=0) "
                     "(same degree sequence, other column draws)",
-           "transport": "peer writes over NVLink" if isinstance(c_out, sharded.PeerOutput) else "NCCL",
+           "transport": sharded.peer_transport_note() if isinstance(c_out, sharded.PeerOutput) else "NCCL",
            "rows_per_rank": [int(op.cuts[k + 1] - op.cuts[k]) for k in range(world)],
            "nnz_per_rank": [sum(op.chunk_sizes[c][k] for c in range(op.chunks)) for k in range(world)],
            "chunks": op.chunks, "per_feat": {}}
@@ -270,9 +270,12 @@ def bench_sddmm_sharded(device, peaks, rank: int, world: int, feats=(32, 128)) -
     for f in feats:
         a = torch.rand(n * f, device=device, generator=gen) * 2 - 1
         b = torch.rand(n * f, device=device, generator=gen) * 2 - 1
+        # kernels alone: the shard's calls writing this GPU's buffer only; with the gather: the
+        # calls prepared on the peer-mapped output (which may store into the peers themselves)
+        local_calls = op.prepare(a, b, sharded.local_tensor(c_out), f)
         calls = op.prepare(a, b, c_out, f)
         dist.barrier()
-        mine = _time(lambda: op.run(calls), number=3, repeat=3, warmup=2)
+        mine = _time(lambda: op.run(local_calls), number=3, repeat=3, warmup=2)
         ms = _max_over_ranks(mine, device)
         ms_min = -_max_over_ranks(-mine, device)
 

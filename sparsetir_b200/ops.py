@@ -167,7 +167,9 @@ class PackedFunc:
 
 csrmm = PackedFunc("sparsetir_csrmm")
 hyb_spmm = PackedFunc("sparsetir_hyb_spmm")
+hyb_spmm_peers = PackedFunc("sparsetir_hyb_spmm_peers")
 sddmm = PackedFunc("sparsetir_sddmm")
+sddmm_peers = PackedFunc("sparsetir_sddmm_peers")
 sddmm_edge_to_row = PackedFunc("sparsetir_sddmm_edge_to_row")
 bsrmm = PackedFunc("sparsetir_bsrmm")
 rgms = PackedFunc("sparsetir_rgms")
@@ -182,16 +184,19 @@ fusedmm = PackedFunc("sparsetir_fusedmm")
 
 
 def hyb_args(x: torch.Tensor, y: torch.Tensor, buckets: Sequence[Sequence[torch.Tensor]],
-             feat_size: int, flags: int = 0) -> list:
+             feat_size: int, flags: int = 0, peer_c: Optional[Sequence[int]] = None) -> list:
     """Argument list of ``hyb_spmm`` in the reference's layout
     (examples/spmm/bench_spmm.py:207-222): ``[b, c] + [w, rows, cols] per bucket`` followed by
-    the scalars this library needs because it is not specialised at build time."""
+    the scalars this library needs because it is not specialised at build time.  With ``peer_c``
+    (addresses of the peers' copies of ``y``) the list is that of ``hyb_spmm_peers``."""
     args = [x.reshape(-1), y.reshape(-1)]
     for w, rows, cols in buckets:
         args += [w.reshape(-1), rows.reshape(-1), cols.reshape(-1)]
     args.append(int(feat_size))
-    if flags:
+    if flags or peer_c is not None:
         args.append(int(flags))
+    if peer_c is not None:
+        args += [int(a) for a in peer_c]
     return args
 
 

@@ -113,10 +113,19 @@ def _peer_transport() -> str:
     """How a block reaches the peers' buffers: ``scatter`` (one kernel of this library that stores
     the block to every peer) or ``copy`` (one copy-engine transfer per peer).
     ``SPARSETIR_PEER_TRANSPORT`` selects; the default is the faster one measured on NVSwitch."""
-    v = os.environ.get("SPARSETIR_PEER_TRANSPORT", "copy").lower()
-    if v not in ("scatter", "copy"):
-        raise ValueError(f"SPARSETIR_PEER_TRANSPORT={v!r}: expected 'scatter' or 'copy'")
+    v = os.environ.get("SPARSETIR_PEER_TRANSPORT", "fused").lower()
+    if v not in ("fused", "scatter", "copy"):
+        raise ValueError(f"SPARSETIR_PEER_TRANSPORT={v!r}: expected 'fused', 'scatter' or 'copy'")
     return v
+
+
+def peer_transport_note() -> str:
+    """One line for reports: what moves the blocks into the peers' buffers."""
+    return {"fused": "the SpMM kernel stores every finished row into the peers' buffers itself "
+                     "(hyb SpMM; other operators: one scatter kernel after the call)",
+            "scatter": "one kernel after the call reads the block once and stores it to every peer",
+            "copy": "one copy-engine transfer per peer after the call"}[_peer_transport()] + \
+        "; peer memory from torch symmetric memory, completion by a one-element all-reduce"
 
 
 class _Gatherer:
@@ -153,7 +162,9 @@ class _Gatherer:
             return
         if isinstance(out, PeerOutput):
             if not self.peer_streams:
-                self.peer_streams = [torch.cuda.Stream(device=self.device) for _ in range(world)]
+                # high priority: a transfer queued behind chunk k starts as soon as chunk k ends,
+                # ahead of the blocks of chunk k+1's kernels that are already waiting for SMs
+                self.peer_streams = [torch.cuda.Stream(device=self.device, priority=-1) for _ in range(world)]
             if mine.data_ptr() != local.data_ptr():
                 mine.copy_(local)
             if local.numel() > 0:
@@ -161,7 +172,7 @@ class _Gatherer:
                 ready.record()
                 lo, hi = int(offsets[rank]), int(offsets[rank]) + int(sizes[rank])
                 order = [(rank + step) % world for step in range(1, world)]  # every rank starts with another peer
-                if _peer_transport() == "scatter":
+                if _peer_transport() in ("scatter", "fused"):
                     # one kernel: the block is read once and stored to every peer
                     from . import _lib as L
                     src = local.contiguous()
@@ -246,6 +257,34 @@ class ShardedHybSpmm:
         ``y_local`` the ``[shard rows * feat]`` output block (zero-filled once by the caller)."""
         return ops.hyb_spmm.prepare(*ops.hyb_args(x, y_local, self.buckets, feat, self.flags))
 
+    def prepare_gathered(self, x: torch.Tensor, out, feat: int) -> Callable[[], None]:
+        """The shard's call that leaves its rows in ``out [num_rows_total * feat]`` on EVERY rank
+        (``out`` from ``peer_empty``, or a plain tensor); ``wait()`` after it orders later work
+        behind the other ranks' rows.  With peer memory and the 'fused' transport the SpMM kernel
+        itself stores each finished row into every peer's buffer (``hyb_spmm_peers``): no copy
+        follows the kernel.  Otherwise the kernel writes this rank's rows and a gather follows."""
+        lo = self.row_offsets[self.rank] * feat
+        n = self.rows_per_rank[self.rank] * feat
+        mine = local_tensor(out)[lo:lo + n]
+        if isinstance(out, PeerOutput) and self.world > 1 and self.flags == 0 and _peer_transport() == "fused":
+            order = [(self.rank + step) % self.world for step in range(1, self.world)]
+            peer_c = [out.peers[k].data_ptr() + lo * out.peers[k].element_size() for k in order]
+            call = ops.hyb_spmm_peers.prepare(*ops.hyb_args(x, mine, self.buckets, feat, 0, peer_c=peer_c))
+            gatherer = self._gatherer
+
+            def run_fused() -> None:
+                call()
+                gatherer.p2p_pending = True  # the peers' rows arrive with THEIR kernels: wait() meets them
+
+            return run_fused
+        call = self.prepare(x, mine, feat)
+
+        def run_then_gather() -> None:
+            call()
+            self.gather(mine, feat, out)
+
+        return run_then_gather
+
     def gather(self, y_local: torch.Tensor, feat: int, out) -> None:
         """Queues the all-gather of the output rows into ``out [num_rows_total * feat]`` (a tensor,
         or a PeerOutput from ``peer_empty``) behind the work queued so far; ``wait()`` orders later
@@ -255,6 +294,12 @@ class ShardedHybSpmm:
 
     def wait(self) -> None:
         self._gatherer.wait(self.group)
+
+
+class _ChunkCalls(list):
+    """The prepared calls of a shard's chunks; ``fused`` says that the kernels themselves store
+    into the peers' buffers, so that no transfer follows them."""
+    fused = False
 
 
 class ShardedSddmm:
@@ -303,15 +348,25 @@ class ShardedSddmm:
         """One call per chunk: ``a`` is the whole row-side operand ``[num_rows_total * feat]`` (only
         the shard's rows are read), ``b`` the replicated column-side operand, ``out_full`` the
         ``[nnz_total]`` result (a tensor or a PeerOutput); each chunk writes its own range of it."""
-        calls = []
+        # with peer memory and the 'fused' transport the kernel stores every finished position
+        # into the peers' buffers itself (sddmm_peers): run() then queues no transfer
+        fused = (isinstance(out_full, PeerOutput) and self.world > 1 and _peer_transport() == "fused"
+                 and feat % 32 == 0 and a.data_ptr() % 32 == 0 and b.data_ptr() % 32 == 0)
+        order = [(self.rank + step) % self.world for step in range(1, self.world)]
+        peers = out_full.peers if fused else None
+        calls = _ChunkCalls()
+        calls.fused = fused
         out_full = local_tensor(out_full)
         for c in range(self.chunks):
             r0, r1 = self.chunk_rows[c], self.chunk_rows[c + 1]
             off, size = self.chunk_offsets[c][self.rank], self.chunk_sizes[c][self.rank]
             args = [a[r0 * feat:r1 * feat], b, out_full[off:off + size], self._ip[c], self._ix[c]]
+            if fused:
+                args += [peers[k].data_ptr() + off * peers[k].element_size() for k in order]
             if self._scale[c] is not None:
                 args.append(self._scale[c])
-            calls.append(ops.sddmm.prepare(*args) if size > 0 else None)
+            fn = ops.sddmm_peers if fused else ops.sddmm
+            calls.append(fn.prepare(*args) if size > 0 else None)
         return calls
 
     def run(self, calls: List, out_full=None) -> None:
@@ -321,7 +376,9 @@ class ShardedSddmm:
         for c, call in enumerate(calls):
             if call is not None:
                 call()
-            if out_full is not None and self.world > 1:
+            if out_full is not None and self.world > 1 and getattr(calls, "fused", False):
+                self._gatherer.p2p_pending = True  # the rows of the others arrive with THEIR kernels
+            elif out_full is not None and self.world > 1:
                 off, size = self.chunk_offsets[c][self.rank], self.chunk_sizes[c][self.rank]
                 self._gatherer.gather(local_tensor(out_full)[off:off + size], self.chunk_sizes[c], out_full,
                                       self.chunk_offsets[c], self.group)

@@ -366,10 +366,19 @@ def ours_arm(args, rank, world, local_rank):
         order = tuple(sorted(FEATS, reverse=True))
 
         gathered = {f: op.prepare_gathered(x_dev[f], y_all[f], f) for f in FEATS}
+        # The five calls are independent: they alternate between two streams, so that the first
+        # rows of one call reach the links while the last blocks of the previous one drain.
+        lanes = [torch.cuda.Stream(), torch.cuda.Stream()]
 
         def gather_step():
-            for f in order:
-                gathered[f]()
+            cur = torch.cuda.current_stream()
+            for s in lanes:
+                s.wait_stream(cur)
+            for i, f in enumerate(order):
+                with torch.cuda.stream(lanes[i % 2]):
+                    gathered[f]()
+            for s in lanes:
+                cur.wait_stream(s)
             op.wait()
 
         gather_ms = timed(gather_step, max(3, min(args.steps, 20)))

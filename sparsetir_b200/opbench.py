@@ -262,7 +262,7 @@ def bench_sddmm_sharded(device, peaks, rank: int, world: int, feats=(32, 128)) -
     out = {"workload": "sddmm_lognormal_232965", "nnz": nnz,
            "graph": "built on the GPU with a torch generator: the twin of datagen.csr_lognormal(seed=0) "
                     "(same degree sequence, other column draws)",
-           "transport": sharded.peer_transport_note() if isinstance(c_out, sharded.PeerOutput) else "NCCL",
+           "transport": sharded.peer_transport_note("sddmm") if isinstance(c_out, sharded.PeerOutput) else "NCCL",
            "rows_per_rank": [int(op.cuts[k + 1] - op.cuts[k]) for k in range(world)],
            "nnz_per_rank": [sum(op.chunk_sizes[c][k] for c in range(op.chunks)) for k in range(world)],
            "chunks": op.chunks, "per_feat": {}}
@@ -368,6 +368,7 @@ def bench_bsrmm_sharded(device, peaks, rank: int, world: int) -> dict:
     flops = 2.0 * bs.nnzb * bs.blk * bs.blk * feat
     res = {"workload": "bsr_spmm_4096_blk32_10pct_F512_f16", "block_rows_per_rank": [r // bs.blk for r in op.rows_per_rank],
            "ms": ms, "gflops": flops / (ms * 1e-3) / 1e9, "ms_with_allgather": ms_g,
+           "transport": sharded.peer_transport_note("bsrmm"),
            "every_rank_matches_oracle": _all_ranks_ok(ok, device)}
     assert res["every_rank_matches_oracle"], "a rank's BSR block rows differ from the oracle"
     return res
@@ -421,7 +422,8 @@ def bench_rgms_sharded(device, peaks, rank: int, world: int) -> dict:
     flops_ref = 2.0 * cf.nnz_j * feat * feat + 2.0 * cf.nnz_j * feat
     res = {"workload": "rgms_100k_46rel_1.5M_F64", "rows_per_rank": op.rows_per_rank,
            "edges_rank0": int(len(s.indices_j)), "ms": ms, "gflops": flops_ref / (ms * 1e-3) / 1e9,
-           "ms_with_allgather": ms_g, "every_rank_matches_oracle": _all_ranks_ok(ok, device)}
+           "ms_with_allgather": ms_g, "transport": sharded.peer_transport_note("rgms"),
+           "every_rank_matches_oracle": _all_ranks_ok(ok, device)}
     assert res["every_rank_matches_oracle"], "a rank's RGMS rows differ from the oracle"
     return res
 

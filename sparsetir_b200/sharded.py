@@ -109,22 +109,34 @@ def local_tensor(out) -> torch.Tensor:
     return out.tensor if isinstance(out, PeerOutput) else out
 
 
-def _peer_transport() -> str:
-    """How a block reaches the peers' buffers: ``scatter`` (one kernel of this library that stores
-    the block to every peer) or ``copy`` (one copy-engine transfer per peer).
-    ``SPARSETIR_PEER_TRANSPORT`` selects; the default is the faster one measured on NVSwitch."""
-    v = os.environ.get("SPARSETIR_PEER_TRANSPORT", "fused").lower()
+_TRANSPORT_DEFAULT = {
+    # measured on NVSwitch (2 and 4 B200s), step ending with the output whole on every rank:
+    "hyb_spmm": "fused",   # 0.56 against 0.68 ms (2 GPUs), 0.96 against 1.22 ms (4 GPUs) for copy engines
+    "sddmm": "copy",       # long gather-bound kernels: copy engines overlap them without SM time
+    "bsrmm": "scatter",    # blocks of a few MB: one kernel costs 46 us where three transfers cost 117
+    "rgms": "scatter",
+}
+
+
+def _peer_transport(op: str = "hyb_spmm") -> str:
+    """How an operator's blocks reach the peers' buffers: ``fused`` (hyb SpMM and SDDMM: the
+    kernel that finishes an output row stores it to every peer itself), ``scatter`` (one kernel
+    after the call reads the block once and stores it to every peer) or ``copy`` (one copy-engine
+    transfer per peer after the call).  ``SPARSETIR_PEER_TRANSPORT`` overrides the per-operator
+    default; operators without a fused form take ``scatter`` for ``fused``."""
+    v = os.environ.get("SPARSETIR_PEER_TRANSPORT", _TRANSPORT_DEFAULT[op]).lower()
     if v not in ("fused", "scatter", "copy"):
         raise ValueError(f"SPARSETIR_PEER_TRANSPORT={v!r}: expected 'fused', 'scatter' or 'copy'")
+    if v == "fused" and op not in ("hyb_spmm", "sddmm"):
+        v = "scatter"
     return v
 
 
-def peer_transport_note() -> str:
-    """One line for reports: what moves the blocks into the peers' buffers."""
-    return {"fused": "the SpMM kernel stores every finished row into the peers' buffers itself "
-                     "(hyb SpMM; other operators: one scatter kernel after the call)",
+def peer_transport_note(op: str = "hyb_spmm") -> str:
+    """One line for reports: what moves the operator's blocks into the peers' buffers."""
+    return {"fused": "the kernel that finishes an output row stores it into the peers' buffers itself",
             "scatter": "one kernel after the call reads the block once and stores it to every peer",
-            "copy": "one copy-engine transfer per peer after the call"}[_peer_transport()] + \
+            "copy": "one copy-engine transfer per peer after the call"}[_peer_transport(op)] + \
         "; peer memory from torch symmetric memory, completion by a one-element all-reduce"
 
 
@@ -140,8 +152,9 @@ class _Gatherer:
     rank have completed (a rank enters the all-reduce only after its own copies).
     Into a plain tensor the blocks go through NCCL (one group of broadcasts for unequal blocks)."""
 
-    def __init__(self, device: torch.device):
+    def __init__(self, device: torch.device, op: str = "hyb_spmm"):
         self.device = device
+        self.op = op
         self.stream = torch.cuda.Stream(device=device) if device.type == "cuda" else None
         self.peer_streams: List = []
         self.pending: List = []
@@ -172,7 +185,7 @@ class _Gatherer:
                 ready.record()
                 lo, hi = int(offsets[rank]), int(offsets[rank]) + int(sizes[rank])
                 order = [(rank + step) % world for step in range(1, world)]  # every rank starts with another peer
-                if _peer_transport() in ("scatter", "fused"):
+                if _peer_transport(self.op) in ("scatter", "fused"):
                     # one kernel: the block is read once and stored to every peer
                     from . import _lib as L
                     src = local.contiguous()
@@ -250,7 +263,7 @@ class ShardedHybSpmm:
         self.rows_per_rank = self.shard.rows_per_rank()
         self.row_offsets = [int(c) for c in self.shard.cuts[:-1]]
         self.referenced_cols = int(np.unique(self.shard.indices).size)
-        self._gatherer = _Gatherer(self.device)
+        self._gatherer = _Gatherer(self.device, "hyb_spmm")
 
     def prepare(self, x: torch.Tensor, y_local: torch.Tensor, feat: int) -> ops.PreparedCall:
         """The shard's call: ``x`` is the whole dense operand ``[num_cols * feat]`` on this GPU,
@@ -262,19 +275,33 @@ class ShardedHybSpmm:
         (``out`` from ``peer_empty``, or a plain tensor); ``wait()`` after it orders later work
         behind the other ranks' rows.  With peer memory and the 'fused' transport the SpMM kernel
         itself stores each finished row into every peer's buffer (``hyb_spmm_peers``): no copy
-        follows the kernel.  Otherwise the kernel writes this rank's rows and a gather follows."""
+        follows the kernel.  Otherwise the kernel writes this rank's rows and a gather follows.
+        As with any collective into a reused buffer: a rank may run the call again only when every
+        rank is done reading the previous result (a ``wait()``, or any other collective, after the
+        reads)."""
         lo = self.row_offsets[self.rank] * feat
         n = self.rows_per_rank[self.rank] * feat
         mine = local_tensor(out)[lo:lo + n]
         if isinstance(out, PeerOutput) and self.world > 1 and self.flags == 0 and _peer_transport() == "fused":
             order = [(self.rank + step) % self.world for step in range(1, self.world)]
             peer_c = [out.peers[k].data_ptr() + lo * out.peers[k].element_size() for k in order]
-            call = ops.hyb_spmm_peers.prepare(*ops.hyb_args(x, mine, self.buckets, feat, 0, peer_c=peer_c))
+            fused_call = ops.hyb_spmm_peers.prepare(*ops.hyb_args(x, mine, self.buckets, feat, 0, peer_c=peer_c))
+            plain_call = self.prepare(x, mine, feat)
             gatherer = self._gatherer
+            state = {"fused": True}
 
             def run_fused() -> None:
-                call()
-                gatherer.p2p_pending = True  # the peers' rows arrive with THEIR kernels: wait() meets them
+                if state["fused"]:
+                    try:
+                        fused_call()
+                        gatherer.p2p_pending = True  # the peers' rows arrive with THEIR kernels: wait() meets them
+                        return
+                    except ops.SparseTIRError:
+                        # shapes the one-writer kernel does not take (refused before any launch):
+                        # from now on the plain call followed by a transfer
+                        state["fused"] = False
+                plain_call()
+                self.gather(mine, feat, out)
 
             return run_fused
         call = self.prepare(x, mine, feat)
@@ -342,7 +369,7 @@ class ShardedSddmm:
             self._ix.append(to_dev(indices[p0:p1]).contiguous())
             self._scale.append(None if scale is None else to_dev(scale[p0:p1]).contiguous())
         self.chunks = chunks
-        self._gatherer = _Gatherer(self.device)
+        self._gatherer = _Gatherer(self.device, "sddmm")
 
     def prepare(self, a: torch.Tensor, b: torch.Tensor, out_full, feat: int) -> List[ops.PreparedCall]:
         """One call per chunk: ``a`` is the whole row-side operand ``[num_rows_total * feat]`` (only
@@ -350,7 +377,7 @@ class ShardedSddmm:
         ``[nnz_total]`` result (a tensor or a PeerOutput); each chunk writes its own range of it."""
         # with peer memory and the 'fused' transport the kernel stores every finished position
         # into the peers' buffers itself (sddmm_peers): run() then queues no transfer
-        fused = (isinstance(out_full, PeerOutput) and self.world > 1 and _peer_transport() == "fused"
+        fused = (isinstance(out_full, PeerOutput) and self.world > 1 and _peer_transport("sddmm") == "fused"
                  and feat % 32 == 0 and a.data_ptr() % 32 == 0 and b.data_ptr() % 32 == 0)
         order = [(self.rank + step) % self.world for step in range(1, self.world)]
         peers = out_full.peers if fused else None
@@ -403,7 +430,7 @@ class ShardedBsrmm:
         self._ip, self._ix = _dev(self.shard.indptr, self.device), _dev(self.shard.indices, self.device)
         self.rows_per_rank = [int(self.shard.cuts[k + 1] - self.shard.cuts[k]) * self.blk for k in range(self.world)]
         self.row_offsets = [int(c) * self.blk for c in self.shard.cuts[:-1]]
-        self._gatherer = _Gatherer(self.device)
+        self._gatherer = _Gatherer(self.device, "bsrmm")
 
     def prepare(self, b: torch.Tensor, c_local: torch.Tensor, feat: int) -> Optional[ops.PreparedCall]:
         if self.block_rows == 0:
@@ -434,7 +461,7 @@ class ShardedRgms:
         self._arrays = [_dev(v, self.device) for v in (s.data, s.indptr_i, s.indices_i, s.indptr_j, s.indices_j)]
         self.rows_per_rank = [int(s.cuts[k + 1] - s.cuts[k]) for k in range(self.world)]
         self.row_offsets = [int(c) for c in s.cuts[:-1]]
-        self._gatherer = _Gatherer(self.device)
+        self._gatherer = _Gatherer(self.device, "rgms")
 
     def prepare(self, w: torch.Tensor, x: torch.Tensor, y_local: torch.Tensor) -> Optional[ops.PreparedCall]:
         """``y_local [shard rows * feat]`` is accumulated into (zero-fill it first)."""

@@ -162,9 +162,10 @@ class _Gatherer:
         self._token = None
 
     def gather(self, local: torch.Tensor, sizes: Sequence[int], out, offsets: Sequence[int],
-               group=None) -> None:
+               group=None, transport: Optional[str] = None) -> None:
         """Blocks of ``sizes[k]`` elements, rank k's going to ``out[offsets[k]:offsets[k]+sizes[k]]``
-        on every rank; runs after everything queued so far on the current stream."""
+        on every rank; runs after everything queued so far on the current stream.  ``transport``
+        ('scatter' or 'copy') overrides the operator's default for this block."""
         world, rank = _world(group), _rank(group)
         mine = local_tensor(out)[int(offsets[rank]):int(offsets[rank]) + int(sizes[rank])]
         if local.numel() != sizes[rank]:
@@ -185,7 +186,7 @@ class _Gatherer:
                 ready.record()
                 lo, hi = int(offsets[rank]), int(offsets[rank]) + int(sizes[rank])
                 order = [(rank + step) % world for step in range(1, world)]  # every rank starts with another peer
-                if _peer_transport(self.op) in ("scatter", "fused"):
+                if (transport or _peer_transport(self.op)) in ("scatter", "fused"):
                     # one kernel: the block is read once and stored to every peer
                     from . import _lib as L
                     src = local.contiguous()
@@ -327,6 +328,7 @@ class _ChunkCalls(list):
     """The prepared calls of a shard's chunks; ``fused`` says that the kernels themselves store
     into the peers' buffers, so that no transfer follows them."""
     fused = False
+    transport: Optional[str] = None  # 'scatter' / 'copy' chosen for these calls, None = the default
 
 
 class ShardedSddmm:
@@ -383,6 +385,15 @@ class ShardedSddmm:
         peers = out_full.peers if fused else None
         calls = _ChunkCalls()
         calls.fused = fused
+        if "SPARSETIR_PEER_TRANSPORT" not in os.environ and self.world > 1:
+            # Copy engines hide a chunk's transfer behind the next chunk's kernels; when the
+            # transfer is more than twice as long as those kernels there is little to hide behind
+            # and the scatter kernel's lower fixed cost wins (4 GPUs, F = 32: 0.83 against 1.00 ms).
+            # Estimates per stored position: 4 (N-1) bytes over ~660 GB/s of NVLink against
+            # 4 F bytes of gathered row over ~15 TB/s of L2-to-SM rate.
+            transfer = 4.0 * (self.world - 1) / 660e9
+            kernels = 4.0 * feat / 15e12
+            calls.transport = "scatter" if transfer > 2.0 * kernels else "copy"
         out_full = local_tensor(out_full)
         for c in range(self.chunks):
             r0, r1 = self.chunk_rows[c], self.chunk_rows[c + 1]
@@ -408,7 +419,7 @@ class ShardedSddmm:
             elif out_full is not None and self.world > 1:
                 off, size = self.chunk_offsets[c][self.rank], self.chunk_sizes[c][self.rank]
                 self._gatherer.gather(local_tensor(out_full)[off:off + size], self.chunk_sizes[c], out_full,
-                                      self.chunk_offsets[c], self.group)
+                                      self.chunk_offsets[c], self.group, getattr(calls, "transport", None))
 
     def wait(self) -> None:
         self._gatherer.wait(self.group)

@@ -190,27 +190,10 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
                                           const float* __restrict__ wts, int r0, int nr, int nslots,
                                           int per_row, const char* __restrict__ bl,
                                           unsigned row_bytes, int lane, unsigned mask,
-                                          RowFlag&& row_flag, RowEnd&& row_end, int* stage = nullptr) {
+                                          RowFlag&& row_flag, RowEnd&& row_end) {
   using LV = LaneVec<W>;
   using V = typename LV::type;
   constexpr int U = (32 / W) < LPR ? (32 / W) : LPR;  // gathered rows in flight: 32 registers
-#ifdef SPTIR_HYB_STAGE
-  // ids and weights of a batch go through shared memory: stage[buf][0][LPR] ids, stage[buf][1][LPR]
-  // weights; four of either come back with one broadcast 16-byte load instead of four shuffles
-  static_assert(U % 4 == 0, "ids are read four at a time");
-  auto ids4 = [&](int buf, int k) -> int4 {
-    return *reinterpret_cast<const int4*>(stage + buf * 2 * LPR + k);
-  };
-  auto wts4 = [&](int buf, int k) -> float4 {
-    return *reinterpret_cast<const float4*>(stage + buf * 2 * LPR + LPR + k);
-  };
-  auto put = [&](int buf, int col, float wt) {
-    stage[buf * 2 * LPR + lane] = col;
-    stage[buf * 2 * LPR + LPR + lane] = __float_as_int(wt);
-    __syncwarp(mask);
-  };
-  int buf = 0;
-#endif
   // address of this lane's vector in dense row `col`: one 32x32->64 multiply-add
   auto vec_of = [&](const char* base, int col) -> const char* {
     return base + static_cast<unsigned long long>(static_cast<unsigned>(col)) * row_bytes;
@@ -231,9 +214,6 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
     if (lane < nr) rf = row_flag(r0 + lane);                  // all rows of the item (nr <= LPR)
   }
   int left = per_row, jrow = 0;  // wide rows only
-#ifdef SPTIR_HYB_STAGE
-  put(0, c, a);
-#endif
 
   for (int s0 = 0; s0 < nslots; s0 += LPR) {
     int cn = 0, rfn = 0;
@@ -248,27 +228,6 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
 #pragma unroll
       for (int k0 = 0; k0 < LPR; k0 += U) {
         V x[U];
-#ifdef SPTIR_HYB_STAGE
-#pragma unroll
-        for (int u = 0; u < U; u += 4) {
-          const int4 q = ids4(buf, k0 + u);
-          x[u] = LV::ldg(vec_of(bl, q.x));
-          x[u + 1] = LV::ldg(vec_of(bl, q.y));
-          x[u + 2] = LV::ldg(vec_of(bl, q.z));
-          x[u + 3] = LV::ldg(vec_of(bl, q.w));
-        }
-#pragma unroll
-        for (int u = 0; u < U; u += 4) {
-          const float4 wv = wts4(buf, k0 + u);
-          const float wk[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            LV::fma(acc, wk[v], x[u + v]);
-            if (WM < 8 && (k0 + u + v + 1) % WM == 0)
-              row_end(acc, __shfl_sync(mask, rf, (k0 + u + v) / WM, LPR));
-          }
-        }
-#else
 #pragma unroll
         for (int u = 0; u < U; ++u)
           x[u] = LV::ldg(vec_of(bl, __shfl_sync(mask, c, k0 + u, LPR)));
@@ -278,7 +237,6 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
           if (WM < 8 && (k0 + u + 1) % WM == 0)
             row_end(acc, __shfl_sync(mask, rf, (k0 + u) / WM, LPR));
         }
-#endif
         if (WM == 8) {
           left -= U;
           if (left == 0) {
@@ -319,10 +277,6 @@ __device__ __forceinline__ void lean_item(const int32_t* __restrict__ cols,
     c = cn;
     a = an;
     if (WM < 8) rf = rfn;
-#ifdef SPTIR_HYB_STAGE
-    buf ^= 1;
-    if (s0 + LPR < nslots) put(buf, c, a);
-#endif
   }
 }
 
@@ -449,12 +403,6 @@ hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const __grid_constant_
   const PeerOut* po = PEERS ? &la.peers : nullptr;
   constexpr int SUBS = kThreads / LPR;
   __shared__ __align__(32) float s_part[SUBS][LPR * W];  // wide rows: partial sums of the spans
-#ifdef SPTIR_HYB_STAGE
-  __shared__ __align__(16) int s_stage[SUBS][2][2][LPR];
-  int* stage = &s_stage[threadIdx.x / LPR][0][0][0];
-#else
-  int* stage = nullptr;
-#endif
   const int lane = threadIdx.x % LPR;
   const int sub = threadIdx.x / LPR;
   const unsigned mask = group_mask<LPR>();
@@ -504,10 +452,10 @@ hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const __grid_constant_
     const int32_t* cols = tb.cols[q] + first;
     const float* wts = tb.w[q] + first;
     const int nslots = nr * width;
-    if (width == 1) lean_item<LPR, 1, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end, stage);
-    else if (width == 2) lean_item<LPR, 2, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end, stage);
-    else if (width == 4) lean_item<LPR, 4, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end, stage);
-    else lean_item<LPR, 8, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end, stage);
+    if (width == 1) lean_item<LPR, 1, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end);
+    else if (width == 2) lean_item<LPR, 2, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end);
+    else if (width == 4) lean_item<LPR, 4, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end);
+    else lean_item<LPR, 8, W>(cols, wts, r0, nr, nslots, width, bl, stride, lane, mask, row_flag, row_end);
     return;
   }
 
@@ -526,7 +474,7 @@ hyb_spmm_lean_kernel(const __grid_constant__ HybTable tb, const __grid_constant_
     auto no_flag = [](int) -> int { return 0; };
     auto keep = [&](V& acc, int) { total = acc; };
     lean_item<LPR, 8, W>(tb.cols[q] + first, tb.w[q] + first, r, 1, nslots, nslots, bl, stride, lane, mask,
-                         no_flag, keep, stage);
+                         no_flag, keep);
   }
   if (part != 0) LV::sts(&s_part[sub][lane * W], total);
   __syncthreads();

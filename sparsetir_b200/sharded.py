@@ -8,7 +8,9 @@ package that: construction shards and uploads the structure (every rank passes t
 matrix), ``run`` launches the shard's kernels, ``gather`` all-gathers the output blocks over NCCL
 into the full result on every rank, optionally in row chunks so that the gather of chunk k
 overlaps the kernels of chunk k + 1.  Into a buffer from ``peer_empty`` the gather is done by
-direct writes into the other GPUs' memory over NVLink (one copy per peer), otherwise by NCCL.
+direct writes into the other GPUs' memory over NVLink — by the operator's own kernel where it has
+a form that stores to peers (hyb SpMM, SDDMM), by one scatter kernel, or by one copy-engine
+transfer per peer — otherwise by NCCL.
 ``replicate_rows`` is the other collective of the path: every rank contributes an equal block of
 rows of the dense operand.
 
@@ -144,12 +146,14 @@ class _Gatherer:
     """All-gather of per-rank output blocks, issued on side streams so that it overlaps whatever
     the caller launches next.
 
-    Into a PeerOutput every rank WRITES its block straight into the other ranks' buffers: one
-    device-to-device copy per peer over NVLink (copy engines, no SM time), all peers at once —
-    measured 740 GB/s out of one GPU against 160-280 GB/s for the NCCL all-gather of the same
-    unequal blocks on two GPUs.  ``wait()`` then joins the copy streams and meets the other ranks
-    in a one-element NCCL all-reduce: when it completes on a rank, every peer's copies into that
-    rank have completed (a rank enters the all-reduce only after its own copies).
+    Into a PeerOutput every rank WRITES its block straight into the other ranks' buffers over
+    NVLink: with one kernel of this library that reads the block once and stores it to every peer
+    (``scatter``), or with one copy-engine transfer per peer, all peers at once (``copy``; no SM
+    time, so it overlaps long kernels) — see ``_peer_transport``.  ``wait()`` then joins the side
+    streams and meets the other ranks in a one-element NCCL all-reduce: when it completes on a
+    rank, every peer's writes into that rank have completed (a rank enters the all-reduce only
+    after its own).  Operators whose kernels store into the peers themselves (``fused``) only mark
+    the gatherer pending, so that ``wait()`` runs the same completion step.
     Into a plain tensor the blocks go through NCCL (one group of broadcasts for unequal blocks)."""
 
     def __init__(self, device: torch.device, op: str = "hyb_spmm"):

@@ -137,3 +137,23 @@ def test_single_process_layer_is_identity():
     sd = sharded.ShardedSddmm(g.indptr, g.indices, None, g.n, chunks=4, device=CPU)
     assert sd.chunks == 1 and sd.chunk_sizes == [[g.nnz]] and sd.chunk_offsets == [[0]]
     assert sharded.row_block(10, 4) == 3
+
+
+def test_transport_selection(monkeypatch):
+    # per-operator defaults, the environment override, operators without a fused form
+    from sparsetir_b200 import sharded
+    monkeypatch.delenv("SPARSETIR_PEER_TRANSPORT", raising=False)
+    assert sharded._peer_transport("hyb_spmm") == "fused"
+    assert sharded._peer_transport("sddmm") == "copy"
+    assert sharded._peer_transport("bsrmm") == "scatter" and sharded._peer_transport("rgms") == "scatter"
+    monkeypatch.setenv("SPARSETIR_PEER_TRANSPORT", "fused")
+    assert sharded._peer_transport("sddmm") == "fused"
+    assert sharded._peer_transport("rgms") == "scatter"  # no kernel of RGMS finishes a row alone
+    monkeypatch.setenv("SPARSETIR_PEER_TRANSPORT", "COPY")
+    assert sharded._peer_transport("hyb_spmm") == "copy"
+    monkeypatch.setenv("SPARSETIR_PEER_TRANSPORT", "carrier-pigeon")
+    with pytest.raises(ValueError, match="SPARSETIR_PEER_TRANSPORT"):
+        sharded._peer_transport("hyb_spmm")
+    for op in ("hyb_spmm", "sddmm", "bsrmm", "rgms"):
+        monkeypatch.setenv("SPARSETIR_PEER_TRANSPORT", "scatter")
+        assert "stores it to every peer" in sharded.peer_transport_note(op)

@@ -40,8 +40,14 @@ constexpr int kMaxB = SPARSETIR_HYB_MAX_BUCKETS;
 // Stored slots covered by one work item (one sub-warp of `lpr` lanes): four id batches, so that
 // the per-item set-up is amortised and the id prefetch of spmm_core.cuh has something to hide.
 constexpr int item_slots(int lpr) { return 4 * lpr; }
-// lean kernel: lpr lanes of w floats each; 4 batches of ids with 16-byte lanes, 8 with 32-byte lanes
-constexpr int lean_item_slots(int lpr, int w) { return lpr * w; }
+// lean kernel: lpr lanes of w floats each, `tiles` feature tiles (blockIdx.y).  Batches of ids
+// per item, measured on the 169,343-node power-law graph: with four feature tiles or more, 8
+// batches of 16-byte lanes (step over F = 32..512 0.386 ms; 4 batches 0.394, 12 batches 0.425,
+// 16 batches 0.448; F = 128 59 against 64 us, F = 512 183 against 188 us) — the launch has blocks
+// enough, and longer items hide more of the id loads; with fewer tiles 4 batches (F = 32: 26.0
+// against 27.3 us).  32-byte lanes: 8 batches (the row ids of an item's rows of 8 slots or more
+// travel in one register per lane, which caps an item at lpr such rows).
+inline int lean_item_slots(int lpr, int w, int tiles) { return lpr * w * ((w == 4 && tiles >= 4) ? 2 : 1); }
 
 struct HybTable {
   const float* w[kMaxB];
@@ -643,6 +649,8 @@ void plan_items(HybTable& tb, int item) {
 void plan_items_lean(HybTable& tb, int item, int subs) {
   for (int q = 0; q < tb.nb; ++q) {
     tb.rows_per_item[q] = std::max(1, item / tb.width[q]);
+    // rows of 8 slots or more: the row ids of an item travel in one register per lane
+    if (tb.width[q] >= 8) tb.rows_per_item[q] = std::min(tb.rows_per_item[q], kThreads / subs);
     int spr = 1;
     while (spr < subs && spr * item < tb.width[q]) spr *= 2;
     tb.chunks_per_row[q] = spr;
@@ -713,7 +721,7 @@ long long plan_blocks(HybTable& tb, int subs) {
 
 template <int LPR, int W>
 int launch_lean(HybTable& tb, const LeanArgs& la, cudaStream_t stream) {
-  plan_items_lean(tb, lean_item_slots(LPR, W), kThreads / LPR);
+  plan_items_lean(tb, lean_item_slots(LPR, W, la.feat / (W * LPR)), kThreads / LPR);
   const long long blocks = plan_blocks_lean(tb, kThreads / LPR);
   if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
   dim3 grid(static_cast<unsigned>(blocks), la.feat / (W * LPR));

@@ -30,9 +30,10 @@
 
 namespace sptir {
 
-// defined in rgms_tc.cu; returns 1 when the shape is not supported by the tensor-core path
-int csrmm_impl(const float* a, const float* b, float* c, const int32_t* indptr, const int32_t* indices,
-               int m, int n, int feat, int nnz, int device_id, void* stream, bool hub_rows);
+// defined in csrmm.cu: the CSR SpMM launcher with 32-byte lanes, never the hub-row launches
+int csrmm_short_rows_impl(const float* a, const float* b, float* c, const int32_t* indptr,
+                          const int32_t* indices, int m, int n, int feat, int nnz, int device_id,
+                          void* stream);
 int rgms_fused_launch(const float* a, const float* w, const float* x, float* y, const int32_t* indptr_i,
                       const int32_t* indices_i, const int32_t* indptr_j, const int32_t* indices_j,
                       int num_rels, int feat, int nnz_i, int nnz_j, int n, int m, cudaStream_t stream);
@@ -232,7 +233,7 @@ extern "C" int sparsetir_rgms_raw(const float* a, const float* w, const float* x
       if (!fused)
         z = static_cast<float*>(workspace(device_id, st, static_cast<size_t>(nnz_i) * 64 * sizeof(float)));
       if (z != nullptr) {
-        if (csrmm_impl(a, x, z, indptr_j, indices_j, nnz_i, n, 64, nnz_j, device_id, stream, /*hub_rows=*/false) != 0)
+        if (csrmm_short_rows_impl(a, x, z, indptr_j, indices_j, nnz_i, n, 64, nnz_j, device_id, stream) != 0)
           return -1;
       }
       int rc = rgms_tc_launch(a, w, x, y, indptr_i, indices_i, indptr_j, indices_j, num_rels, feat,

@@ -725,10 +725,14 @@ int launch_lean(HybTable& tb, const LeanArgs& la, cudaStream_t stream) {
   const long long blocks = plan_blocks_lean(tb, kThreads / LPR);
   if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
   dim3 grid(static_cast<unsigned>(blocks), la.feat / (W * LPR));
-  if (la.peers.n > 0)
-    hyb_spmm_lean_kernel<LPR, W, true><<<grid, kThreads, 0, stream>>>(tb, la);
-  else
+  if (la.peers.n > 0) {
+    if constexpr (W == 4)
+      hyb_spmm_lean_kernel<LPR, W, true><<<grid, kThreads, 0, stream>>>(tb, la);
+    else
+      return fail("sparsetir_hyb_spmm_peers: no 32-byte-lane form");  // the dispatcher picks 16-byte lanes
+  } else {
     hyb_spmm_lean_kernel<LPR, W, false><<<grid, kThreads, 0, stream>>>(tb, la);
+  }
   SPTIR_LAUNCH_OK("hyb_spmm_lean_kernel");
   return 0;
 }
@@ -836,7 +840,9 @@ int hyb_spmm_run(const float* b, float* c, const SparsetirEllBucket* buckets, co
     const int w = tb.width[q];
     lean = lean && (w == 1 || w == 2 || w == 4 || w % 8 == 0);
   }
-  int lane_w = (lean && feat % 32 == 0 && aligned32(b) && aligned32(c)) ? max_lane_floats() : 4;
+  const bool to_peers = peers != nullptr && peers->n > 0;
+  // the form that stores to peers exists for 16-byte lanes only (the library's default)
+  int lane_w = (lean && !to_peers && feat % 32 == 0 && aligned32(b) && aligned32(c)) ? max_lane_floats() : 4;
   int lanes = lanes_per_row_impl(feat, vec4, n, lane_w);
   if (lane_w == 8 && feat % (lane_w * lanes) != 0) {  // no whole tiles of 8-float lanes
     lane_w = 4;
@@ -844,7 +850,6 @@ int hyb_spmm_run(const float* b, float* c, const SparsetirEllBucket* buckets, co
   }
   lean = lean && feat % (lane_w * lanes) == 0;
   const size_t c_bytes = static_cast<size_t>(m) * feat * sizeof(float);
-  const bool to_peers = peers != nullptr && peers->n > 0;
   if (to_peers && (!lean || all_atomic || (flags & SPARSETIR_HYB_ZERO_C)))
     return fail("sparsetir_hyb_spmm_peers: needs the one-writer kernel (feat_size a multiple of its tile, "
                 "16-byte aligned b and c, bucket widths 1, 2, 4 or multiples of 8, no ALL_ATOMIC or ZERO_C "

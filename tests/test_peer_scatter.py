@@ -153,3 +153,94 @@ def test_sddmm_peers_refuses_what_it_cannot_do(cuda_device):
         ops.sddmm_peers(*base, other.data_ptr())
     with pytest.raises(ops.SparseTIRError, match="peer"):
         ops.sddmm_peers(*base)
+
+
+# ---- random shapes: the peer-storing forms against the plain calls, bit for bit
+
+@pytest.mark.parametrize("seed", range(24))
+def test_fuzz_hyb_spmm_peers_equals_plain_call(cuda_device, seed):
+    import numpy as np
+    import test_gpu_fuzz as F
+    import test_gpu_ops as T
+    from sparsetir_b200 import datagen as dg, ops
+    rng = np.random.default_rng(7000 + seed)
+    n = int(rng.integers(2, 3000))
+    c = F.random_csr(rng, n, n)
+    feat = int(rng.choice([32, 64, 96, 128, 160, 256, 512]))
+    nb = int(rng.integers(1, 8))
+    buckets = sorted(set(int(b) for b in rng.choice([1, 2, 4, 8, 16, 24, 32, 64, 128, 256, 512], size=nb)))
+    x = T.dev(dg.dense_operand(seed, n, feat), cuda_device).reshape(-1)
+    _, devb = T.hyb_device_buckets(c, 1, buckets, cuda_device)
+    plain = torch.zeros(c.m * feat, device=cuda_device)
+    ops.hyb_spmm(*ops.hyb_args(x, plain, devb, feat))
+    y = torch.zeros(c.m * feat, device=cuda_device)
+    copies = [torch.zeros(c.m * feat, device=cuda_device) for _ in range(int(rng.integers(1, 4)))]
+    try:
+        ops.hyb_spmm_peers(*ops.hyb_args(x, y, devb, feat, 0, peer_c=[t.data_ptr() for t in copies]))
+    except ops.SparseTIRError as e:
+        # a feature count that is not a whole number of the kernel's tiles (96, 160): refused
+        # before any launch, nothing written
+        assert "one-writer" in str(e) and feat in (96, 160)
+        torch.cuda.synchronize()
+        assert not bool(y.any()) and not any(bool(t.any()) for t in copies)
+        return
+    torch.cuda.synchronize()
+    assert torch.equal(y, plain)
+    for t in copies:  # rows in no bucket stay zero in all of them
+        assert torch.equal(t, plain)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_fuzz_sddmm_peers_equals_plain_call(cuda_device, seed):
+    import numpy as np
+    import test_gpu_fuzz as F
+    import test_gpu_ops as T
+    from sparsetir_b200 import datagen as dg, ops
+    rng = np.random.default_rng(8000 + seed)
+    m, n = int(rng.integers(1, 2000)), int(rng.integers(1, 2000))
+    c = F.random_csr(rng, m, n)
+    if c.nnz == 0:
+        pytest.skip("no stored position")
+    feat = int(rng.choice([32, 64, 96, 128, 256, 288, 512]))
+    a, b = dg.dense_operand(seed, m, feat), dg.dense_operand(seed + 1, n, feat)
+    plain = T.run_sddmm(c, a, b, cuda_device)
+    out = torch.full((c.nnz,), -7.0, device=cuda_device)
+    copies = [torch.full((c.nnz,), -1.0, device=cuda_device) for _ in range(int(rng.integers(1, 4)))]
+    ops.sddmm_peers(T.dev(a.reshape(-1), cuda_device), T.dev(b.reshape(-1), cuda_device), out,
+                    T.dev(c.indptr, cuda_device), T.dev(c.indices, cuda_device), *[t.data_ptr() for t in copies])
+    torch.cuda.synchronize()
+    assert torch.equal(out, plain)
+    for t in copies:
+        assert torch.equal(t, plain)
+
+
+def test_hyb_spmm_peers_with_32_byte_lanes_selected_in_child_process(cuda_device):
+    # SPARSETIR_LANE_FLOATS=8 selects 32-byte lanes for the plain call; the peer-storing form keeps
+    # 16-byte lanes and must still agree with the oracle (split rows included)
+    import subprocess
+    import sys
+    code = r'''
+import os, sys
+sys.path.insert(0, os.path.join(os.getcwd(), "tests"))
+import numpy as np, torch
+import test_gpu_ops as T
+from sparsetir_b200 import datagen as dg, ops
+dev = torch.device("cuda", 0)
+for feat in (32, 64, 128):
+    c = dg.csr_powerlaw(n=5000, max_deg=3000, seed=10 + feat)
+    host, devb = T.hyb_device_buckets(c, 1, T.BK10, dev)
+    xh = dg.dense_operand(1, c.n, feat)
+    x = torch.from_numpy(xh).to(dev).reshape(-1)
+    y = torch.zeros(c.m * feat, device=dev)
+    cp = torch.zeros(c.m * feat, device=dev)
+    ops.hyb_spmm_peers(*ops.hyb_args(x, y, devb, feat, 0, peer_c=[cp.data_ptr()]))
+    torch.cuda.synchronize()
+    assert torch.equal(y, cp)
+    T.close(y, T.oracle_hyb(host, xh, c.m))
+print("ok")
+'''
+    import os
+    env = dict(os.environ, SPARSETIR_LANE_FLOATS="8")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]

@@ -40,14 +40,19 @@ constexpr int kMaxB = SPARSETIR_HYB_MAX_BUCKETS;
 // Stored slots covered by one work item (one sub-warp of `lpr` lanes): four id batches, so that
 // the per-item set-up is amortised and the id prefetch of spmm_core.cuh has something to hide.
 constexpr int item_slots(int lpr) { return 4 * lpr; }
-// lean kernel: lpr lanes of w floats each, `tiles` feature tiles (blockIdx.y).  Batches of ids
-// per item, measured on the 169,343-node power-law graph: with four feature tiles or more, 8
-// batches of 16-byte lanes (step over F = 32..512 0.386 ms; 4 batches 0.394, 12 batches 0.425,
-// 16 batches 0.448; F = 128 59 against 64 us, F = 512 183 against 188 us) — the launch has blocks
-// enough, and longer items hide more of the id loads; with fewer tiles 4 batches (F = 32: 26.0
-// against 27.3 us).  32-byte lanes: 8 batches (the row ids of an item's rows of 8 slots or more
-// travel in one register per lane, which caps an item at lpr such rows).
-inline int lean_item_slots(int lpr, int w, int tiles) { return lpr * w * ((w == 4 && tiles >= 4) ? 2 : 1); }
+// lean kernel: lpr lanes of w floats each, `tiles` feature tiles (blockIdx.y), `slots` stored
+// slots in all buckets.  Batches of ids per item, measured on the 169,343-node power-law graph
+// (945,629 slots): with four feature tiles or more, 8 batches of 16-byte lanes (step over
+// F = 32..512 0.385 ms; 4 batches 0.394, 12 batches 0.425, 16 batches 0.448; F = 128 59 against
+// 64 us, F = 512 183 against 188 us) — longer items hide more of the id loads; with fewer tiles 4
+// batches (F = 32: 26.0 against 27.3 us).  Row shards of that graph (half or a quarter of the
+// slots) lose 5-9 % with 8 batches (F = 512 on half: 115 against 109 us): a pass over one feature
+// tile then has too few blocks, so the longer items are for launches of 3/4 M slots or more.
+// 32-byte lanes: 8 batches (the row ids of an item's rows of 8 slots or more travel in one
+// register per lane, which caps an item at lpr such rows).
+inline int lean_item_slots(int lpr, int w, int tiles, long long slots) {
+  return lpr * w * ((w == 4 && tiles >= 4 && slots >= 3 * (1ll << 18)) ? 2 : 1);
+}
 
 struct HybTable {
   const float* w[kMaxB];
@@ -721,7 +726,9 @@ long long plan_blocks(HybTable& tb, int subs) {
 
 template <int LPR, int W>
 int launch_lean(HybTable& tb, const LeanArgs& la, cudaStream_t stream) {
-  plan_items_lean(tb, lean_item_slots(LPR, W, la.feat / (W * LPR)), kThreads / LPR);
+  long long slots = 0;
+  for (int q = 0; q < tb.nb; ++q) slots += static_cast<long long>(tb.nrows[q]) * tb.width[q];
+  plan_items_lean(tb, lean_item_slots(LPR, W, la.feat / (W * LPR), slots), kThreads / LPR);
   const long long blocks = plan_blocks_lean(tb, kThreads / LPR);
   if (blocks < 0) return fail("sparsetir_hyb_spmm: too many thread blocks");
   dim3 grid(static_cast<unsigned>(blocks), la.feat / (W * LPR));

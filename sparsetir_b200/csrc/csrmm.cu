@@ -405,11 +405,13 @@ int csrmm_impl(const float* a, const float* b, float* c, const int32_t* indptr, 
 
 // For matrices of very short rows (the aggregation launch of RGMS: 2.2 entries per row), where the
 // kernel is bound by instruction issue: 32-byte lanes halve the instructions per gathered byte
-// (60 -> 56.5 us at 690,812 rows x 64 features), although they lose on long rows.
+// (60 -> 56.5 us at 690,812 rows x 64 features), although they lose on long rows and on launches
+// too small to fill the SMs with the halved number of lanes (a quarter of those rows: 64 against
+// 58 us for the whole operator), so they are taken from half a million rows up.
 int csrmm_short_rows_impl(const float* a, const float* b, float* c, const int32_t* indptr,
                           const int32_t* indices, int m, int n, int feat, int nnz, int device_id,
                           void* stream) {
-  return csrmm_run(a, b, c, indptr, indices, m, n, feat, nnz, device_id, stream, false, 8);
+  return csrmm_run(a, b, c, indptr, indices, m, n, feat, nnz, device_id, stream, false, m >= (1 << 19) ? 8 : 0);
 }
 }  // namespace sptir
 

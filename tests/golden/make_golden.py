@@ -76,8 +76,11 @@ class _GraphStandIn:
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference", help="SparseTIR checkout")
+    ap.add_argument("--reference", default=os.environ.get("SPARSETIR_REFERENCE"),
+                    help="SparseTIR checkout (or set SPARSETIR_REFERENCE)")
     ref_root = ap.parse_args().reference
+    if not ref_root:
+        ap.error("give the SparseTIR checkout with --reference or SPARSETIR_REFERENCE")
     fns = reference_test_functions(ref_root, ("scipy_column_part_hyb", "condense_py"))
     hyb_fn, hyb_lines = fns["scipy_column_part_hyb"]
     cond_fn, cond_lines = fns["condense_py"]

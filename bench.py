@@ -520,8 +520,9 @@ def ours_arm(args, rank, world, local_rank):
                          "alg_gbs": byts / (per_f_ms[f] * 1e-3) / 1e9,
                          "hbm_frac": byts / (per_f_ms[f] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
 
-    # ---- CPU baseline on the host cores (bounded sample), OpenMP and serial
-    cpu = cpu_legs(g, {f: x_host[f].numpy() for f in FEATS}, total_flops)
+    # ---- CPU baseline on the host cores (bounded sample), OpenMP and serial: one-GPU runs only
+    # (with N ranks on the box the other processes' threads would share the cores it is timed on)
+    cpu = cpu_legs(g, {f: x_host[f].numpy() for f in FEATS}, total_flops) if world == 1 else None
 
     # ---- the same step with 2 and 4 column partitions (every contribution added atomically into
     # a C that the call clears first), one GPU only
